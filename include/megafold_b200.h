@@ -207,6 +207,9 @@ MF_API int mf_version(void);                     /* MF_ABI_VERSION the library w
 MF_API uint64_t mf_kernel_launch_count(void);
 /* Name of the kernel family the last successful call on this thread used: "tcgen05" or "simt". */
 MF_API const char* mf_last_path(void);
+/* Non-zero once a kernel on the current device gave up on one of its bounded waits (its outputs are
+ * then invalid).  Readable without a device synchronisation; sticky until the process ends. */
+MF_API int mf_async_status(void);
 
 #ifdef __cplusplus
 }

@@ -92,6 +92,7 @@ SYMBOLS = {
     "mf_version": (C.c_int, []),
     "mf_kernel_launch_count": (C.c_uint64, []),
     "mf_last_path": (C.c_char_p, []),
+    "mf_async_status": (C.c_int, []),
 }
 
 _lib = None

@@ -69,7 +69,7 @@ int mf_evo_fwd(const mf_evo_fwd_args* args, void* stream) {
 }
 
 static bool evo_bwd_use_tc(const mf_evo_bwd_args& a) {
-  return !(a.flags & MF_FLAG_FORCE_SIMT) &&
+  return !(a.flags & MF_FLAG_FORCE_SIMT) && evo_bwd_tc_available() &&
          evo_tc_supported(a.B, a.N, a.L, a.H, a.D, a.dtype, a.q_strides, a.k_strides, a.v_strides, a.q, a.k, a.v);
 }
 
@@ -196,5 +196,6 @@ const char* mf_last_error_string(void) { return last_error_buf(); }
 int mf_version(void) { return MF_ABI_VERSION; }
 uint64_t mf_kernel_launch_count(void) { return g_launches.load(); }
 const char* mf_last_path(void) { return t_last_path; }
+int mf_async_status(void) { return tc_async_status(); }
 
 }  // extern "C"

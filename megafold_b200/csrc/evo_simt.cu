@@ -195,7 +195,8 @@ __global__ void __launch_bounds__(kWarps * 32) evo_bwd_dq_simt_kernel(EvoP p) {
         s += load_rt(p.bias, b * p.bs[0] + h * p.bs[1] + (int64_t)i * p.bs[2] + j * p.bs[3], p.bias_dtype);
         const float mt = mask_term(p.mask, b * p.ms[0] + n * p.ms[1] + j * p.ms[2], p.mask_dtype);
         s += mt;
-        const float pr = expf(s - lse);
+        // a row whose keys are all masked has lse = -FLT_MAX (log l is absorbed): it is uniform over its L keys
+        const float pr = lse <= -3e38f ? 1.f / p.L : expf(s - lse);
         // a masked logit is a constant (masked_fill): no gradient flows into q, k or the bias through it,
         // which only matters for a row whose keys are ALL masked (elsewhere pr is exactly 0)
         ds = mt <= -FLT_MAX ? 0.f : pr * (dp - dl);
@@ -270,7 +271,8 @@ __global__ void __launch_bounds__(kWarps * 32) evo_bwd_dkv_simt_kernel(EvoP p) {
       const int64_t srow = (((int64_t)b * p.N + n) * p.H + h) * p.L + i;
       s += load_rt(p.bias, b * p.bs[0] + h * p.bs[1] + (int64_t)i * p.bs[2] + j * p.bs[3], p.bias_dtype);
       s += mt;
-      pr = expf(s - p.lse[srow]);
+      const float lse = p.lse[srow];
+      pr = lse <= -3e38f ? 1.f / p.L : expf(s - lse);
       ds = mt <= -FLT_MAX ? 0.f : pr * (dp - p.delta[srow]);
     }
     for (int ii = 0; ii < kTile; ++ii) {

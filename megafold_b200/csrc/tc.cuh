@@ -39,6 +39,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// Non-blocking probe of a phase: for role loops that watch several barriers at once (try_wait may
+// suspend the thread on one barrier while another one is already complete).
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 // Bounded wait.  try_wait itself blocks for a hardware-defined slice, so the cap below is many
 // milliseconds of wall time; a healthy pipeline never comes close.
 constexpr uint32_t kWaitCap = 4u << 20;
