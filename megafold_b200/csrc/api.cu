@@ -69,7 +69,7 @@ int mf_evo_fwd(const mf_evo_fwd_args* args, void* stream) {
 }
 
 static bool evo_bwd_use_tc(const mf_evo_bwd_args& a) {
-  return !(a.flags & MF_FLAG_FORCE_SIMT) && evo_bwd_tc_available() &&
+  return !(a.flags & MF_FLAG_FORCE_SIMT) && evo_bwd_tc_available() && evo_bwd_tc_shape_ok(a.L, a.D) &&
          evo_tc_supported(a.B, a.N, a.L, a.H, a.D, a.dtype, a.q_strides, a.k_strides, a.v_strides, a.q, a.k, a.v);
 }
 

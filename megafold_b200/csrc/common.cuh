@@ -124,6 +124,7 @@ size_t evo_bwd_simt_workspace(const mf_evo_bwd_args& a);
 bool evo_tc_supported(int B, int N, int L, int H, int D, int dtype, const int64_t* qs, const int64_t* ks,
                       const int64_t* vs, const void* q, const void* k, const void* v);
 bool evo_bwd_tc_available();
+bool evo_bwd_tc_shape_ok(int L, int D);   // the dQ accumulators of all query tiles must fit in TMEM
 int tc_async_status();
 int evo_fwd_tc(const mf_evo_fwd_args& a, cudaStream_t st);
 int evo_bwd_tc(const mf_evo_bwd_args& a, cudaStream_t st);

@@ -1,0 +1,445 @@
+// Pair-biased masked attention backward on the tensor cores (tcgen05 + TMEM + TMA): dQ, dK, dV and dBias.
+//
+// One CTA (256 threads, one per SM, persistent) owns a whole (b, n, h) at a time and walks its
+// 128-key tiles j and, inside, its 128-query tiles i.  Everything is computed TRANSPOSED, keys on the
+// TMEM lanes:
+//
+//   S^T  = K_j Q_i^T,   dP^T = V_j dO_i^T                       (tcgen05.mma, both into TMEM)
+//   thread (w, r): key row r, query half w -> 64 columns of S^T and dP^T into registers, then
+//   P^T  = exp2(S^T c1 + bias log2e + mask_j - lse2_i),   dS^T = P^T (dP^T - delta_i)
+//   written as 16-bit tiles to shared memory ([128 keys][2 x 64 queries], 128-byte rows, 128B swizzle)
+//   dV_j += P^T dO_i      A = P^T tile (K-major),  B = dO_i tile (MN-major)
+//   dK_j += dS^T Q_i      A = dS^T tile (K-major), B = Q_i tile  (MN-major)
+//   dQ_i += dS K_j        A = the same dS^T tile read MN-major (M = queries), B = K_j tile (MN-major)
+//
+// dK_j / dV_j accumulate in TMEM over the query tiles, dQ_i (one accumulator per query tile, all kept in
+// TMEM for the whole item) over the key tiles; nothing is reduced across CTAs, so dQ/dK/dV are
+// bit-reproducible.  The scores for the next block are issued as soon as the current ones have been read
+// into registers.  dBias is the sum of dS over the N rows that share the bias: every row adds its dS to
+// an fp32 buffer with coalesced red.global.add (lanes = consecutive keys), the same scheme as the
+// reference's atomic adds; its summation order is not fixed.
+//
+// delta_i = rowsum(dO_i * O_i) comes from a small pre-kernel.  All waits are bounded (see tc.cuh).
+#include "evo_tc_common.cuh"
+
+namespace mf {
+namespace {
+using namespace tcx;
+
+constexpr int kT = 128;            // tile edge (keys and queries)
+constexpr int kThreads = 256;
+constexpr int kTileP = 2 * 128 * 128;   // bytes of a [128 x 128] 16-bit tile (two 64-wide atoms)
+
+template <int DP> struct Cfg {
+  static constexpr int ROWB = DP * 2;
+  static constexpr int TILEB = 128 * ROWB;
+  static constexpr Swizzle SW = DP == 32 ? kSw64 : kSw128;
+  static constexpr int SBO = 8 * ROWB;
+  static constexpr int MAX_QT = (512 - 256 - 2 * DP) / DP;   // dQ accumulators that fit next to S^T, dP^T, dK, dV
+};
+
+struct BwdP {
+  int B, N, L, H, D;
+  int n_t, n_items, lpad;
+  float c1, scale, inv_L;
+  uint32_t ab_fmt;
+  const void* bias; int64_t bs[4];
+  const void* mask; int64_t ms[3]; int mask_dtype;
+  const float* lse; const float* delta;
+  void *dq, *dk, *dv; float* dbias;      // dbias: fp32 [B, H, L, L], zeroed by the host side
+  int* status;
+};
+
+struct Bars {
+  uint64_t kv_full[2], qd_full[3], sd_ready, acc_done;
+};
+
+template <typename T>
+__global__ void evo_delta_tc_kernel(const T* __restrict__ o, const T* __restrict__ d_o, float* __restrict__ delta,
+                                    int64_t rows, int L, int H, int D) {
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  float s = 0.f;
+  for (int d = lane; d < D; d += 32) s = fmaf(to_f(o[row * D + d]), to_f(d_o[row * D + d]), s);
+  s = warp_sum(s);
+  if (lane == 0) {
+    int h = row % H; int64_t t = row / H; int i = t % L; int64_t bn = t / L;
+    delta[(bn * H + h) * L + i] = s;
+  }
+}
+
+template <typename T>
+__global__ void cast_f32_kernel(const float* __restrict__ src, T* __restrict__ dst, int64_t n) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) dst[i] = from_f<T>(src[i]);
+}
+
+template <int DP, typename T, typename TB>
+__global__ void __launch_bounds__(kThreads, 1)
+evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mk,
+                  const __grid_constant__ CUtensorMap mv, const __grid_constant__ CUtensorMap mg, const BwdP p) {
+  using C = Cfg<DP>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* sP = smem;                         // P^T tile
+  uint8_t* sDS = sP + kTileP;                 // dS^T tile
+  uint8_t* sKV = sDS + kTileP;                // [2 stages][K, V]
+  uint8_t* sQD = sKV + 4 * C::TILEB;          // [3 stages][Q, dO]
+  float* lse2 = reinterpret_cast<float*>(sQD + 6 * C::TILEB);
+  float* dlt = lse2 + p.lpad;
+
+  __shared__ Bars bar;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_s;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int w = warp >> 2;                          // query half handled by this thread
+  const int r = (warp & 3) * 32 + lane;             // TMEM lane = key row inside the tile
+  if (tid == 0) {
+    abort_s = 0;
+    mbar_init(&bar.kv_full[0], 1); mbar_init(&bar.kv_full[1], 1);
+    mbar_init(&bar.qd_full[0], 1); mbar_init(&bar.qd_full[1], 1); mbar_init(&bar.qd_full[2], 1);
+    mbar_init(&bar.sd_ready, 1);
+    mbar_init(&bar.acc_done, 3);
+    mbar_fence_init();
+    prefetch_tmap(&mq); prefetch_tmap(&mk); prefetch_tmap(&mv); prefetch_tmap(&mg);
+  }
+  if (warp == 0) { tmem_alloc(&tmem_base_s, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  volatile int* abort_flag = &abort_s;
+  const uint32_t tm0 = tmem_base_s;
+  const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+  const uint32_t tST = tm0, tDP = tm0 + 128, tDK = tm0 + 256, tDV = tm0 + 256 + DP, tDQ = tm0 + 256 + 2 * DP;
+  const uint32_t id_s = idesc_f16(128, 128, p.ab_fmt, 0, 0);
+  const uint32_t id_kv = idesc_f16(128, DP, p.ab_fmt, 0, 1);    // A K-major, B MN-major
+  const uint32_t id_q = idesc_f16(128, DP, p.ab_fmt, 1, 1);     // A MN-major, B MN-major
+  // officers: MMA issue is split over three threads (one per accumulator), TMA on a fourth
+  const bool off_s = tid == 0, off_dv = tid == 0, off_dk = tid == 32, off_dq = tid == 64, off_tma = tid == 96;
+  const TB* bias = static_cast<const TB*>(p.bias);
+  const int nt = p.n_t, blocks_per_item = nt * nt;
+
+  uint32_t g = 0;                 // blocks processed by this CTA: sd_ready / acc_done parity g & 1;
+                                  // Q/dO tile of block g lives in stage g % 3 (qd_full parity (g / 3) & 1)
+  uint32_t kv_cnt = 0;            // (item, j) pairs so far: K/V stage kv_cnt & 1, kv_full parity (kv_cnt >> 1) & 1
+  bool dead = false;
+  auto qd_stage = [&](uint32_t gg) { return sQD + (gg % 3) * 2 * C::TILEB; };
+  auto load_qd = [&](uint32_t gg, int it2, int h, int n, int b) {
+    uint64_t* fb = &bar.qd_full[gg % 3];
+    mbar_expect_tx(fb, 2 * C::TILEB);
+    tma_load_5d(qd_stage(gg), &mq, fb, 0, h, it2 * kT, n, b);
+    tma_load_5d(qd_stage(gg) + C::TILEB, &mg, fb, 0, h, it2 * kT, n, b);
+  };
+  auto load_kv = [&](uint32_t kc, int jt2, int h, int n, int b) {
+    uint64_t* fb = &bar.kv_full[kc & 1];
+    mbar_expect_tx(fb, 2 * C::TILEB);
+    tma_load_5d(sKV + (kc & 1) * 2 * C::TILEB, &mk, fb, 0, h, jt2 * kT, n, b);
+    tma_load_5d(sKV + (kc & 1) * 2 * C::TILEB + C::TILEB, &mv, fb, 0, h, jt2 * kT, n, b);
+  };
+  auto issue_scores = [&](uint32_t gg, uint32_t kc) {     // S^T = K Q^T and dP^T = V dO^T of block gg
+    const uint32_t ka = smem_u32(sKV + (kc & 1) * 2 * C::TILEB), va = ka + C::TILEB;
+    const uint32_t qa = smem_u32(qd_stage(gg)), ga = qa + C::TILEB;
+#pragma unroll
+    for (int ks = 0; ks < DP / 16; ++ks)
+      mma_ss(tST, smem_desc(ka + ks * 32, 16, C::SBO, C::SW), smem_desc(qa + ks * 32, 16, C::SBO, C::SW), id_s, ks > 0);
+#pragma unroll
+    for (int ks = 0; ks < DP / 16; ++ks)
+      mma_ss(tDP, smem_desc(va + ks * 32, 16, C::SBO, C::SW), smem_desc(ga + ks * 32, 16, C::SBO, C::SW), id_s, ks > 0);
+    tc_commit(&bar.sd_ready);
+  };
+
+  for (int item = blockIdx.x; item < p.n_items && !dead; item += gridDim.x) {
+    const int h = item % p.H, bn = item / p.H, n = bn % p.N, b = bn / p.N;
+    const int64_t stat_row = ((int64_t)bn * p.H + h) * p.L;
+    // ---- per-item statistics: lse in base 2 and delta; queries beyond L get lse = +inf (P = 0)
+    int special = 0;
+    for (int i = tid; i < p.lpad; i += kThreads) {
+      float l2 = INFINITY, dl = 0.f;
+      if (i < p.L) {
+        const float lv = p.lse[stat_row + i];
+        special |= lv <= -3e38f;
+        l2 = lv * kLog2e; dl = p.delta[stat_row + i];
+      }
+      lse2[i] = l2; dlt[i] = dl;
+    }
+    // barrier (also: everybody is done with the previous item's statistics); rows that are fully masked
+    // (lse = -FLT_MAX) switch the item to the careful path
+    special = named_sync_or(1, kThreads, special) ? 1 : 0;
+
+    if (off_tma) {
+      // first K/V of the item and the Q/dO tiles of its first two blocks (their stages were drained by the previous item)
+      load_kv(kv_cnt, 0, h, n, b);
+      load_qd(g, 0, h, n, b);
+      if (blocks_per_item > 1) load_qd(g + 1, 1 % nt, h, n, b);
+    }
+    if (off_s) {
+      wait_or_flag(&bar.kv_full[kv_cnt & 1], (kv_cnt >> 1) & 1, abort_flag);
+      wait_or_flag(&bar.qd_full[g % 3], (g / 3) & 1, abort_flag);
+      tc_fence_after();
+      if (!*abort_flag) issue_scores(g, kv_cnt);
+    }
+
+    for (int jt = 0; jt < nt && !dead; ++jt) {
+      const int j = jt * kT + r;
+      const bool j_ok = j < p.L;
+      float mask2 = -INFINITY;
+      if (j_ok) {
+        const int64_t mi = b * p.ms[0] + n * p.ms[1] + (int64_t)j * p.ms[2];
+        mask2 = p.mask_dtype == MF_U8 ? (static_cast<const uint8_t*>(p.mask)[mi] ? 0.f : -FLT_MAX)
+                                      : load_rt(p.mask, mi, p.mask_dtype) * kLog2e;
+      }
+      const bool masked_key = mask2 <= -FLT_MAX;
+      for (int it = 0; it < nt; ++it, ++g) {
+        const int i0 = it * kT + w * 64;
+        const bool last_block = (jt == nt - 1) && (it == nt - 1);
+        // ---- bias column of this key for the 64 queries: coalesced over the warp's 32 keys
+        float bv[64];
+        {
+          const TB* bp = bias + b * p.bs[0] + h * p.bs[1] + (int64_t)j * p.bs[3];
+#pragma unroll
+          for (int c = 0; c < 64; ++c) bv[c] = (j_ok && i0 + c < p.L) ? to_f(bp[(int64_t)(i0 + c) * p.bs[2]]) : 0.f;
+        }
+        // ---- S^T, dP^T of this block -> registers
+        wait_or_flag(&bar.sd_ready, g & 1, abort_flag);
+        tc_fence_after();
+        uint32_t sr[64], dr[64];
+        {
+          uint32_t (*s2)[32] = reinterpret_cast<uint32_t (*)[32]>(sr);
+          uint32_t (*d2)[32] = reinterpret_cast<uint32_t (*)[32]>(dr);
+          tmem_ld32(tST + lane_addr + w * 64, s2[0]); tmem_ld32(tST + lane_addr + w * 64 + 32, s2[1]);
+          tmem_ld32(tDP + lane_addr + w * 64, d2[0]); tmem_ld32(tDP + lane_addr + w * 64 + 32, d2[1]);
+          tmem_ld_wait();
+        }
+        tc_fence_before();
+        if (named_sync_or(1, kThreads, *abort_flag)) { dead = true; break; }
+        // ---- next block's scores (the S^T / dP^T buffers are free again)
+        const bool new_j = (it == nt - 1);
+        if (!last_block && off_s) {
+          const uint32_t kc = new_j ? kv_cnt + 1 : kv_cnt;
+          if (new_j) wait_or_flag(&bar.kv_full[kc & 1], (kc >> 1) & 1, abort_flag);
+          wait_or_flag(&bar.qd_full[(g + 1) % 3], ((g + 1) / 3) & 1, abort_flag);
+          tc_fence_after();
+          if (!*abort_flag) issue_scores(g + 1, kc);
+        }
+        // ---- P^T and dS^T for my 64 queries
+        uint32_t pp[32], dd[32];
+        float* dbrow = p.dbias + (((int64_t)b * p.H + h) * p.L) * p.L + j;      // + i * L
+#pragma unroll
+        for (int c4 = 0; c4 < 16; ++c4) {
+          const float4 l4 = *reinterpret_cast<const float4*>(lse2 + i0 + c4 * 4);
+          const float4 d4 = *reinterpret_cast<const float4*>(dlt + i0 + c4 * 4);
+          const float ls[4] = {l4.x, l4.y, l4.z, l4.w}, de[4] = {d4.x, d4.y, d4.z, d4.w};
+          float pv[4], dv[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int c = c4 * 4 + e;
+            const float x = fmaf(__uint_as_float(sr[c]), p.c1, fmaf(bv[c], kLog2e, mask2)) - ls[e];
+            float pr = ex2f(x);
+            if (special && ls[e] <= -3e38f) pr = j_ok ? p.inv_L : 0.f;       // fully masked row: uniform
+            float ds = pr * (__uint_as_float(dr[c]) - de[e]);
+            if (special && masked_key) ds = 0.f;                             // no gradient through a masked logit
+            pv[e] = pr; dv[e] = ds;
+            if (j_ok && i0 + c < p.L) asm volatile("red.global.add.f32 [%0], %1;" ::"l"(dbrow + (int64_t)(i0 + c) * p.L), "f"(ds) : "memory");
+          }
+          pp[c4 * 2] = Pack2<T>::pack(pv[0], pv[1]); pp[c4 * 2 + 1] = Pack2<T>::pack(pv[2], pv[3]);
+          dd[c4 * 2] = Pack2<T>::pack(dv[0], dv[1]); dd[c4 * 2 + 1] = Pack2<T>::pack(dv[2], dv[3]);
+        }
+        // the MMAs of the previous block have finished reading the P^T / dS^T tiles?
+        if (g > 0) wait_or_flag(&bar.acc_done, (g - 1) & 1, abort_flag);
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) {
+          const uint32_t off = w * 16384 + swz_offset(r, ch, 128);
+          *reinterpret_cast<uint4*>(sP + off) = make_uint4(pp[ch * 4], pp[ch * 4 + 1], pp[ch * 4 + 2], pp[ch * 4 + 3]);
+          *reinterpret_cast<uint4*>(sDS + off) = make_uint4(dd[ch * 4], dd[ch * 4 + 1], dd[ch * 4 + 2], dd[ch * 4 + 3]);
+        }
+        fence_async_smem();
+        tc_fence_before();
+        if (named_sync_or(1, kThreads, *abort_flag)) { dead = true; break; }
+        // ---- accumulate MMAs of this block, one officer per accumulator
+        {
+          const uint32_t kvb = smem_u32(sKV + (kv_cnt & 1) * 2 * C::TILEB);
+          const uint32_t qdb = smem_u32(qd_stage(g));
+          if (off_dv) {       // dV_j += P^T dO_i
+            tc_fence_after();
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks)
+              mma_ss(tDV, smem_desc(smem_u32(sP) + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024, kSw128),
+                     smem_desc(qdb + C::TILEB + ks * 16 * C::ROWB, 16, C::SBO, C::SW), id_kv, it > 0 || ks > 0);
+            tc_commit(&bar.acc_done);
+          }
+          if (off_dk) {       // dK_j += dS^T Q_i
+            tc_fence_after();
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks)
+              mma_ss(tDK, smem_desc(smem_u32(sDS) + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024, kSw128),
+                     smem_desc(qdb + ks * 16 * C::ROWB, 16, C::SBO, C::SW), id_kv, it > 0 || ks > 0);
+            tc_commit(&bar.acc_done);
+          }
+          if (off_dq) {       // dQ_i += dS K_j   (A = dS^T tile read MN-major: M = queries)
+            tc_fence_after();
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks)
+              mma_ss(tDQ + it * DP, smem_desc(smem_u32(sDS) + ks * 2048, 16384, 1024, kSw128),
+                     smem_desc(kvb + ks * 16 * C::ROWB, 16, C::SBO, C::SW), id_q, jt > 0 || ks > 0);
+            tc_commit(&bar.acc_done);
+          }
+        }
+        // ---- TMA one block ahead: the stage of block g-1 is free (its accumulate MMAs were awaited above) and
+        // takes the Q/dO tile of block g+2; the K/V of the next key tile goes to the stage of key tile jt-1
+        if (off_tma) {
+          const int k2 = jt * nt + it + 2;
+          if (k2 < blocks_per_item) load_qd(g + 2, k2 % nt, h, n, b);
+          if (it == 0 && jt + 1 < nt) load_kv(kv_cnt + 1, jt + 1, h, n, b);
+        }
+        if (new_j) {
+          // dK_j, dV_j are complete once this block's MMAs are done
+          wait_or_flag(&bar.acc_done, g & 1, abort_flag);
+          tc_fence_after();
+          uint32_t o32[DP];
+#pragma unroll
+          for (int cb = 0; cb < DP / 32; ++cb) tmem_ld32((w == 0 ? tDK : tDV) + lane_addr + cb * 32, *reinterpret_cast<uint32_t (*)[32]>(o32 + cb * 32));
+          tmem_ld_wait();
+          if (j_ok && !*abort_flag) {
+            const float sc = w == 0 ? p.scale : 1.f;
+            T* orow = static_cast<T*>(w == 0 ? p.dk : p.dv) + ((((int64_t)b * p.N + n) * p.L + j) * p.H + h) * p.D;
+#pragma unroll
+            for (int d8 = 0; d8 < DP / 8; ++d8) {
+              if (d8 * 8 < p.D) {
+                uint4 v;
+                v.x = Pack2<T>::pack(__uint_as_float(o32[d8 * 8]) * sc, __uint_as_float(o32[d8 * 8 + 1]) * sc);
+                v.y = Pack2<T>::pack(__uint_as_float(o32[d8 * 8 + 2]) * sc, __uint_as_float(o32[d8 * 8 + 3]) * sc);
+                v.z = Pack2<T>::pack(__uint_as_float(o32[d8 * 8 + 4]) * sc, __uint_as_float(o32[d8 * 8 + 5]) * sc);
+                v.w = Pack2<T>::pack(__uint_as_float(o32[d8 * 8 + 6]) * sc, __uint_as_float(o32[d8 * 8 + 7]) * sc);
+                *reinterpret_cast<uint4*>(orow + d8 * 8) = v;
+              }
+            }
+          }
+          tc_fence_before();
+        }
+      }
+      if (!dead) ++kv_cnt;
+    }
+    if (dead) break;
+    // ---- dQ of every query tile (all MMAs of the item are complete: acc_done of the last block was awaited)
+    tc_fence_after();
+    for (int it = w; it < nt; it += 2) {
+      const int i = it * kT + r;
+      uint32_t o32[DP];
+#pragma unroll
+      for (int cb = 0; cb < DP / 32; ++cb) tmem_ld32(tDQ + it * DP + lane_addr + cb * 32, *reinterpret_cast<uint32_t (*)[32]>(o32 + cb * 32));
+      tmem_ld_wait();
+      if (i < p.L && !*abort_flag) {
+        T* orow = static_cast<T*>(p.dq) + ((((int64_t)b * p.N + n) * p.L + i) * p.H + h) * p.D;
+#pragma unroll
+        for (int d8 = 0; d8 < DP / 8; ++d8) {
+          if (d8 * 8 < p.D) {
+            uint4 v;
+            v.x = Pack2<T>::pack(__uint_as_float(o32[d8 * 8]) * p.scale, __uint_as_float(o32[d8 * 8 + 1]) * p.scale);
+            v.y = Pack2<T>::pack(__uint_as_float(o32[d8 * 8 + 2]) * p.scale, __uint_as_float(o32[d8 * 8 + 3]) * p.scale);
+            v.z = Pack2<T>::pack(__uint_as_float(o32[d8 * 8 + 4]) * p.scale, __uint_as_float(o32[d8 * 8 + 5]) * p.scale);
+            v.w = Pack2<T>::pack(__uint_as_float(o32[d8 * 8 + 6]) * p.scale, __uint_as_float(o32[d8 * 8 + 7]) * p.scale);
+            *reinterpret_cast<uint4*>(orow + d8 * 8) = v;
+          }
+        }
+      }
+    }
+    tc_fence_before();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (tid == 0 && abort_s) *reinterpret_cast<volatile int*>(p.status) = 1;
+  if (warp == 0) tmem_dealloc(tmem_base_s, 512);
+}
+
+template <int DP, typename T, typename TB>
+int launch_bwd(const mf_evo_bwd_args& a, cudaStream_t st) {
+  using C = Cfg<DP>;
+  CUtensorMap mq, mk, mv, mg;
+  int r;
+  const int64_t cs[5] = {(int64_t)a.N * a.L * a.H * a.D, (int64_t)a.L * a.H * a.D, (int64_t)a.H * a.D, a.D, 1};
+  if ((r = make_qkv_map(&mq, a.q, a.dtype, a.B, a.N, a.L, a.H, a.D, a.q_strides, DP, kT))) return r;
+  if ((r = make_qkv_map(&mk, a.k, a.dtype, a.B, a.N, a.L, a.H, a.D, a.k_strides, DP, kT))) return r;
+  if ((r = make_qkv_map(&mv, a.v, a.dtype, a.B, a.N, a.L, a.H, a.D, a.v_strides, DP, kT))) return r;
+  if ((r = make_qkv_map(&mg, a.d_o, a.dtype, a.B, a.N, a.L, a.H, a.D, cs, DP, kT))) return r;
+  BwdP p{};
+  p.B = a.B; p.N = a.N; p.L = a.L; p.H = a.H; p.D = a.D;
+  p.n_t = (a.L + kT - 1) / kT;
+  p.n_items = a.B * a.N * a.H;
+  p.lpad = p.n_t * kT;
+  p.scale = 1.0f / sqrtf((float)a.D);
+  p.c1 = kLog2e * p.scale;
+  p.inv_L = 1.0f / a.L;
+  p.ab_fmt = a.dtype == MF_BF16 ? 1u : 0u;
+  p.bias = a.bias; for (int i = 0; i < 4; ++i) p.bs[i] = a.bias_strides[i];
+  p.mask = a.mask; for (int i = 0; i < 3; ++i) p.ms[i] = a.mask_strides[i];
+  p.mask_dtype = a.mask_dtype;
+  p.lse = a.lse;
+  p.dq = a.dq; p.dk = a.dk; p.dv = a.dv;
+  p.status = status_word();
+  MF_REQUIRE(p.status, MF_ERR_CUDA, "could not allocate the device status word");
+  MF_REQUIRE(tc_async_status() == 0, MF_ERR_CUDA, "an earlier tensor-core kernel gave up on a bounded wait; results are invalid");
+  // workspace: delta [B,N,H,L] fp32, then (if d_bias is not fp32) the fp32 dBias accumulator
+  float* delta = static_cast<float*>(a.workspace);
+  const size_t delta_bytes = align_up(sizeof(float) * (size_t)a.B * a.N * a.H * a.L, 256);
+  const int64_t nb = (int64_t)a.B * a.H * a.L * a.L;
+  float* dbias = a.dbias_dtype == MF_F32 ? static_cast<float*>(a.d_bias)
+                                         : reinterpret_cast<float*>(static_cast<char*>(a.workspace) + delta_bytes);
+  p.delta = delta; p.dbias = dbias;
+  const int64_t rows = (int64_t)a.B * a.N * a.L * a.H;
+  evo_delta_tc_kernel<T><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(static_cast<const T*>(a.o), static_cast<const T*>(a.d_o),
+                                                                      delta, rows, a.L, a.H, a.D);
+  MF_LAUNCHED("evo_delta_tc_kernel");
+  MF_CUDA(cudaMemsetAsync(dbias, 0, sizeof(float) * nb, st));
+  const size_t smem = 1024 + 2 * kTileP + 10 * (size_t)C::TILEB + 2 * sizeof(float) * p.lpad;
+  auto kern = evo_bwd_tc_kernel<DP, T, TB>;
+  MF_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  int grid = sm_count();
+  if (grid > p.n_items) grid = p.n_items;
+  kern<<<grid, kThreads, smem, st>>>(mq, mk, mv, mg, p);
+  MF_LAUNCHED("evo_bwd_tc_kernel");
+  if (a.dbias_dtype != MF_F32) {
+    cast_f32_kernel<T><<<(unsigned)((nb + 255) / 256), 256, 0, st>>>(dbias, static_cast<T*>(a.d_bias), nb);
+    MF_LAUNCHED("cast_f32_kernel");
+  }
+  return MF_OK;
+}
+
+}  // namespace
+
+bool evo_bwd_tc_shape_ok(int L, int D) {
+  const int nt = (L + kT - 1) / kT;
+  return D <= 32 ? nt <= Cfg<32>::MAX_QT : nt <= Cfg<64>::MAX_QT;
+}
+
+size_t evo_bwd_tc_workspace(const mf_evo_bwd_args& a) {
+  size_t b = align_up(sizeof(float) * (size_t)a.B * a.N * a.H * a.L, 256);
+  if (a.dbias_dtype != MF_F32) b += align_up(sizeof(float) * (size_t)a.B * a.H * a.L * a.L, 256);
+  return b;
+}
+
+#define MF_DISPATCH_BIAS(dt, TB, ...)                                         \
+  switch (dt) {                                                               \
+    case MF_F32: { using TB = float; __VA_ARGS__; } break;                    \
+    case MF_BF16: { using TB = __nv_bfloat16; __VA_ARGS__; } break;           \
+    case MF_F16: { using TB = __half; __VA_ARGS__; } break;                   \
+    default: return fail(MF_ERR_BAD_ARG, "unknown bias dtype %d", (int)(dt)); \
+  }
+
+int evo_bwd_tc(const mf_evo_bwd_args& a, cudaStream_t st) {
+  int r = MF_OK;
+  if (a.dtype == MF_BF16) {
+    MF_DISPATCH_BIAS(a.bias_dtype, TB, {
+      r = a.D <= 32 ? launch_bwd<32, __nv_bfloat16, TB>(a, st) : launch_bwd<64, __nv_bfloat16, TB>(a, st);
+    });
+  } else {
+    MF_DISPATCH_BIAS(a.bias_dtype, TB, {
+      r = a.D <= 32 ? launch_bwd<32, __half, TB>(a, st) : launch_bwd<64, __half, TB>(a, st);
+    });
+  }
+  return r;
+}
+
+}  // namespace mf

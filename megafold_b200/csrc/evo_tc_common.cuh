@@ -1,0 +1,159 @@
+// Pieces shared by the tensor-core attention kernels (forward, backward, bias gradient):
+// bounded waits with a CTA-wide abort flag, 16-bit packing, base-2 exponentials, tensor-map
+// construction and the host-visible status word.
+#pragma once
+
+#include <cuda.h>
+
+#include <mutex>
+
+#include "common.cuh"
+#include "tc.cuh"
+
+namespace mf {
+namespace tcx {
+using namespace tc;
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+// Waits for a phase; on expiry raises the CTA's abort flag and returns (the caller carries on to its
+// next group barrier, where everybody sees the flag and leaves the loop).
+__device__ __forceinline__ void wait_or_flag(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < kWaitCap; ++i) {
+    if (mbar_try_wait(bar, parity)) return;
+    if ((i & 63u) == 63u && *abort_flag) return;
+  }
+  *abort_flag = 1;
+}
+__device__ __forceinline__ void named_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+// Group barrier that also ORs a flag over the group: every thread gets the same answer, so the whole
+// group takes the same exit decision.
+__device__ __forceinline__ bool named_sync_or(int id, int threads, int flag) {
+  uint32_t out;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 p, %3, 0;\n\t"
+      "bar.red.or.pred q, %1, %2, p;\n\t"
+      "selp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(out)
+      : "r"(id), "r"(threads), "r"(flag)
+      : "memory");
+  return out != 0;
+}
+__device__ __forceinline__ float ex2f(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float lg2f(float x) {
+  float y;
+  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <typename T> struct Pack2;
+template <> struct Pack2<__nv_bfloat16> {
+  static __device__ __forceinline__ uint32_t pack(float a, float b) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+  static __device__ __forceinline__ float2 unpack(uint32_t u) {
+    return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xffff0000u));
+  }
+};
+template <> struct Pack2<__half> {
+  static __device__ __forceinline__ uint32_t pack(float a, float b) {
+    __half2 v = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+  static __device__ __forceinline__ float2 unpack(uint32_t u) {
+    return __half22float2(*reinterpret_cast<__half2*>(&u));
+  }
+};
+template <> struct Pack2<float> {   // only so that code templated on the bias type compiles; never packed
+  static __device__ __forceinline__ float2 unpack(uint32_t u) { return make_float2(__uint_as_float(u), 0.f); }
+};
+
+// 4-D tiled TMA load
+__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* m, uint64_t* bar, int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
+// ---- host side ------------------------------------------------------------------------------------
+typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                             const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                             CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeFn encode_fn() {
+  static EncodeFn fn = [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess) f = nullptr;
+    return reinterpret_cast<EncodeFn>(f);
+  }();
+  return fn;
+}
+
+inline CUtensorMapDataType tm_dtype(int dt) {
+  return dt == MF_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : dt == MF_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                                         : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+}
+inline CUtensorMapSwizzle tm_swizzle(int row_bytes) {
+  return row_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : row_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+       : row_bytes == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE;
+}
+
+// Generic tiled map: `rank` dims, innermost first; strides in ELEMENTS for dims 1..rank-1 (dim 0 is unit
+// stride).  Dims of size 1 get a dummy 16-byte stride.  The box's innermost extent times the element size
+// must equal the swizzle width (`row_bytes`).
+inline int make_tiled_map(CUtensorMap* m, const void* ptr, int dtype, int rank, const int64_t* dims, const int64_t* strides,
+                          const int* box, int row_bytes) {
+  EncodeFn enc = encode_fn();
+  MF_REQUIRE(enc, MF_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  const int64_t es = (int64_t)dtype_size(dtype);
+  cuuint64_t gdim[5], gstr[4];
+  cuuint32_t bx[5], estr[5];
+  for (int i = 0; i < rank; ++i) { gdim[i] = (cuuint64_t)dims[i]; bx[i] = (cuuint32_t)box[i]; estr[i] = 1; }
+  for (int i = 1; i < rank; ++i) gstr[i - 1] = (cuuint64_t)((dims[i] == 1 || strides[i] <= 0) ? 16 : strides[i] * es);
+  CUresult r = enc(m, tm_dtype(dtype), (cuuint32_t)rank, const_cast<void*>(ptr), gdim, gstr, bx, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, tm_swizzle(row_bytes), CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  MF_REQUIRE(r == CUDA_SUCCESS, MF_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return MF_OK;
+}
+
+// 5-D map over a [B, N, L, H, D] operand (element strides s = {b, n, l, h, d}); box = DP x 1 x rows x 1 x 1
+inline int make_qkv_map(CUtensorMap* m, const void* ptr, int dtype, int B, int N, int L, int H, int D, const int64_t* s,
+                        int DP, int rows) {
+  const int64_t dims[5] = {D, H, L, N, B};
+  const int64_t str[5] = {1, s[3], s[2], s[1], s[0]};
+  const int box[5] = {DP, 1, rows, 1, 1};
+  return make_tiled_map(m, ptr, dtype, 5, dims, str, box, DP * 2);
+}
+
+inline bool qkv_strides_ok(const void* p, const int64_t* s, int B, int N, int L, int H) {
+  if ((reinterpret_cast<uintptr_t>(p) & 15) != 0 || s[4] != 1) return false;
+  const int sizes[4] = {B, N, L, H};
+  for (int i = 0; i < 4; ++i)
+    if (sizes[i] > 1 && (s[i] <= 0 || (s[i] % 8) != 0)) return false;
+  return true;
+}
+
+// Status word of the calling thread's device: pinned host memory mapped into the device, so that a
+// kernel that gave up on a bounded wait can say so and the host can read it without a device sync.
+struct StatusWord { int* host = nullptr; int* dev = nullptr; };
+StatusWord* status_slot();
+inline int* status_word() {
+  StatusWord* w = status_slot();
+  return w ? w->dev : nullptr;
+}
+int sm_count();
+
+}  // namespace tcx
+}  // namespace mf
