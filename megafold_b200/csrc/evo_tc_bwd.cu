@@ -44,11 +44,21 @@ struct BwdP {
   float c1, scale, inv_L;
   uint32_t ab_fmt;
   const void* bias; int64_t bs[4];
+  const void* biasT_;                    // transposed, row-padded copy of the bias (same dtype)
   const void* mask; int64_t ms[3]; int mask_dtype;
   const float* lse; const float* delta;
   void *dq, *dk, *dv; float* dbias;      // dbias: fp32 [B, H, L, L], zeroed by the host side
   int* status;
+  long long* timeline;   // debug builds only
 };
+
+// Phase timestamps of thread 0 of CTA 0; compiled in only with -DMF_TIMELINE.
+#ifdef MF_TIMELINE
+long long* g_timeline_bwd = nullptr;
+#define MF_TL(tag) do { if (p.timeline && blockIdx.x == 0 && tid == 0 && tl_n < 250) { p.timeline[2 * tl_n] = (tag); p.timeline[2 * tl_n + 1] = clock64(); ++tl_n; } } while (0)
+#else
+#define MF_TL(tag) do { } while (0)
+#endif
 
 struct Bars {
   uint64_t kv_full[2], qd_full[3], sd_ready, acc_done;
@@ -69,16 +79,81 @@ __global__ void evo_delta_tc_kernel(const T* __restrict__ o, const T* __restrict
   }
 }
 
+// dst[row][0..L) = src[row][0..L) with the source rows `pitch` floats apart
 template <typename T>
-__global__ void cast_f32_kernel(const float* __restrict__ src, T* __restrict__ dst, int64_t n) {
+__global__ void cast_rows_pitched_kernel(const float* __restrict__ src, T* __restrict__ dst, int64_t rows, int L, int pitch) {
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < n) dst[i] = from_f<T>(src[i]);
+  if (i >= rows * L) return;
+  const int64_t row = i / L; const int c = (int)(i - row * L);
+  dst[i] = from_f<T>(src[row * pitch + c]);
+}
+
+// biasT[b][h][j][i] = bias[b][h][i][j], rows padded to `lpad` entries so that every 64-query run is aligned
+// and in bounds.  The backward kernel works with keys on the TMEM lanes, so a thread needs the bias of ONE key
+// for a run of queries; with this copy that run is contiguous.
+template <typename TB>
+__global__ void transpose_bias_kernel(const TB* __restrict__ bias, TB* __restrict__ biasT, int H, int L, int lpad,
+                                      int64_t sb, int64_t sh, int64_t si, int64_t sj) {
+  __shared__ TB tile[32][33];
+  const int bh = blockIdx.z, b = bh / H, h = bh % H;
+  const int i0 = blockIdx.y * 32, j0 = blockIdx.x * 32;
+  for (int k = threadIdx.y; k < 32; k += blockDim.y) {
+    const int i = i0 + k, j = j0 + threadIdx.x;
+    if (i < L && j < L) tile[k][threadIdx.x] = bias[b * sb + h * sh + (int64_t)i * si + (int64_t)j * sj];
+  }
+  __syncthreads();
+  for (int k = threadIdx.y; k < 32; k += blockDim.y) {
+    const int j = j0 + k, i = i0 + threadIdx.x;
+    if (i < L && j < L) biasT[((int64_t)bh * L + j) * lpad + i] = tile[threadIdx.x][k];
+  }
+}
+
+// 64 consecutive bias values held in registers (packed for 16-bit types)
+template <typename TB> struct BiasRun {
+  uint4 v[8];
+  __device__ __forceinline__ void load(const TB* p) {
+    const uint4* q = reinterpret_cast<const uint4*>(p);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = __ldg(q + i);
+  }
+  __device__ __forceinline__ float get(int c) const {
+    const uint4& x = v[c >> 3];
+    const uint32_t u = ((c >> 1) & 3) == 0 ? x.x : ((c >> 1) & 3) == 1 ? x.y : ((c >> 1) & 3) == 2 ? x.z : x.w;
+    const float2 f = Pack2<TB>::unpack(u);
+    return (c & 1) ? f.y : f.x;
+  }
+};
+template <> struct BiasRun<float> {
+  float4 v[16];
+  __device__ __forceinline__ void load(const float* p) {
+    const float4* q = reinterpret_cast<const float4*>(p);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __ldg(q + i);
+  }
+  __device__ __forceinline__ float get(int c) const {
+    const float4& x = v[c >> 2];
+    return (c & 3) == 0 ? x.x : (c & 3) == 1 ? x.y : (c & 3) == 2 ? x.z : x.w;
+  }
+};
+
+// dBias staging: fp32 [16 queries][32 keys] per warp, pushed to global memory with a TMA add-reduction
+__device__ __forceinline__ void tma_reduce_add_4d(const CUtensorMap* m, const void* src, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+template <int N> __device__ __forceinline__ void bulk_wait() {
+  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
 }
 
 template <int DP, typename T, typename TB>
 __global__ void __launch_bounds__(kThreads, 1)
 evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mk,
-                  const __grid_constant__ CUtensorMap mv, const __grid_constant__ CUtensorMap mg, const BwdP p) {
+                  const __grid_constant__ CUtensorMap mv, const __grid_constant__ CUtensorMap mg,
+                  const __grid_constant__ CUtensorMap mdb, const BwdP p) {
   using C = Cfg<DP>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -96,6 +171,7 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int w = warp >> 2;                          // query half handled by this thread
   const int r = (warp & 3) * 32 + lane;             // TMEM lane = key row inside the tile
+  float* stage = dlt + p.lpad + warp * 1024;        // per warp: 2 buffers x [16 queries][32 keys] fp32
   if (tid == 0) {
     abort_s = 0;
     mbar_init(&bar.kv_full[0], 1); mbar_init(&bar.kv_full[1], 1);
@@ -118,13 +194,14 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
   const uint32_t id_q = idesc_f16(128, DP, p.ab_fmt, 1, 1);     // A MN-major, B MN-major
   // officers: MMA issue is split over three threads (one per accumulator), TMA on a fourth
   const bool off_s = tid == 0, off_dv = tid == 0, off_dk = tid == 32, off_dq = tid == 64, off_tma = tid == 96;
-  const TB* bias = static_cast<const TB*>(p.bias);
   const int nt = p.n_t, blocks_per_item = nt * nt;
 
   uint32_t g = 0;                 // blocks processed by this CTA: sd_ready / acc_done parity g & 1;
                                   // Q/dO tile of block g lives in stage g % 3 (qd_full parity (g / 3) & 1)
   uint32_t kv_cnt = 0;            // (item, j) pairs so far: K/V stage kv_cnt & 1, kv_full parity (kv_cnt >> 1) & 1
   bool dead = false;
+  int tl_n = 0; (void)tl_n;
+  uint32_t rnd = 0;               // dBias staging rounds of this warp (buffer = rnd & 1)
   auto qd_stage = [&](uint32_t gg) { return sQD + (gg % 3) * 2 * C::TILEB; };
   auto load_qd = [&](uint32_t gg, int it2, int h, int n, int b) {
     uint64_t* fb = &bar.qd_full[gg % 3];
@@ -194,16 +271,15 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
       for (int it = 0; it < nt; ++it, ++g) {
         const int i0 = it * kT + w * 64;
         const bool last_block = (jt == nt - 1) && (it == nt - 1);
-        // ---- bias column of this key for the 64 queries: coalesced over the warp's 32 keys
-        float bv[64];
-        {
-          const TB* bp = bias + b * p.bs[0] + h * p.bs[1] + (int64_t)j * p.bs[3];
-#pragma unroll
-          for (int c = 0; c < 64; ++c) bv[c] = (j_ok && i0 + c < p.L) ? to_f(bp[(int64_t)(i0 + c) * p.bs[2]]) : 0.f;
-        }
+        MF_TL(20);
+        // ---- bias for my key and my 64 queries: one contiguous run of the transposed copy biasT[b][h][j][i]
+        BiasRun<TB> bv;
+        bv.load(static_cast<const TB*>(p.biasT_) + (((int64_t)b * p.H + h) * p.L + (j_ok ? j : 0)) * p.lpad + i0);
+        MF_TL(21);
         // ---- S^T, dP^T of this block -> registers
         wait_or_flag(&bar.sd_ready, g & 1, abort_flag);
         tc_fence_after();
+        MF_TL(22);
         uint32_t sr[64], dr[64];
         {
           uint32_t (*s2)[32] = reinterpret_cast<uint32_t (*)[32]>(sr);
@@ -212,8 +288,10 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
           tmem_ld32(tDP + lane_addr + w * 64, d2[0]); tmem_ld32(tDP + lane_addr + w * 64 + 32, d2[1]);
           tmem_ld_wait();
         }
+        MF_TL(23);
         tc_fence_before();
         if (named_sync_or(1, kThreads, *abort_flag)) { dead = true; break; }
+        MF_TL(24);
         // ---- next block's scores (the S^T / dP^T buffers are free again)
         const bool new_j = (it == nt - 1);
         if (!last_block && off_s) {
@@ -223,9 +301,9 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
           tc_fence_after();
           if (!*abort_flag) issue_scores(g + 1, kc);
         }
+        MF_TL(25);
         // ---- P^T and dS^T for my 64 queries
         uint32_t pp[32], dd[32];
-        float* dbrow = p.dbias + (((int64_t)b * p.H + h) * p.L) * p.L + j;      // + i * L
 #pragma unroll
         for (int c4 = 0; c4 < 16; ++c4) {
           const float4 l4 = *reinterpret_cast<const float4*>(lse2 + i0 + c4 * 4);
@@ -235,17 +313,30 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const int c = c4 * 4 + e;
-            const float x = fmaf(__uint_as_float(sr[c]), p.c1, fmaf(bv[c], kLog2e, mask2)) - ls[e];
+            const float x = fmaf(__uint_as_float(sr[c]), p.c1, fmaf(bv.get(c), kLog2e, mask2)) - ls[e];
             float pr = ex2f(x);
             if (special && ls[e] <= -3e38f) pr = j_ok ? p.inv_L : 0.f;       // fully masked row: uniform
             float ds = pr * (__uint_as_float(dr[c]) - de[e]);
             if (special && masked_key) ds = 0.f;                             // no gradient through a masked logit
             pv[e] = pr; dv[e] = ds;
-            if (j_ok && i0 + c < p.L) asm volatile("red.global.add.f32 [%0], %1;" ::"l"(dbrow + (int64_t)(i0 + c) * p.L), "f"(ds) : "memory");
+            stage[(rnd & 1) * 512 + ((c4 & 3) * 4 + e) * 32 + lane] = ds;
+          }
+          if ((c4 & 3) == 3) {
+            // 16 queries x 32 keys of dS are staged: add them to dBias[b, h, i, j] (TMA clips rows/columns >= L)
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_reduce_add_4d(&mdb, stage + (rnd & 1) * 512, jt * kT + (warp & 3) * 32, i0 + (c4 >> 2) * 16, h, b);
+              bulk_commit();
+              bulk_wait_read<1>();      // the buffer written two rounds ago has been read: it may be refilled
+            }
+            __syncwarp();
+            ++rnd;
           }
           pp[c4 * 2] = Pack2<T>::pack(pv[0], pv[1]); pp[c4 * 2 + 1] = Pack2<T>::pack(pv[2], pv[3]);
           dd[c4 * 2] = Pack2<T>::pack(dv[0], dv[1]); dd[c4 * 2 + 1] = Pack2<T>::pack(dv[2], dv[3]);
         }
+        MF_TL(26);
         // the MMAs of the previous block have finished reading the P^T / dS^T tiles?
         if (g > 0) wait_or_flag(&bar.acc_done, (g - 1) & 1, abort_flag);
 #pragma unroll
@@ -256,7 +347,9 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
         }
         fence_async_smem();
         tc_fence_before();
+        MF_TL(27);
         if (named_sync_or(1, kThreads, *abort_flag)) { dead = true; break; }
+        MF_TL(28);
         // ---- accumulate MMAs of this block, one officer per accumulator
         {
           const uint32_t kvb = smem_u32(sKV + (kv_cnt & 1) * 2 * C::TILEB);
@@ -286,6 +379,7 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
             tc_commit(&bar.acc_done);
           }
         }
+        MF_TL(29);
         // ---- TMA one block ahead: the stage of block g-1 is free (its accumulate MMAs were awaited above) and
         // takes the Q/dO tile of block g+2; the K/V of the next key tile goes to the stage of key tile jt-1
         if (off_tma) {
@@ -348,6 +442,7 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
     tc_fence_before();
   }
 
+  if (lane == 0) bulk_wait<0>();      // my dBias reductions have left shared memory and reached global memory
   tc_fence_before();
   __syncthreads();
   if (tid == 0 && abort_s) *reinterpret_cast<volatile int*>(p.status) = 1;
@@ -357,7 +452,7 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
 template <int DP, typename T, typename TB>
 int launch_bwd(const mf_evo_bwd_args& a, cudaStream_t st) {
   using C = Cfg<DP>;
-  CUtensorMap mq, mk, mv, mg;
+  CUtensorMap mq, mk, mv, mg, mdb;
   int r;
   const int64_t cs[5] = {(int64_t)a.N * a.L * a.H * a.D, (int64_t)a.L * a.H * a.D, (int64_t)a.H * a.D, a.D, 1};
   if ((r = make_qkv_map(&mq, a.q, a.dtype, a.B, a.N, a.L, a.H, a.D, a.q_strides, DP, kT))) return r;
@@ -378,36 +473,64 @@ int launch_bwd(const mf_evo_bwd_args& a, cudaStream_t st) {
   p.mask_dtype = a.mask_dtype;
   p.lse = a.lse;
   p.dq = a.dq; p.dk = a.dk; p.dv = a.dv;
+#ifdef MF_TIMELINE
+  p.timeline = g_timeline_bwd;
+#endif
   p.status = status_word();
   MF_REQUIRE(p.status, MF_ERR_CUDA, "could not allocate the device status word");
   MF_REQUIRE(tc_async_status() == 0, MF_ERR_CUDA, "an earlier tensor-core kernel gave up on a bounded wait; results are invalid");
-  // workspace: delta [B,N,H,L] fp32, then (if d_bias is not fp32) the fp32 dBias accumulator
+  // workspace: delta [B,N,H,L] fp32 | fp32 dBias accumulator (unless d_bias itself can serve) | transposed bias
   float* delta = static_cast<float*>(a.workspace);
   const size_t delta_bytes = align_up(sizeof(float) * (size_t)a.B * a.N * a.H * a.L, 256);
-  const int64_t nb = (int64_t)a.B * a.H * a.L * a.L;
-  float* dbias = a.dbias_dtype == MF_F32 ? static_cast<float*>(a.d_bias)
-                                         : reinterpret_cast<float*>(static_cast<char*>(a.workspace) + delta_bytes);
+  const int lp4 = (a.L + 3) / 4 * 4;                 // TMA needs 16-byte row pitch
+  const bool direct = a.dbias_dtype == MF_F32 && lp4 == a.L;
+  const int64_t nb = (int64_t)a.B * a.H * a.L * lp4;
+  const size_t acc_bytes = direct ? 0 : align_up(sizeof(float) * (size_t)nb, 256);
+  float* dbias = direct ? static_cast<float*>(a.d_bias) : reinterpret_cast<float*>(static_cast<char*>(a.workspace) + delta_bytes);
   p.delta = delta; p.dbias = dbias;
+  {
+    const int64_t dims[4] = {a.L, a.L, a.H, a.B};
+    const int64_t str[4] = {1, lp4, (int64_t)a.L * lp4, (int64_t)a.H * a.L * lp4};
+    const int box[4] = {32, 16, 1, 1};
+    if ((r = make_tiled_map(&mdb, dbias, MF_F32, 4, dims, str, box, 0))) return r;
+  }
+  TB* biasT = reinterpret_cast<TB*>(static_cast<char*>(a.workspace) + delta_bytes + acc_bytes);
+  p.biasT_ = biasT;
+  {
+    MF_CUDA(cudaMemsetAsync(biasT, 0, sizeof(TB) * (size_t)a.B * a.H * a.L * p.lpad, st));
+    dim3 grid((a.L + 31) / 32, (a.L + 31) / 32, a.B * a.H), block(32, 8);
+    transpose_bias_kernel<TB><<<grid, block, 0, st>>>(static_cast<const TB*>(a.bias), biasT, a.H, a.L, p.lpad, a.bias_strides[0],
+                                                       a.bias_strides[1], a.bias_strides[2], a.bias_strides[3]);
+    MF_LAUNCHED("transpose_bias_kernel");
+  }
   const int64_t rows = (int64_t)a.B * a.N * a.L * a.H;
   evo_delta_tc_kernel<T><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(static_cast<const T*>(a.o), static_cast<const T*>(a.d_o),
                                                                       delta, rows, a.L, a.H, a.D);
   MF_LAUNCHED("evo_delta_tc_kernel");
   MF_CUDA(cudaMemsetAsync(dbias, 0, sizeof(float) * nb, st));
-  const size_t smem = 1024 + 2 * kTileP + 10 * (size_t)C::TILEB + 2 * sizeof(float) * p.lpad;
+  const size_t smem = 1024 + 2 * kTileP + 10 * (size_t)C::TILEB + 2 * sizeof(float) * p.lpad + 8 * 4096;
   auto kern = evo_bwd_tc_kernel<DP, T, TB>;
   MF_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int grid = sm_count();
   if (grid > p.n_items) grid = p.n_items;
-  kern<<<grid, kThreads, smem, st>>>(mq, mk, mv, mg, p);
+  kern<<<grid, kThreads, smem, st>>>(mq, mk, mv, mg, mdb, p);
   MF_LAUNCHED("evo_bwd_tc_kernel");
-  if (a.dbias_dtype != MF_F32) {
-    cast_f32_kernel<T><<<(unsigned)((nb + 255) / 256), 256, 0, st>>>(dbias, static_cast<T*>(a.d_bias), nb);
-    MF_LAUNCHED("cast_f32_kernel");
+  if (!direct) {
+    const int64_t rows_b = (int64_t)a.B * a.H * a.L, n_out = rows_b * a.L;
+    if (a.dbias_dtype == MF_F32)
+      cast_rows_pitched_kernel<float><<<(unsigned)((n_out + 255) / 256), 256, 0, st>>>(dbias, static_cast<float*>(a.d_bias), rows_b, a.L, lp4);
+    else
+      cast_rows_pitched_kernel<T><<<(unsigned)((n_out + 255) / 256), 256, 0, st>>>(dbias, static_cast<T*>(a.d_bias), rows_b, a.L, lp4);
+    MF_LAUNCHED("cast_rows_pitched_kernel");
   }
   return MF_OK;
 }
 
 }  // namespace
+
+#ifdef MF_TIMELINE
+extern "C" __attribute__((visibility("default"))) void mf_debug_set_timeline_bwd(long long* p) { g_timeline_bwd = p; }
+#endif
 
 bool evo_bwd_tc_shape_ok(int L, int D) {
   const int nt = (L + kT - 1) / kT;
@@ -416,7 +539,10 @@ bool evo_bwd_tc_shape_ok(int L, int D) {
 
 size_t evo_bwd_tc_workspace(const mf_evo_bwd_args& a) {
   size_t b = align_up(sizeof(float) * (size_t)a.B * a.N * a.H * a.L, 256);
-  if (a.dbias_dtype != MF_F32) b += align_up(sizeof(float) * (size_t)a.B * a.H * a.L * a.L, 256);
+  const size_t lp4 = (size_t)(a.L + 3) / 4 * 4;
+  if (!(a.dbias_dtype == MF_F32 && lp4 == (size_t)a.L)) b += align_up(sizeof(float) * (size_t)a.B * a.H * a.L * lp4, 256);
+  const size_t lpad = (size_t)((a.L + kT - 1) / kT) * kT;
+  b += align_up(dtype_size(a.bias_dtype) * (size_t)a.B * a.H * a.L * lpad, 256);     // transposed bias copy
   return b;
 }
 
