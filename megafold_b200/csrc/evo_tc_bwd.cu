@@ -64,19 +64,26 @@ struct Bars {
   uint64_t kv_full[2], qd_full[3], sd_ready, acc_done;
 };
 
+// delta[b,n,h,i] = sum_d dO * O; one thread per (b,n,i,h) row, 16-byte loads (D is a multiple of 8)
 template <typename T>
 __global__ void evo_delta_tc_kernel(const T* __restrict__ o, const T* __restrict__ d_o, float* __restrict__ delta,
                                     int64_t rows, int L, int H, int D) {
-  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int64_t row = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (row >= rows) return;
-  const int lane = threadIdx.x & 31;
+  const uint4* po = reinterpret_cast<const uint4*>(o + row * D);
+  const uint4* pg = reinterpret_cast<const uint4*>(d_o + row * D);
   float s = 0.f;
-  for (int d = lane; d < D; d += 32) s = fmaf(to_f(o[row * D + d]), to_f(d_o[row * D + d]), s);
-  s = warp_sum(s);
-  if (lane == 0) {
-    int h = row % H; int64_t t = row / H; int i = t % L; int64_t bn = t / L;
-    delta[(bn * H + h) * L + i] = s;
+  for (int c = 0; c < D / 8; ++c) {
+    const uint4 a = __ldg(po + c), g = __ldg(pg + c);
+    const uint32_t av[4] = {a.x, a.y, a.z, a.w}, gv[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 x = Pack2<T>::unpack(av[e]), y = Pack2<T>::unpack(gv[e]);
+      s = fmaf(x.x, y.x, s); s = fmaf(x.y, y.y, s);
+    }
   }
+  const int h = (int)(row % H); const int64_t t = row / H; const int i = (int)(t % L); const int64_t bn = t / L;
+  delta[(bn * H + h) * L + i] = s;
 }
 
 // dst[row][0..L) = src[row][0..L) with the source rows `pitch` floats apart
@@ -504,7 +511,7 @@ int launch_bwd(const mf_evo_bwd_args& a, cudaStream_t st) {
     MF_LAUNCHED("transpose_bias_kernel");
   }
   const int64_t rows = (int64_t)a.B * a.N * a.L * a.H;
-  evo_delta_tc_kernel<T><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(static_cast<const T*>(a.o), static_cast<const T*>(a.d_o),
+  evo_delta_tc_kernel<T><<<(unsigned)((rows + 255) / 256), 256, 0, st>>>(static_cast<const T*>(a.o), static_cast<const T*>(a.d_o),
                                                                       delta, rows, a.L, a.H, a.D);
   MF_LAUNCHED("evo_delta_tc_kernel");
   MF_CUDA(cudaMemsetAsync(dbias, 0, sizeof(float) * nb, st));

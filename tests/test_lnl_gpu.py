@@ -87,9 +87,9 @@ def test_swiglu_fp32_and_bf16():
     x = torch.randn(37, 2 * 24, generator=g)
     dy = torch.randn(37, 24, generator=g)
     for dtype, check in ((torch.float32, assert_close_fp32), (torch.bfloat16, assert_close_lowp)):
-        xr = x.to(dtype).float().requires_grad_(True)
+        xr = x.to(dtype).float().detach().clone().requires_grad_(True)
         orc.swiglu(xr).backward(dy.to(dtype).float())
-        xg = x.to(DEV, dtype).requires_grad_(True)
+        xg = x.detach().to(DEV, dtype).clone().requires_grad_(True)
         saved = xg.detach().clone()
         y = mfb.FusedSwiGLU()(xg)
         y.backward(dy.to(DEV, dtype))
