@@ -115,6 +115,30 @@ typedef struct mf_evo_bwd_args {
 MF_API size_t mf_evo_bwd_workspace_bytes(const mf_evo_bwd_args* args);
 MF_API int mf_evo_bwd(const mf_evo_bwd_args* args, void* stream);
 
+/*
+ * mf_evo_bwd without a workspace and without any allocation.  (No counterpart in the reference; added for
+ * hosts that cannot allocate.)
+ *
+ * Who needs it: a process that handed the whole of the GPU's memory to its own pool at start-up (so that a
+ * cudaMalloc would fail), or one that may not run into the device-wide synchronisation that cudaMalloc and
+ * cudaFree imply, has no way to provide the scratch buffer mf_evo_bwd asks for.  This variant keeps its
+ * scratch (one float per query row, i.e. B*N*H*L floats) in an array that is part of the library image:
+ * 4 MiB, held by every GPU that loads the library until the process exits.  It never calls cudaMalloc,
+ * cudaFree or any allocating library routine, and it ignores args->workspace / workspace_bytes.
+ *
+ *  - Limit: B*N*H*L <= mf_evo_bwd_noalloc_max_rows() (1,048,576); larger problems get MF_ERR_UNSUPPORTED and
+ *    must use mf_evo_bwd.
+ *  - It always runs the fp32 CUDA-core kernels (the tensor-core path needs more scratch), so its results
+ *    equal those of mf_evo_bwd called with MF_FLAG_FORCE_SIMT.
+ *  - The first call on a device looks up the device address of the built-in array (with that device
+ *    current); make that first call before any stream capture is begun.
+ *  - All calls share the one array.  Its previous contents do not matter (the kernels overwrite every entry
+ *    they read), but two calls whose kernels overlap on the GPU - different streams, or different host
+ *    threads - race on it: serialise them.
+ */
+MF_API int mf_evo_bwd_noalloc(const mf_evo_bwd_args* args, void* stream);
+MF_API size_t mf_evo_bwd_noalloc_max_rows(void);
+
 /* ------------------------------------------------------------------------------------------
  * LayernormLinear:  y[M,N] = LayerNorm_K(x[M,K]; ln_w, ln_b, eps) @ w[K,N] (+ b[N])
  *

@@ -79,6 +79,8 @@ SYMBOLS = {
     "mf_evo_fwd": (C.c_int, [C.POINTER(EvoFwdArgs), _vp]),
     "mf_evo_bwd_workspace_bytes": (_sz, [C.POINTER(EvoBwdArgs)]),
     "mf_evo_bwd": (C.c_int, [C.POINTER(EvoBwdArgs), _vp]),
+    "mf_evo_bwd_noalloc": (C.c_int, [C.POINTER(EvoBwdArgs), _vp]),
+    "mf_evo_bwd_noalloc_max_rows": (_sz, []),
     "mf_lnl_fwd": (C.c_int, [C.POINTER(LnlFwdArgs), _vp]),
     "mf_lnl_bwd_workspace_bytes": (_sz, [C.POINTER(LnlBwdArgs)]),
     "mf_lnl_bwd": (C.c_int, [C.POINTER(LnlBwdArgs), _vp]),

@@ -102,6 +102,22 @@ int mf_evo_bwd(const mf_evo_bwd_args* args, void* stream) {
   return r;
 }
 
+int mf_evo_bwd_noalloc(const mf_evo_bwd_args* args, void* stream) {
+  MF_REQUIRE(args, MF_ERR_BAD_ARG, "args is NULL");
+  const mf_evo_bwd_args& a = *args;
+  int r = check_evo_common(a); if (r) return r;
+  MF_REQUIRE(a.o && a.d_o && a.lse, MF_ERR_BAD_ARG, "o, d_o and lse must not be NULL");
+  MF_REQUIRE(a.dq && a.dk && a.dv && a.d_bias, MF_ERR_BAD_ARG, "dq, dk, dv and d_bias must not be NULL");
+  MF_REQUIRE(a.dbias_dtype == MF_F32 || a.dbias_dtype == a.dtype, MF_ERR_BAD_ARG,
+             "d_bias dtype must be fp32 or the q/k/v dtype");
+  r = check_device(); if (r) return r;
+  r = evo_bwd_simt_noalloc(a, static_cast<cudaStream_t>(stream));
+  if (r == MF_OK) set_last_path("simt");
+  return r;
+}
+
+size_t mf_evo_bwd_noalloc_max_rows(void) { return evo_bwd_noalloc_max_rows(); }
+
 int mf_lnl_fwd(const mf_lnl_fwd_args* args, void* stream) {
   MF_REQUIRE(args, MF_ERR_BAD_ARG, "args is NULL");
   const mf_lnl_fwd_args& a = *args;

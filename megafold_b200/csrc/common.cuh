@@ -120,6 +120,8 @@ __device__ __forceinline__ float warp_sum(float v) {
 int evo_fwd_simt(const mf_evo_fwd_args& a, cudaStream_t st);
 int evo_bwd_simt(const mf_evo_bwd_args& a, cudaStream_t st);
 size_t evo_bwd_simt_workspace(const mf_evo_bwd_args& a);
+int evo_bwd_simt_noalloc(const mf_evo_bwd_args& a, cudaStream_t st);
+size_t evo_bwd_noalloc_max_rows();
 
 bool evo_tc_supported(int B, int N, int L, int H, int D, int dtype, const int64_t* qs, const int64_t* ks,
                       const int64_t* vs, const void* q, const void* k, const void* v);

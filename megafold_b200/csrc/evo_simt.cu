@@ -380,4 +380,35 @@ int evo_bwd_simt(const mf_evo_bwd_args& a, cudaStream_t st) {
   return MF_OK;
 }
 
+// ---- backward without any allocation ------------------------------------------------------------------
+// Scratch for the variant below: the per-query delta = rowsum(dO * O) values, B*N*H*L floats.  The array is part
+// of the library image, so every GPU that loads the library holds these 4 MiB until the process exits.
+constexpr size_t kNoAllocDeltaFloats = size_t(1) << 20;
+static __device__ __align__(256) float g_noalloc_delta[kNoAllocDeltaFloats];
+
+size_t evo_bwd_noalloc_max_rows() { return kNoAllocDeltaFloats; }
+
+int evo_bwd_simt_noalloc(const mf_evo_bwd_args& a, cudaStream_t st) {
+  const size_t need = (size_t)a.B * a.N * a.H * a.L;
+  MF_REQUIRE(need <= kNoAllocDeltaFloats, MF_ERR_UNSUPPORTED,
+             "mf_evo_bwd_noalloc: B*N*H*L = %zu query rows exceed the built-in scratch of %zu rows; use mf_evo_bwd with a workspace",
+             need, kNoAllocDeltaFloats);
+  // In host code `g_noalloc_delta` is only a handle of the device array, not its address: the address is asked
+  // for once per device (with that device current) and remembered.
+  static float* dev_ptr[64] = {};
+  int dev = 0;
+  MF_CUDA(cudaGetDevice(&dev));
+  MF_REQUIRE(dev >= 0 && dev < 64, MF_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+  float* scratch = __atomic_load_n(&dev_ptr[dev], __ATOMIC_ACQUIRE);
+  if (!scratch) {
+    MF_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&scratch), g_noalloc_delta));
+    MF_REQUIRE(scratch != nullptr, MF_ERR_CUDA, "cudaGetSymbolAddress returned a null scratch address");
+    __atomic_store_n(&dev_ptr[dev], scratch, __ATOMIC_RELEASE);
+  }
+  mf_evo_bwd_args b = a;
+  b.workspace = scratch;
+  b.workspace_bytes = kNoAllocDeltaFloats * sizeof(float);
+  return evo_bwd_simt(b, st);     // delta is fully rewritten for the B*N*H*L rows in use: nothing to clear
+}
+
 }  // namespace mf
