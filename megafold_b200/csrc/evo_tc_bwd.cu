@@ -20,6 +20,8 @@
 // reference's atomic adds; its summation order is not fixed.
 //
 // delta_i = rowsum(dO_i * O_i) comes from a small pre-kernel.  All waits are bounded (see tc.cuh).
+#include <type_traits>
+
 #include "evo_tc_common.cuh"
 
 namespace mf {
@@ -27,7 +29,7 @@ namespace {
 using namespace tcx;
 
 constexpr int kT = 128;            // tile edge (keys and queries)
-constexpr int kThreads = 256;
+constexpr int kThreads = 512;      // 16 warps: 4 per scheduler, to hide the latencies of the per-element work
 constexpr int kTileP = 2 * 128 * 128;   // bytes of a [128 x 128] 16-bit tile (two 64-wide atoms)
 
 template <int DP> struct Cfg {
@@ -62,6 +64,8 @@ long long* g_timeline_bwd = nullptr;
 
 struct Bars {
   uint64_t kv_full[2], qd_full[3], sd_ready, acc_done;
+  uint64_t loaded, written, item_sync;     // one arrival per warp
+  int special[2];
 };
 
 // delta[b,n,h,i] = sum_d dO * O; one thread per (b,n,i,h) row, 16-byte loads (D is a multiple of 8)
@@ -115,13 +119,13 @@ __global__ void transpose_bias_kernel(const TB* __restrict__ bias, TB* __restric
   }
 }
 
-// 64 consecutive bias values held in registers (packed for 16-bit types)
+// 32 consecutive bias values held in registers (packed for 16-bit types)
 template <typename TB> struct BiasRun {
-  uint4 v[8];
+  uint4 v[4];
   __device__ __forceinline__ void load(const TB* p) {
     const uint4* q = reinterpret_cast<const uint4*>(p);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = __ldg(q + i);
+    for (int i = 0; i < 4; ++i) v[i] = __ldg(q + i);
   }
   __device__ __forceinline__ float get(int c) const {
     const uint4& x = v[c >> 3];
@@ -131,11 +135,11 @@ template <typename TB> struct BiasRun {
   }
 };
 template <> struct BiasRun<float> {
-  float4 v[16];
+  float4 v[8];
   __device__ __forceinline__ void load(const float* p) {
     const float4* q = reinterpret_cast<const float4*>(p);
 #pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = __ldg(q + i);
+    for (int i = 0; i < 8; ++i) v[i] = __ldg(q + i);
   }
   __device__ __forceinline__ float get(int c) const {
     const float4& x = v[c >> 2];
@@ -176,7 +180,7 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
   __shared__ int abort_s;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int w = warp >> 2;                          // query half handled by this thread
+  const int w = warp >> 2;                          // query quarter (32 columns) handled by this thread
   const int r = (warp & 3) * 32 + lane;             // TMEM lane = key row inside the tile
   float* stage = dlt + p.lpad + warp * 1024;        // per warp: 2 buffers x [16 queries][32 keys] fp32
   if (tid == 0) {
@@ -185,6 +189,8 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
     mbar_init(&bar.qd_full[0], 1); mbar_init(&bar.qd_full[1], 1); mbar_init(&bar.qd_full[2], 1);
     mbar_init(&bar.sd_ready, 1);
     mbar_init(&bar.acc_done, 3);
+    mbar_init(&bar.loaded, kThreads / 32); mbar_init(&bar.written, kThreads / 32); mbar_init(&bar.item_sync, kThreads / 32);
+    bar.special[0] = 0; bar.special[1] = 0;
     mbar_fence_init();
     prefetch_tmap(&mq); prefetch_tmap(&mk); prefetch_tmap(&mv); prefetch_tmap(&mg);
   }
@@ -200,7 +206,7 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
   const uint32_t id_kv = idesc_f16(128, DP, p.ab_fmt, 0, 1);    // A K-major, B MN-major
   const uint32_t id_q = idesc_f16(128, DP, p.ab_fmt, 1, 1);     // A MN-major, B MN-major
   // officers: MMA issue is split over three threads (one per accumulator), TMA on a fourth
-  const bool off_s = tid == 0, off_dv = tid == 0, off_dk = tid == 32, off_dq = tid == 64, off_tma = tid == 96;
+  const bool off_s = tid == 128, off_dv = tid == 0, off_dk = tid == 32, off_dq = tid == 64, off_tma = tid == 96;
   const int nt = p.n_t, blocks_per_item = nt * nt;
 
   uint32_t g = 0;                 // blocks processed by this CTA: sd_ready / acc_done parity g & 1;
@@ -209,6 +215,7 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
   bool dead = false;
   int tl_n = 0; (void)tl_n;
   uint32_t rnd = 0;               // dBias staging rounds of this warp (buffer = rnd & 1)
+  uint32_t isync = 0;             // CTA rendezvous counter (two per item)
   auto qd_stage = [&](uint32_t gg) { return sQD + (gg % 3) * 2 * C::TILEB; };
   auto load_qd = [&](uint32_t gg, int it2, int h, int n, int b) {
     uint64_t* fb = &bar.qd_full[gg % 3];
@@ -237,20 +244,30 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
   for (int item = blockIdx.x; item < p.n_items && !dead; item += gridDim.x) {
     const int h = item % p.H, bn = item / p.H, n = bn % p.N, b = bn / p.N;
     const int64_t stat_row = ((int64_t)bn * p.H + h) * p.L;
-    // ---- per-item statistics: lse in base 2 and delta; queries beyond L get lse = +inf (P = 0)
-    int special = 0;
+    // ---- per-item statistics: lse in base 2 and delta; queries beyond L get lse = +inf (P = 0).
+    // Two CTA-wide rendezvous (bounded mbarrier waits, one arrival per warp): everybody has left the previous
+    // item before the statistics are overwritten, and everybody sees the new ones before using them.
+    auto cta_sync = [&]() {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar.item_sync);
+      wait_or_flag(&bar.item_sync, isync & 1, abort_flag);
+      ++isync;
+    };
+    cta_sync();
+    if (__any_sync(0xffffffffu, *abort_flag)) { dead = true; break; }
+    const int sp_slot = (isync >> 1) & 1;
     for (int i = tid; i < p.lpad; i += kThreads) {
       float l2 = INFINITY, dl = 0.f;
       if (i < p.L) {
         const float lv = p.lse[stat_row + i];
-        special |= lv <= -3e38f;
+        if (lv <= -3e38f) bar.special[sp_slot] = 1;     // a fully masked row: the item takes the careful path
         l2 = lv * kLog2e; dl = p.delta[stat_row + i];
       }
       lse2[i] = l2; dlt[i] = dl;
     }
-    // barrier (also: everybody is done with the previous item's statistics); rows that are fully masked
-    // (lse = -FLT_MAX) switch the item to the careful path
-    special = named_sync_or(1, kThreads, special) ? 1 : 0;
+    cta_sync();
+    const bool special = *reinterpret_cast<volatile int*>(&bar.special[sp_slot]) != 0;
+    if (tid == 0) bar.special[sp_slot ^ 1] = 0;         // slot of the next item; nobody reads it before the next rendezvous
 
     if (off_tma) {
       // first K/V of the item and the Q/dO tiles of its first two blocks (their stages were drained by the previous item)
@@ -276,7 +293,7 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
       }
       const bool masked_key = mask2 <= -FLT_MAX;
       for (int it = 0; it < nt; ++it, ++g) {
-        const int i0 = it * kT + w * 64;
+        const int i0 = it * kT + w * 32;
         const bool last_block = (jt == nt - 1) && (it == nt - 1);
         MF_TL(20);
         // ---- bias for my key and my 64 queries: one contiguous run of the transposed copy biasT[b][h][j][i]
@@ -287,21 +304,23 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
         wait_or_flag(&bar.sd_ready, g & 1, abort_flag);
         tc_fence_after();
         MF_TL(22);
-        uint32_t sr[64], dr[64];
+        uint32_t sr[32], dr[32];
         {
           uint32_t (*s2)[32] = reinterpret_cast<uint32_t (*)[32]>(sr);
           uint32_t (*d2)[32] = reinterpret_cast<uint32_t (*)[32]>(dr);
-          tmem_ld32(tST + lane_addr + w * 64, s2[0]); tmem_ld32(tST + lane_addr + w * 64 + 32, s2[1]);
-          tmem_ld32(tDP + lane_addr + w * 64, d2[0]); tmem_ld32(tDP + lane_addr + w * 64 + 32, d2[1]);
+          tmem_ld32(tST + lane_addr + w * 32, s2[0]);
+          tmem_ld32(tDP + lane_addr + w * 32, d2[0]);
           tmem_ld_wait();
         }
         MF_TL(23);
         tc_fence_before();
-        if (named_sync_or(1, kThreads, *abort_flag)) { dead = true; break; }
+        if (__any_sync(0xffffffffu, *abort_flag)) { dead = true; break; }
+        if (lane == 0) mbar_arrive(&bar.loaded);
         MF_TL(24);
         // ---- next block's scores (the S^T / dP^T buffers are free again)
         const bool new_j = (it == nt - 1);
         if (!last_block && off_s) {
+          wait_or_flag(&bar.loaded, g & 1, abort_flag);      // every warp holds its part of S^T, dP^T in registers
           const uint32_t kc = new_j ? kv_cnt + 1 : kv_cnt;
           if (new_j) wait_or_flag(&bar.kv_full[kc & 1], (kc >> 1) & 1, abort_flag);
           wait_or_flag(&bar.qd_full[(g + 1) % 3], ((g + 1) / 3) & 1, abort_flag);
@@ -310,9 +329,10 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
         }
         MF_TL(25);
         // ---- P^T and dS^T for my 64 queries
-        uint32_t pp[32], dd[32];
+        uint32_t pp[16], dd[16];
+        auto compute = [&](auto careful) {
 #pragma unroll
-        for (int c4 = 0; c4 < 16; ++c4) {
+        for (int c4 = 0; c4 < 8; ++c4) {
           const float4 l4 = *reinterpret_cast<const float4*>(lse2 + i0 + c4 * 4);
           const float4 d4 = *reinterpret_cast<const float4*>(dlt + i0 + c4 * 4);
           const float ls[4] = {l4.x, l4.y, l4.z, l4.w}, de[4] = {d4.x, d4.y, d4.z, d4.w};
@@ -322,9 +342,9 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
             const int c = c4 * 4 + e;
             const float x = fmaf(__uint_as_float(sr[c]), p.c1, fmaf(bv.get(c), kLog2e, mask2)) - ls[e];
             float pr = ex2f(x);
-            if (special && ls[e] <= -3e38f) pr = j_ok ? p.inv_L : 0.f;       // fully masked row: uniform
+            if (decltype(careful)::value && ls[e] <= -3e38f) pr = j_ok ? p.inv_L : 0.f;   // fully masked row: uniform
             float ds = pr * (__uint_as_float(dr[c]) - de[e]);
-            if (special && masked_key) ds = 0.f;                             // no gradient through a masked logit
+            if (decltype(careful)::value && masked_key) ds = 0.f;                         // no gradient through a masked logit
             pv[e] = pr; dv[e] = ds;
             stage[(rnd & 1) * 512 + ((c4 & 3) * 4 + e) * 32 + lane] = ds;
           }
@@ -333,7 +353,9 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
             fence_async_smem();
             __syncwarp();
             if (lane == 0) {
+#ifndef MF_NO_REDUCE
               tma_reduce_add_4d(&mdb, stage + (rnd & 1) * 512, jt * kT + (warp & 3) * 32, i0 + (c4 >> 2) * 16, h, b);
+#endif
               bulk_commit();
               bulk_wait_read<1>();      // the buffer written two rounds ago has been read: it may be refilled
             }
@@ -343,25 +365,30 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
           pp[c4 * 2] = Pack2<T>::pack(pv[0], pv[1]); pp[c4 * 2 + 1] = Pack2<T>::pack(pv[2], pv[3]);
           dd[c4 * 2] = Pack2<T>::pack(dv[0], dv[1]); dd[c4 * 2 + 1] = Pack2<T>::pack(dv[2], dv[3]);
         }
+        };
+        if (special) compute(std::true_type{}); else compute(std::false_type{});
         MF_TL(26);
         // the MMAs of the previous block have finished reading the P^T / dS^T tiles?
         if (g > 0) wait_or_flag(&bar.acc_done, (g - 1) & 1, abort_flag);
 #pragma unroll
-        for (int ch = 0; ch < 8; ++ch) {
-          const uint32_t off = w * 16384 + swz_offset(r, ch, 128);
+        for (int ch = 0; ch < 4; ++ch) {
+          const uint32_t off = (w >> 1) * 16384 + swz_offset(r, (w & 1) * 4 + ch, 128);
           *reinterpret_cast<uint4*>(sP + off) = make_uint4(pp[ch * 4], pp[ch * 4 + 1], pp[ch * 4 + 2], pp[ch * 4 + 3]);
           *reinterpret_cast<uint4*>(sDS + off) = make_uint4(dd[ch * 4], dd[ch * 4 + 1], dd[ch * 4 + 2], dd[ch * 4 + 3]);
         }
         fence_async_smem();
         tc_fence_before();
         MF_TL(27);
-        if (named_sync_or(1, kThreads, *abort_flag)) { dead = true; break; }
+        if (__any_sync(0xffffffffu, *abort_flag)) { dead = true; break; }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar.written);
         MF_TL(28);
         // ---- accumulate MMAs of this block, one officer per accumulator
         {
           const uint32_t kvb = smem_u32(sKV + (kv_cnt & 1) * 2 * C::TILEB);
           const uint32_t qdb = smem_u32(qd_stage(g));
           if (off_dv) {       // dV_j += P^T dO_i
+            wait_or_flag(&bar.written, g & 1, abort_flag);
             tc_fence_after();
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks)
@@ -370,6 +397,7 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
             tc_commit(&bar.acc_done);
           }
           if (off_dk) {       // dK_j += dS^T Q_i
+            wait_or_flag(&bar.written, g & 1, abort_flag);
             tc_fence_after();
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks)
@@ -378,6 +406,7 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
             tc_commit(&bar.acc_done);
           }
           if (off_dq) {       // dQ_i += dS K_j   (A = dS^T tile read MN-major: M = queries)
+            wait_or_flag(&bar.written, g & 1, abort_flag);
             tc_fence_after();
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks)
@@ -399,10 +428,12 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
           wait_or_flag(&bar.acc_done, g & 1, abort_flag);
           tc_fence_after();
           uint32_t o32[DP];
+          if (w < 2) {
 #pragma unroll
           for (int cb = 0; cb < DP / 32; ++cb) tmem_ld32((w == 0 ? tDK : tDV) + lane_addr + cb * 32, *reinterpret_cast<uint32_t (*)[32]>(o32 + cb * 32));
           tmem_ld_wait();
-          if (j_ok && !*abort_flag) {
+          }
+          if (w < 2 && j_ok && !*abort_flag) {
             const float sc = w == 0 ? p.scale : 1.f;
             T* orow = static_cast<T*>(w == 0 ? p.dk : p.dv) + ((((int64_t)b * p.N + n) * p.L + j) * p.H + h) * p.D;
 #pragma unroll
@@ -425,7 +456,7 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
     if (dead) break;
     // ---- dQ of every query tile (all MMAs of the item are complete: acc_done of the last block was awaited)
     tc_fence_after();
-    for (int it = w; it < nt; it += 2) {
+    for (int it = w; it < nt; it += 4) {
       const int i = it * kT + r;
       uint32_t o32[DP];
 #pragma unroll
@@ -515,7 +546,7 @@ int launch_bwd(const mf_evo_bwd_args& a, cudaStream_t st) {
                                                                       delta, rows, a.L, a.H, a.D);
   MF_LAUNCHED("evo_delta_tc_kernel");
   MF_CUDA(cudaMemsetAsync(dbias, 0, sizeof(float) * nb, st));
-  const size_t smem = 1024 + 2 * kTileP + 10 * (size_t)C::TILEB + 2 * sizeof(float) * p.lpad + 8 * 4096;
+  const size_t smem = 1024 + 2 * kTileP + 10 * (size_t)C::TILEB + 2 * sizeof(float) * p.lpad + 16 * 4096;
   auto kern = evo_bwd_tc_kernel<DP, T, TB>;
   MF_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int grid = sm_count();
@@ -541,7 +572,8 @@ extern "C" __attribute__((visibility("default"))) void mf_debug_set_timeline_bwd
 
 bool evo_bwd_tc_shape_ok(int L, int D) {
   const int nt = (L + kT - 1) / kT;
-  return D <= 32 ? nt <= Cfg<32>::MAX_QT : nt <= Cfg<64>::MAX_QT;
+  // head sizes above 32 would need more shared memory than an SM has with this tiling: CUDA-core path
+  return D <= 32 && nt <= Cfg<32>::MAX_QT;
 }
 
 size_t evo_bwd_tc_workspace(const mf_evo_bwd_args& a) {
