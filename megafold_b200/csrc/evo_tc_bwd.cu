@@ -29,7 +29,8 @@ namespace {
 using namespace tcx;
 
 constexpr int kT = 128;            // tile edge (keys and queries)
-constexpr int kThreads = 512;      // 16 warps: 4 per scheduler, to hide the latencies of the per-element work
+constexpr int kComputeWarps = 16;  // 4 per scheduler, to hide the latencies of the per-element work
+constexpr int kThreads = (kComputeWarps + 4) * 32;   // + one warpgroup: MMA issuer warp, TMA warp, two idle warps
 constexpr int kTileP = 2 * 128 * 128;   // bytes of a [128 x 128] 16-bit tile (two 64-wide atoms)
 
 template <int DP> struct Cfg {
@@ -63,7 +64,7 @@ long long* g_timeline_bwd = nullptr;
 #endif
 
 struct Bars {
-  uint64_t kv_full[2], qd_full[3], sd_ready, acc_done;
+  uint64_t kv_full[2], kv_empty[2], qd_full[3], qd_empty[3], sd_ready, acc_done;
   uint64_t loaded, written, item_sync;     // one arrival per warp
   int special[2];
 };
@@ -188,8 +189,10 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
     mbar_init(&bar.kv_full[0], 1); mbar_init(&bar.kv_full[1], 1);
     mbar_init(&bar.qd_full[0], 1); mbar_init(&bar.qd_full[1], 1); mbar_init(&bar.qd_full[2], 1);
     mbar_init(&bar.sd_ready, 1);
-    mbar_init(&bar.acc_done, 3);
-    mbar_init(&bar.loaded, kThreads / 32); mbar_init(&bar.written, kThreads / 32); mbar_init(&bar.item_sync, kThreads / 32);
+    mbar_init(&bar.acc_done, 1);
+    mbar_init(&bar.kv_empty[0], 1); mbar_init(&bar.kv_empty[1], 1);
+    mbar_init(&bar.qd_empty[0], 1); mbar_init(&bar.qd_empty[1], 1); mbar_init(&bar.qd_empty[2], 1);
+    mbar_init(&bar.loaded, kComputeWarps); mbar_init(&bar.written, kComputeWarps); mbar_init(&bar.item_sync, kComputeWarps);
     bar.special[0] = 0; bar.special[1] = 0;
     mbar_fence_init();
     prefetch_tmap(&mq); prefetch_tmap(&mk); prefetch_tmap(&mv); prefetch_tmap(&mg);
@@ -205,8 +208,6 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
   const uint32_t id_s = idesc_f16(128, 128, p.ab_fmt, 0, 0);
   const uint32_t id_kv = idesc_f16(128, DP, p.ab_fmt, 0, 1);    // A K-major, B MN-major
   const uint32_t id_q = idesc_f16(128, DP, p.ab_fmt, 1, 1);     // A MN-major, B MN-major
-  // officers: MMA issue is split over three threads (one per accumulator), TMA on a fourth
-  const bool off_s = tid == 128, off_dv = tid == 0, off_dk = tid == 32, off_dq = tid == 64, off_tma = tid == 96;
   const int nt = p.n_t, blocks_per_item = nt * nt;
 
   uint32_t g = 0;                 // blocks processed by this CTA: sd_ready / acc_done parity g & 1;
@@ -241,6 +242,12 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
     tc_commit(&bar.sd_ready);
   };
 
+  if (warp < kComputeWarps) {
+  // Register re-partition: the CTA is launched with 96 registers per thread (640 threads); the issuer warpgroup
+  // drops to 32 and the compute warpgroups rise to 112.  The raise can only draw on what the drop releases inside
+  // this CTA, so 512 * 112 + 128 * 32 must not exceed 640 * 96 (it is equal) - otherwise the raise never returns.
+  static_assert(kComputeWarps * 32 * 112 + 128 * 32 <= kThreads * 96, "setmaxnreg budget");
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 112;");
   for (int item = blockIdx.x; item < p.n_items && !dead; item += gridDim.x) {
     const int h = item % p.H, bn = item / p.H, n = bn % p.N, b = bn / p.N;
     const int64_t stat_row = ((int64_t)bn * p.H + h) * p.L;
@@ -256,7 +263,7 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
     cta_sync();
     if (__any_sync(0xffffffffu, *abort_flag)) { dead = true; break; }
     const int sp_slot = (isync >> 1) & 1;
-    for (int i = tid; i < p.lpad; i += kThreads) {
+    for (int i = tid; i < p.lpad; i += kComputeWarps * 32) {
       float l2 = INFINITY, dl = 0.f;
       if (i < p.L) {
         const float lv = p.lse[stat_row + i];
@@ -268,19 +275,6 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
     cta_sync();
     const bool special = *reinterpret_cast<volatile int*>(&bar.special[sp_slot]) != 0;
     if (tid == 0) bar.special[sp_slot ^ 1] = 0;         // slot of the next item; nobody reads it before the next rendezvous
-
-    if (off_tma) {
-      // first K/V of the item and the Q/dO tiles of its first two blocks (their stages were drained by the previous item)
-      load_kv(kv_cnt, 0, h, n, b);
-      load_qd(g, 0, h, n, b);
-      if (blocks_per_item > 1) load_qd(g + 1, 1 % nt, h, n, b);
-    }
-    if (off_s) {
-      wait_or_flag(&bar.kv_full[kv_cnt & 1], (kv_cnt >> 1) & 1, abort_flag);
-      wait_or_flag(&bar.qd_full[g % 3], (g / 3) & 1, abort_flag);
-      tc_fence_after();
-      if (!*abort_flag) issue_scores(g, kv_cnt);
-    }
 
     for (int jt = 0; jt < nt && !dead; ++jt) {
       const int j = jt * kT + r;
@@ -294,7 +288,7 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
       const bool masked_key = mask2 <= -FLT_MAX;
       for (int it = 0; it < nt; ++it, ++g) {
         const int i0 = it * kT + w * 32;
-        const bool last_block = (jt == nt - 1) && (it == nt - 1);
+        const bool new_j = (it == nt - 1);
         MF_TL(20);
         // ---- bias for my key and my 64 queries: one contiguous run of the transposed copy biasT[b][h][j][i]
         BiasRun<TB> bv;
@@ -317,16 +311,6 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
         if (__any_sync(0xffffffffu, *abort_flag)) { dead = true; break; }
         if (lane == 0) mbar_arrive(&bar.loaded);
         MF_TL(24);
-        // ---- next block's scores (the S^T / dP^T buffers are free again)
-        const bool new_j = (it == nt - 1);
-        if (!last_block && off_s) {
-          wait_or_flag(&bar.loaded, g & 1, abort_flag);      // every warp holds its part of S^T, dP^T in registers
-          const uint32_t kc = new_j ? kv_cnt + 1 : kv_cnt;
-          if (new_j) wait_or_flag(&bar.kv_full[kc & 1], (kc >> 1) & 1, abort_flag);
-          wait_or_flag(&bar.qd_full[(g + 1) % 3], ((g + 1) / 3) & 1, abort_flag);
-          tc_fence_after();
-          if (!*abort_flag) issue_scores(g + 1, kc);
-        }
         MF_TL(25);
         // ---- P^T and dS^T for my 64 queries
         uint32_t pp[16], dd[16];
@@ -383,46 +367,6 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
         __syncwarp();
         if (lane == 0) mbar_arrive(&bar.written);
         MF_TL(28);
-        // ---- accumulate MMAs of this block, one officer per accumulator
-        {
-          const uint32_t kvb = smem_u32(sKV + (kv_cnt & 1) * 2 * C::TILEB);
-          const uint32_t qdb = smem_u32(qd_stage(g));
-          if (off_dv) {       // dV_j += P^T dO_i
-            wait_or_flag(&bar.written, g & 1, abort_flag);
-            tc_fence_after();
-#pragma unroll
-            for (int ks = 0; ks < 8; ++ks)
-              mma_ss(tDV, smem_desc(smem_u32(sP) + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024, kSw128),
-                     smem_desc(qdb + C::TILEB + ks * 16 * C::ROWB, 16, C::SBO, C::SW), id_kv, it > 0 || ks > 0);
-            tc_commit(&bar.acc_done);
-          }
-          if (off_dk) {       // dK_j += dS^T Q_i
-            wait_or_flag(&bar.written, g & 1, abort_flag);
-            tc_fence_after();
-#pragma unroll
-            for (int ks = 0; ks < 8; ++ks)
-              mma_ss(tDK, smem_desc(smem_u32(sDS) + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024, kSw128),
-                     smem_desc(qdb + ks * 16 * C::ROWB, 16, C::SBO, C::SW), id_kv, it > 0 || ks > 0);
-            tc_commit(&bar.acc_done);
-          }
-          if (off_dq) {       // dQ_i += dS K_j   (A = dS^T tile read MN-major: M = queries)
-            wait_or_flag(&bar.written, g & 1, abort_flag);
-            tc_fence_after();
-#pragma unroll
-            for (int ks = 0; ks < 8; ++ks)
-              mma_ss(tDQ + it * DP, smem_desc(smem_u32(sDS) + ks * 2048, 16384, 1024, kSw128),
-                     smem_desc(kvb + ks * 16 * C::ROWB, 16, C::SBO, C::SW), id_q, jt > 0 || ks > 0);
-            tc_commit(&bar.acc_done);
-          }
-        }
-        MF_TL(29);
-        // ---- TMA one block ahead: the stage of block g-1 is free (its accumulate MMAs were awaited above) and
-        // takes the Q/dO tile of block g+2; the K/V of the next key tile goes to the stage of key tile jt-1
-        if (off_tma) {
-          const int k2 = jt * nt + it + 2;
-          if (k2 < blocks_per_item) load_qd(g + 2, k2 % nt, h, n, b);
-          if (it == 0 && jt + 1 < nt) load_kv(kv_cnt + 1, jt + 1, h, n, b);
-        }
         if (new_j) {
           // dK_j, dV_j are complete once this block's MMAs are done
           wait_or_flag(&bar.acc_done, g & 1, abort_flag);
@@ -481,6 +425,77 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
   }
 
   if (lane == 0) bulk_wait<0>();      // my dBias reductions have left shared memory and reached global memory
+  } else {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 32;");
+  if (warp == kComputeWarps && lane == 0) {
+    // ---------------------------------------------------------------- MMA issuer: scores one block ahead,
+    // then the three accumulations of the block whose P^T / dS^T tiles have just been written
+    uint32_t g = 0, kv = 0;
+    bool first = true;
+    for (int item = blockIdx.x; item < p.n_items && !*abort_flag; item += gridDim.x) {
+      const bool last_item = item + (int)gridDim.x >= p.n_items;
+      for (int jt = 0; jt < nt && !*abort_flag; ++jt) {
+        for (int it = 0; it < nt; ++it, ++g) {
+          if (first) {
+            wait_or_flag(&bar.kv_full[0], 0, abort_flag);
+            wait_or_flag(&bar.qd_full[0], 0, abort_flag);
+            tc_fence_after();
+            issue_scores(0, 0);
+            first = false;
+          }
+          const bool new_j = (it == nt - 1);
+          const bool last_block = last_item && (jt == nt - 1) && new_j;
+          if (!last_block) {
+            wait_or_flag(&bar.loaded, g & 1, abort_flag);        // every compute warp holds its part of S^T, dP^T
+            const uint32_t kc = new_j ? kv + 1 : kv;
+            if (new_j) wait_or_flag(&bar.kv_full[kc & 1], (kc >> 1) & 1, abort_flag);
+            wait_or_flag(&bar.qd_full[(g + 1) % 3], ((g + 1) / 3) & 1, abort_flag);
+            tc_fence_after();
+            if (*abort_flag) break;
+            issue_scores(g + 1, kc);
+          }
+          wait_or_flag(&bar.written, g & 1, abort_flag);
+          tc_fence_after();
+          if (*abort_flag) break;
+          const uint32_t kvb = smem_u32(sKV + (kv & 1) * 2 * C::TILEB);
+          const uint32_t qdb = smem_u32(qd_stage(g));
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks)      // dV_j += P^T dO_i
+            mma_ss(tDV, smem_desc(smem_u32(sP) + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024, kSw128),
+                   smem_desc(qdb + C::TILEB + ks * 16 * C::ROWB, 16, C::SBO, C::SW), id_kv, it > 0 || ks > 0);
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks)      // dK_j += dS^T Q_i
+            mma_ss(tDK, smem_desc(smem_u32(sDS) + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024, kSw128),
+                   smem_desc(qdb + ks * 16 * C::ROWB, 16, C::SBO, C::SW), id_kv, it > 0 || ks > 0);
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks)      // dQ_i += dS K_j   (A = dS^T tile read MN-major: M = queries)
+            mma_ss(tDQ + it * DP, smem_desc(smem_u32(sDS) + ks * 2048, 16384, 1024, kSw128),
+                   smem_desc(kvb + ks * 16 * C::ROWB, 16, C::SBO, C::SW), id_q, jt > 0 || ks > 0);
+          tc_commit(&bar.acc_done);
+          tc_commit(&bar.qd_empty[g % 3]);
+          if (new_j) { tc_commit(&bar.kv_empty[kv & 1]); ++kv; }
+        }
+      }
+    }
+  } else if (warp == kComputeWarps + 1 && lane == 0) {
+    // ---------------------------------------------------------------- TMA producer, in order of need
+    uint32_t g = 0, kv = 0;
+    for (int item = blockIdx.x; item < p.n_items && !*abort_flag; item += gridDim.x) {
+      const int h = item % p.H, bn = item / p.H, n = bn % p.N, b = bn / p.N;
+      for (int jt = 0; jt < nt && !*abort_flag; ++jt) {
+        if (kv >= 2) wait_or_flag(&bar.kv_empty[kv & 1], ((kv >> 1) - 1) & 1, abort_flag);
+        if (*abort_flag) break;
+        load_kv(kv, jt, h, n, b);
+        ++kv;
+        for (int it = 0; it < nt; ++it, ++g) {
+          if (g >= 3) wait_or_flag(&bar.qd_empty[g % 3], ((g / 3) - 1) & 1, abort_flag);
+          if (*abort_flag) break;
+          load_qd(g, it, h, n, b);
+        }
+      }
+    }
+  }
+  }
   tc_fence_before();
   __syncthreads();
   if (tid == 0 && abort_s) *reinterpret_cast<volatile int*>(p.status) = 1;
