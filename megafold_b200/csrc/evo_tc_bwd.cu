@@ -30,7 +30,7 @@ using namespace tcx;
 
 constexpr int kT = 128;            // tile edge (keys and queries)
 constexpr int kComputeWarps = 16;  // 4 per scheduler, to hide the latencies of the per-element work
-constexpr int kThreads = (kComputeWarps + 4) * 32;   // + one warpgroup: MMA issuer warp, TMA warp, two idle warps
+constexpr int kThreads = (kComputeWarps + 4) * 32;   // + one warpgroup: accumulate-MMA issuer, TMA producer, score-MMA issuer, idle
 constexpr int kTileP = 2 * 128 * 128;   // bytes of a [128 x 128] 16-bit tile (two 64-wide atoms)
 
 template <int DP> struct Cfg {
@@ -58,7 +58,12 @@ struct BwdP {
 // Phase timestamps of thread 0 of CTA 0; compiled in only with -DMF_TIMELINE.
 #ifdef MF_TIMELINE
 long long* g_timeline_bwd = nullptr;
-#define MF_TL(tag) do { if (p.timeline && blockIdx.x == 0 && tid == 0 && tl_n < 250) { p.timeline[2 * tl_n] = (tag); p.timeline[2 * tl_n + 1] = clock64(); ++tl_n; } } while (0)
+#ifdef MF_TL_MMA
+#define MF_TL_WHO (kComputeWarps * 32)
+#else
+#define MF_TL_WHO 0
+#endif
+#define MF_TL(tag) do { if (p.timeline && blockIdx.x == 0 && tid == MF_TL_WHO && tl_n < 250) { p.timeline[2 * tl_n] = (tag); p.timeline[2 * tl_n + 1] = clock64(); ++tl_n; } } while (0)
 #else
 #define MF_TL(tag) do { } while (0)
 #endif
@@ -174,7 +179,7 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
   uint8_t* sKV = sDS + kTileP;                // [2 stages][K, V]
   uint8_t* sQD = sKV + 4 * C::TILEB;          // [3 stages][Q, dO]
   float* lse2 = reinterpret_cast<float*>(sQD + 6 * C::TILEB);
-  float* dlt = lse2 + p.lpad;
+  float* dlt = lse2 + 2 * p.lpad;            // lse2, dlt: two buffers each (current item / next item)
 
   __shared__ Bars bar;
   __shared__ uint32_t tmem_base_s;
@@ -183,7 +188,7 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int w = warp >> 2;                          // query quarter (32 columns) handled by this thread
   const int r = (warp & 3) * 32 + lane;             // TMEM lane = key row inside the tile
-  float* stage = dlt + p.lpad + warp * 1024;        // per warp: 2 buffers x [16 queries][32 keys] fp32
+  float* stage = dlt + 2 * p.lpad + warp * 1024;        // per warp: 2 buffers x [16 queries][32 keys] fp32
   if (tid == 0) {
     abort_s = 0;
     mbar_init(&bar.kv_full[0], 1); mbar_init(&bar.kv_full[1], 1);
@@ -204,7 +209,12 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
   volatile int* abort_flag = &abort_s;
   const uint32_t tm0 = tmem_base_s;
   const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
-  const uint32_t tST = tm0, tDP = tm0 + 128, tDK = tm0 + 256, tDV = tm0 + 256 + DP, tDQ = tm0 + 256 + 2 * DP;
+  // dK/dV accumulators are double-buffered over the key tiles when the dQ accumulators leave room for it: their
+  // write-out is then deferred by one block and no longer stalls the pipeline at the end of a key tile
+  const bool dbuf = p.n_t <= (512 - 256 - 4 * DP) / DP;
+  const uint32_t tST = tm0, tDP = tm0 + 128, tKV = tm0 + 256, tDQ = tm0 + 256 + (dbuf ? 4 : 2) * DP;
+  auto tDK_of = [&](uint32_t kc) { return tKV + (dbuf ? (kc & 1) * 2 * DP : 0); };
+  auto tDV_of = [&](uint32_t kc) { return tDK_of(kc) + DP; };
   const uint32_t id_s = idesc_f16(128, 128, p.ab_fmt, 0, 0);
   const uint32_t id_kv = idesc_f16(128, DP, p.ab_fmt, 0, 1);    // A K-major, B MN-major
   const uint32_t id_q = idesc_f16(128, DP, p.ab_fmt, 1, 1);     // A MN-major, B MN-major
@@ -216,7 +226,9 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
   bool dead = false;
   int tl_n = 0; (void)tl_n;
   uint32_t rnd = 0;               // dBias staging rounds of this warp (buffer = rnd & 1)
-  uint32_t isync = 0;             // CTA rendezvous counter (two per item)
+  uint32_t isync = 0;             // CTA rendezvous counter (one per item)
+  int item_no = 0;                // items this CTA has started (statistics buffer = item_no & 1)
+  int pend_j = -1; uint32_t pend_kc = 0; int pend_b = 0, pend_n = 0, pend_h = 0;   // deferred dK/dV write-out
   auto qd_stage = [&](uint32_t gg) { return sQD + (gg % 3) * 2 * C::TILEB; };
   auto load_qd = [&](uint32_t gg, int it2, int h, int n, int b) {
     uint64_t* fb = &bar.qd_full[gg % 3];
@@ -242,6 +254,34 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
     tc_commit(&bar.sd_ready);
   };
 
+  // dK (scaled) and dV rows of key `j` from accumulator buffer `kc`: quarter 0 writes dK, quarter 1 writes dV
+  auto store_kv = [&](uint32_t kc, int j, int b, int n, int h) {
+    tc_fence_after();
+    if (w < 2) {
+      uint32_t o32[DP];
+#pragma unroll
+      for (int cb = 0; cb < DP / 32; ++cb)
+        tmem_ld32((w == 0 ? tDK_of(kc) : tDV_of(kc)) + lane_addr + cb * 32, *reinterpret_cast<uint32_t (*)[32]>(o32 + cb * 32));
+      tmem_ld_wait();
+      if (j < p.L && !*abort_flag) {
+        const float sc = w == 0 ? p.scale : 1.f;
+        T* orow = static_cast<T*>(w == 0 ? p.dk : p.dv) + ((((int64_t)b * p.N + n) * p.L + j) * p.H + h) * p.D;
+#pragma unroll
+        for (int d8 = 0; d8 < DP / 8; ++d8) {
+          if (d8 * 8 < p.D) {
+            uint4 v;
+            v.x = Pack2<T>::pack(__uint_as_float(o32[d8 * 8]) * sc, __uint_as_float(o32[d8 * 8 + 1]) * sc);
+            v.y = Pack2<T>::pack(__uint_as_float(o32[d8 * 8 + 2]) * sc, __uint_as_float(o32[d8 * 8 + 3]) * sc);
+            v.z = Pack2<T>::pack(__uint_as_float(o32[d8 * 8 + 4]) * sc, __uint_as_float(o32[d8 * 8 + 5]) * sc);
+            v.w = Pack2<T>::pack(__uint_as_float(o32[d8 * 8 + 6]) * sc, __uint_as_float(o32[d8 * 8 + 7]) * sc);
+            *reinterpret_cast<uint4*>(orow + d8 * 8) = v;
+          }
+        }
+      }
+    }
+    tc_fence_before();
+  };
+
   if (warp < kComputeWarps) {
   // Register re-partition: the CTA is launched with 96 registers per thread (640 threads); the issuer warpgroup
   // drops to 32 and the compute warpgroups rise to 112.  The raise can only draw on what the drop releases inside
@@ -250,40 +290,60 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
   asm volatile("setmaxnreg.inc.sync.aligned.u32 112;");
   for (int item = blockIdx.x; item < p.n_items && !dead; item += gridDim.x) {
     const int h = item % p.H, bn = item / p.H, n = bn % p.N, b = bn / p.N;
-    const int64_t stat_row = ((int64_t)bn * p.H + h) * p.L;
-    // ---- per-item statistics: lse in base 2 and delta; queries beyond L get lse = +inf (P = 0).
-    // Two CTA-wide rendezvous (bounded mbarrier waits, one arrival per warp): everybody has left the previous
-    // item before the statistics are overwritten, and everybody sees the new ones before using them.
+    // ---- per-item statistics (lse in base 2, delta; queries beyond L get lse = +inf so that P = 0) live in two
+    // buffers: the current item's were stored while the previous item was running.  One CTA-wide rendezvous per item
+    // (bounded mbarrier wait, one arrival per warp): everybody has left the previous item, so the other buffer may be
+    // refilled, and everybody's earlier stores to this buffer are visible.
+    auto load_stats = [&](int item2, int buf, int stamp) {
+      if (item2 >= p.n_items) return;
+      const int64_t row2 = (int64_t)item2 / p.H * p.H * p.L + (int64_t)(item2 % p.H) * p.L;   // ((b*N+n)*H + h) * L
+      for (int i = tid; i < p.lpad; i += kComputeWarps * 32) {
+        float l2 = INFINITY, dl = 0.f;
+        if (i < p.L) {
+          const float lv = p.lse[row2 + i];
+          if (lv <= -3e38f) bar.special[buf] = stamp;  // a fully masked row: the item (identified by its stamp) takes the careful path
+          l2 = lv * kLog2e; dl = p.delta[row2 + i];
+        }
+        lse2[buf * p.lpad + i] = l2; dlt[buf * p.lpad + i] = dl;
+      }
+    };
     auto cta_sync = [&]() {
       __syncwarp();
       if (lane == 0) mbar_arrive(&bar.item_sync);
       wait_or_flag(&bar.item_sync, isync & 1, abort_flag);
       ++isync;
     };
+    const int sbuf = item_no & 1;
+    if (item_no == 0) { load_stats(item, 0, 1); }
     cta_sync();
     if (__any_sync(0xffffffffu, *abort_flag)) { dead = true; break; }
-    const int sp_slot = (isync >> 1) & 1;
-    for (int i = tid; i < p.lpad; i += kComputeWarps * 32) {
-      float l2 = INFINITY, dl = 0.f;
-      if (i < p.L) {
-        const float lv = p.lse[stat_row + i];
-        if (lv <= -3e38f) bar.special[sp_slot] = 1;     // a fully masked row: the item takes the careful path
-        l2 = lv * kLog2e; dl = p.delta[stat_row + i];
+    const bool special = *reinterpret_cast<volatile int*>(&bar.special[sbuf]) == item_no + 1;
+    load_stats(item + (int)gridDim.x, sbuf ^ 1, item_no + 2);
+    const float* lse2c = lse2 + sbuf * p.lpad;
+    const float* dltc = dlt + sbuf * p.lpad;
+    ++item_no;
+    float mask2_next = -INFINITY;
+    {
+      const int j0r = r;
+      if (j0r < p.L) {
+        const int64_t mi = b * p.ms[0] + n * p.ms[1] + (int64_t)j0r * p.ms[2];
+        mask2_next = p.mask_dtype == MF_U8 ? (static_cast<const uint8_t*>(p.mask)[mi] ? 0.f : -FLT_MAX)
+                                           : load_rt(p.mask, mi, p.mask_dtype) * kLog2e;
       }
-      lse2[i] = l2; dlt[i] = dl;
     }
-    cta_sync();
-    const bool special = *reinterpret_cast<volatile int*>(&bar.special[sp_slot]) != 0;
-    if (tid == 0) bar.special[sp_slot ^ 1] = 0;         // slot of the next item; nobody reads it before the next rendezvous
 
     for (int jt = 0; jt < nt && !dead; ++jt) {
       const int j = jt * kT + r;
       const bool j_ok = j < p.L;
-      float mask2 = -INFINITY;
-      if (j_ok) {
-        const int64_t mi = b * p.ms[0] + n * p.ms[1] + (int64_t)j * p.ms[2];
-        mask2 = p.mask_dtype == MF_U8 ? (static_cast<const uint8_t*>(p.mask)[mi] ? 0.f : -FLT_MAX)
-                                      : load_rt(p.mask, mi, p.mask_dtype) * kLog2e;
+      const float mask2 = mask2_next;          // fetched one key tile ahead
+      if (jt + 1 < nt) {
+        const int jn = (jt + 1) * kT + r;
+        mask2_next = -INFINITY;
+        if (jn < p.L) {
+          const int64_t mi = b * p.ms[0] + n * p.ms[1] + (int64_t)jn * p.ms[2];
+          mask2_next = p.mask_dtype == MF_U8 ? (static_cast<const uint8_t*>(p.mask)[mi] ? 0.f : -FLT_MAX)
+                                             : load_rt(p.mask, mi, p.mask_dtype) * kLog2e;
+        }
       }
       const bool masked_key = mask2 <= -FLT_MAX;
       for (int it = 0; it < nt; ++it, ++g) {
@@ -317,8 +377,8 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
         auto compute = [&](auto careful) {
 #pragma unroll
         for (int c4 = 0; c4 < 8; ++c4) {
-          const float4 l4 = *reinterpret_cast<const float4*>(lse2 + i0 + c4 * 4);
-          const float4 d4 = *reinterpret_cast<const float4*>(dlt + i0 + c4 * 4);
+          const float4 l4 = *reinterpret_cast<const float4*>(lse2c + i0 + c4 * 4);
+          const float4 d4 = *reinterpret_cast<const float4*>(dltc + i0 + c4 * 4);
           const float ls[4] = {l4.x, l4.y, l4.z, l4.w}, de[4] = {d4.x, d4.y, d4.z, d4.w};
           float pv[4], dv[4];
 #pragma unroll
@@ -367,38 +427,22 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
         __syncwarp();
         if (lane == 0) mbar_arrive(&bar.written);
         MF_TL(28);
-        if (new_j) {
-          // dK_j, dV_j are complete once this block's MMAs are done
+        // ---- dK_j, dV_j write-out.  Double-buffered: the key tile that finished one block ago (its MMAs were
+        // awaited before this block's tiles were written).  Otherwise: right now, after waiting for this block's MMAs.
+        if (dbuf) {
+          if (pend_j >= 0) { store_kv(pend_kc, pend_j, pend_b, pend_n, pend_h); pend_j = -1; }
+          if (new_j) { pend_j = j; pend_kc = kv_cnt; pend_b = b; pend_n = n; pend_h = h; }
+        } else if (new_j) {
           wait_or_flag(&bar.acc_done, g & 1, abort_flag);
-          tc_fence_after();
-          uint32_t o32[DP];
-          if (w < 2) {
-#pragma unroll
-          for (int cb = 0; cb < DP / 32; ++cb) tmem_ld32((w == 0 ? tDK : tDV) + lane_addr + cb * 32, *reinterpret_cast<uint32_t (*)[32]>(o32 + cb * 32));
-          tmem_ld_wait();
-          }
-          if (w < 2 && j_ok && !*abort_flag) {
-            const float sc = w == 0 ? p.scale : 1.f;
-            T* orow = static_cast<T*>(w == 0 ? p.dk : p.dv) + ((((int64_t)b * p.N + n) * p.L + j) * p.H + h) * p.D;
-#pragma unroll
-            for (int d8 = 0; d8 < DP / 8; ++d8) {
-              if (d8 * 8 < p.D) {
-                uint4 v;
-                v.x = Pack2<T>::pack(__uint_as_float(o32[d8 * 8]) * sc, __uint_as_float(o32[d8 * 8 + 1]) * sc);
-                v.y = Pack2<T>::pack(__uint_as_float(o32[d8 * 8 + 2]) * sc, __uint_as_float(o32[d8 * 8 + 3]) * sc);
-                v.z = Pack2<T>::pack(__uint_as_float(o32[d8 * 8 + 4]) * sc, __uint_as_float(o32[d8 * 8 + 5]) * sc);
-                v.w = Pack2<T>::pack(__uint_as_float(o32[d8 * 8 + 6]) * sc, __uint_as_float(o32[d8 * 8 + 7]) * sc);
-                *reinterpret_cast<uint4*>(orow + d8 * 8) = v;
-              }
-            }
-          }
-          tc_fence_before();
+          store_kv(kv_cnt, j, b, n, h);
         }
       }
       if (!dead) ++kv_cnt;
     }
     if (dead) break;
-    // ---- dQ of every query tile (all MMAs of the item are complete: acc_done of the last block was awaited)
+    // ---- dQ of every query tile, once the last block's MMAs are complete; and the last key tile's dK/dV
+    wait_or_flag(&bar.acc_done, (g - 1) & 1, abort_flag);
+    if (pend_j >= 0) { store_kv(pend_kc, pend_j, pend_b, pend_n, pend_h); pend_j = -1; }
     tc_fence_after();
     for (int it = w; it < nt; it += 4) {
       const int i = it * kT + r;
@@ -428,52 +472,61 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
   } else {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 32;");
   if (warp == kComputeWarps && lane == 0) {
-    // ---------------------------------------------------------------- MMA issuer: scores one block ahead,
-    // then the three accumulations of the block whose P^T / dS^T tiles have just been written
+    // ---------------------------------------------------------------- accumulate-MMA issuer: the three
+    // accumulations of each block, as soon as its P^T / dS^T tiles have been written
     uint32_t g = 0, kv = 0;
-    bool first = true;
     for (int item = blockIdx.x; item < p.n_items && !*abort_flag; item += gridDim.x) {
-      const bool last_item = item + (int)gridDim.x >= p.n_items;
       for (int jt = 0; jt < nt && !*abort_flag; ++jt) {
         for (int it = 0; it < nt; ++it, ++g) {
-          if (first) {
-            wait_or_flag(&bar.kv_full[0], 0, abort_flag);
-            wait_or_flag(&bar.qd_full[0], 0, abort_flag);
-            tc_fence_after();
-            issue_scores(0, 0);
-            first = false;
-          }
-          const bool new_j = (it == nt - 1);
-          const bool last_block = last_item && (jt == nt - 1) && new_j;
-          if (!last_block) {
-            wait_or_flag(&bar.loaded, g & 1, abort_flag);        // every compute warp holds its part of S^T, dP^T
-            const uint32_t kc = new_j ? kv + 1 : kv;
-            if (new_j) wait_or_flag(&bar.kv_full[kc & 1], (kc >> 1) & 1, abort_flag);
-            wait_or_flag(&bar.qd_full[(g + 1) % 3], ((g + 1) / 3) & 1, abort_flag);
-            tc_fence_after();
-            if (*abort_flag) break;
-            issue_scores(g + 1, kc);
-          }
+          MF_TL(43);
           wait_or_flag(&bar.written, g & 1, abort_flag);
+          MF_TL(44);
           tc_fence_after();
           if (*abort_flag) break;
           const uint32_t kvb = smem_u32(sKV + (kv & 1) * 2 * C::TILEB);
           const uint32_t qdb = smem_u32(qd_stage(g));
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks)      // dV_j += P^T dO_i
-            mma_ss(tDV, smem_desc(smem_u32(sP) + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024, kSw128),
+            mma_ss(tDV_of(kv), smem_desc(smem_u32(sP) + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024, kSw128),
                    smem_desc(qdb + C::TILEB + ks * 16 * C::ROWB, 16, C::SBO, C::SW), id_kv, it > 0 || ks > 0);
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks)      // dK_j += dS^T Q_i
-            mma_ss(tDK, smem_desc(smem_u32(sDS) + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024, kSw128),
+            mma_ss(tDK_of(kv), smem_desc(smem_u32(sDS) + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024, kSw128),
                    smem_desc(qdb + ks * 16 * C::ROWB, 16, C::SBO, C::SW), id_kv, it > 0 || ks > 0);
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks)      // dQ_i += dS K_j   (A = dS^T tile read MN-major: M = queries)
             mma_ss(tDQ + it * DP, smem_desc(smem_u32(sDS) + ks * 2048, 16384, 1024, kSw128),
                    smem_desc(kvb + ks * 16 * C::ROWB, 16, C::SBO, C::SW), id_q, jt > 0 || ks > 0);
+          MF_TL(45);
           tc_commit(&bar.acc_done);
+          // the stages are also read by this block's score MMAs, which completed before its tiles were written
           tc_commit(&bar.qd_empty[g % 3]);
-          if (new_j) { tc_commit(&bar.kv_empty[kv & 1]); ++kv; }
+          if (it == nt - 1) { tc_commit(&bar.kv_empty[kv & 1]); ++kv; }
+        }
+      }
+    }
+  } else if (warp == kComputeWarps + 2 && lane == 0) {
+    // ---------------------------------------------------------------- score-MMA issuer, one block ahead of
+    // the compute warps: S^T, dP^T of block g+1 as soon as every warp holds block g's in registers
+    uint32_t g = 0, kv = 0;
+    wait_or_flag(&bar.kv_full[0], 0, abort_flag);
+    wait_or_flag(&bar.qd_full[0], 0, abort_flag);
+    tc_fence_after();
+    if (!*abort_flag) issue_scores(0, 0);
+    for (int item = blockIdx.x; item < p.n_items && !*abort_flag; item += gridDim.x) {
+      const bool last_item = item + (int)gridDim.x >= p.n_items;
+      for (int jt = 0; jt < nt && !*abort_flag; ++jt) {
+        for (int it = 0; it < nt; ++it, ++g) {
+          const bool new_j = (it == nt - 1);
+          if (last_item && (jt == nt - 1) && new_j) break;
+          wait_or_flag(&bar.loaded, g & 1, abort_flag);
+          const uint32_t kc = new_j ? kv + 1 : kv;
+          if (new_j) wait_or_flag(&bar.kv_full[kc & 1], (kc >> 1) & 1, abort_flag);
+          wait_or_flag(&bar.qd_full[(g + 1) % 3], ((g + 1) / 3) & 1, abort_flag);
+          tc_fence_after();
+          if (*abort_flag) break;
+          issue_scores(g + 1, kc);
+          if (new_j) ++kv;
         }
       }
     }
@@ -561,7 +614,7 @@ int launch_bwd(const mf_evo_bwd_args& a, cudaStream_t st) {
                                                                       delta, rows, a.L, a.H, a.D);
   MF_LAUNCHED("evo_delta_tc_kernel");
   MF_CUDA(cudaMemsetAsync(dbias, 0, sizeof(float) * nb, st));
-  const size_t smem = 1024 + 2 * kTileP + 10 * (size_t)C::TILEB + 2 * sizeof(float) * p.lpad + 16 * 4096;
+  const size_t smem = 1024 + 2 * kTileP + 10 * (size_t)C::TILEB + 4 * sizeof(float) * p.lpad + 16 * 4096;
   auto kern = evo_bwd_tc_kernel<DP, T, TB>;
   MF_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int grid = sm_count();
