@@ -126,6 +126,11 @@ int mf_lnl_fwd(const mf_lnl_fwd_args* args, void* stream) {
   MF_REQUIRE(a.x && a.ln_w && a.w && a.y && a.mean && a.rstd, MF_ERR_BAD_ARG, "x, ln_w, w, y, mean, rstd must not be NULL");
   if (a.M == 0) return MF_OK;
   int r = check_device(); if (r) return r;
+  if (!(a.flags & MF_FLAG_FORCE_SIMT) && lnl_fwd_tc_supported(a)) {
+    r = lnl_fwd_tc(a, static_cast<cudaStream_t>(stream));
+    if (r == MF_OK) set_last_path("tcgen05");
+    return r;
+  }
   r = lnl_fwd_simt(a, static_cast<cudaStream_t>(stream));
   if (r == MF_OK) set_last_path("simt");
   return r;

@@ -133,6 +133,8 @@ int evo_bwd_tc(const mf_evo_bwd_args& a, cudaStream_t st);
 size_t evo_bwd_tc_workspace(const mf_evo_bwd_args& a);
 
 int lnl_fwd_simt(const mf_lnl_fwd_args& a, cudaStream_t st);
+bool lnl_fwd_tc_supported(const mf_lnl_fwd_args& a);
+int lnl_fwd_tc(const mf_lnl_fwd_args& a, cudaStream_t st);
 int lnl_bwd_simt(const mf_lnl_bwd_args& a, cudaStream_t st);
 size_t lnl_bwd_simt_workspace(const mf_lnl_bwd_args& a);
 
