@@ -170,8 +170,13 @@ int mf_swiglu_bwd(const void* x, const void* dy, void* dx, int64_t M, int32_t in
   return swiglu_bwd(x, dy, dx, M, inner, dtype, static_cast<cudaStream_t>(stream));
 }
 
+static bool transition_fwd_use_tc(const mf_transition_fwd_args& a) {
+  return !(a.flags & MF_FLAG_FORCE_SIMT) && transition_fwd_tc_supported(a);
+}
+
 size_t mf_transition_fwd_workspace_bytes(const mf_transition_fwd_args* args) {
   if (!args) return 0;
+  if (transition_fwd_use_tc(*args)) return 0;      // the fused kernel keeps the hidden activation on chip
   return transition_fwd_simt_workspace(*args);
 }
 
@@ -186,6 +191,11 @@ int mf_transition_fwd(const mf_transition_fwd_args* args, void* stream) {
   MF_REQUIRE(need == 0 || (a.workspace && a.workspace_bytes >= need), MF_ERR_WORKSPACE,
              "workspace of %zu bytes needed, %zu given", need, a.workspace ? a.workspace_bytes : (size_t)0);
   int r = check_device(); if (r) return r;
+  if (transition_fwd_use_tc(a)) {
+    r = transition_fwd_tc(a, static_cast<cudaStream_t>(stream));
+    if (r == MF_OK) set_last_path("tcgen05");
+    return r;
+  }
   r = transition_fwd_simt(a, static_cast<cudaStream_t>(stream));
   if (r == MF_OK) set_last_path("simt");
   return r;

@@ -139,6 +139,8 @@ int lnl_bwd_simt(const mf_lnl_bwd_args& a, cudaStream_t st);
 size_t lnl_bwd_simt_workspace(const mf_lnl_bwd_args& a);
 
 int transition_fwd_simt(const mf_transition_fwd_args& a, cudaStream_t st);
+bool transition_fwd_tc_supported(const mf_transition_fwd_args& a);
+int transition_fwd_tc(const mf_transition_fwd_args& a, cudaStream_t st);
 int transition_bwd_simt(const mf_transition_bwd_args& a, cudaStream_t st);
 size_t transition_fwd_simt_workspace(const mf_transition_fwd_args& a);
 size_t transition_bwd_simt_workspace(const mf_transition_bwd_args& a);
