@@ -159,7 +159,7 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=dev)
     group = None
 
-    host = workloads.triangle_attention(L=L, N=ROWS, H=H, D=D, seed=rank)
+    host = workloads.triangle_attention(L=L, N=ROWS, H=H, D=D, seed=rank)      # the metric's workload: always 384 rows per GPU
     host["bias"] = workloads.triangle_attention(L=L, N=1, H=H, D=D, seed=0)["bias"]     # shared by all ranks
     pinned = {k: v.pin_memory() for k, v in host.items()}
     c = {k: v.to(dev) for k, v in host.items()}
@@ -259,9 +259,111 @@ def run_ours(args):
                      "traffic": None, "peak_source": peaks["src"] + " bf16 burst"},
         "cpu_baseline": cpu_baseline() if world == 1 else None,
     }
+    if world == 1 and not args.no_extras:
+        del c
+        torch.cuda.empty_cache()
+        line["extras"] = extras(dev)
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def _time_cuda(fn, steps, warmup):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def run_only(args):
+    """One kernel family in a loop on a (small) case: the command ncu captures are taken from."""
+    import megafold_b200 as mfb
+    from megafold_b200 import workloads
+    from megafold_b200.fused_layernorm_linear import layernorm_linear_forward
+    from megafold_b200.fused_transition import transition_forward
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    if args.only in ("fwd", "bwd"):
+        c = {k: v.to(dev) for k, v in workloads.triangle_attention(L=L, N=args.rows, H=H, D=D).items()}
+        o, lse = mfb.evo_attention_forward(c["q"], c["k"], c["v"], c["mask"], c["bias"])
+        if args.only == "fwd":
+            fn = lambda: mfb.evo_attention_forward(c["q"], c["k"], c["v"], c["mask"], c["bias"])            # noqa: E731
+        else:
+            fn = lambda: mfb.evo_attention_backward(c["d_out"], c["q"], c["k"], c["v"], c["mask"], c["bias"], o, lse)  # noqa: E731
+    elif args.only == "lnl":
+        c = {k: (v.to(dev) if v is not None else None) for k, v in workloads.layernorm_linear(M=args.rows * L).items()}
+        fn = lambda: layernorm_linear_forward(c["x"], c["w"], c["b"], c["ln_w"], c["ln_b"])                   # noqa: E731
+    else:
+        c = {k: v.to(dev) for k, v in workloads.transition(M=args.rows * L).items()}
+        fn = lambda: transition_forward(c["x"], c["ln_w"], c["ln_b"], c["w1"], c["w2"])                       # noqa: E731
+    ms = _time_cuda(fn, args.steps, args.warmup)
+    print(f"{args.only}: rows={args.rows} {ms * 1e3:.1f} us per call")
+
+
+def extras(dev, steps=5):
+    """Secondary workloads of the path (BASELINE configs 3 and 4 and the LayernormLinear around config 2):
+    CUDA-event timings with inputs resident in HBM, a few repetitions each."""
+    import megafold_b200 as mfb
+    from megafold_b200 import _lib, workloads
+    from megafold_b200.fused_layernorm_linear import layernorm_linear_backward, layernorm_linear_forward
+    from megafold_b200.fused_transition import transition_backward, transition_forward
+    peaks = measured_peaks()
+    out = {}
+    # config 3: single-representation attention with pair bias, D = 24
+    c = {k: v.to(dev) for k, v in workloads.single_attention().items()}
+    o, lse = mfb.evo_attention_forward(c["q"], c["k"], c["v"], c["mask"], c["bias"])
+    pf = _lib.last_path()
+    ms_f = _time_cuda(lambda: mfb.evo_attention_forward(c["q"], c["k"], c["v"], c["mask"], c["bias"]), steps, 2)
+    ms_b = _time_cuda(lambda: mfb.evo_attention_backward(c["d_out"], c["q"], c["k"], c["v"], c["mask"], c["bias"], o, lse), steps, 2)
+    B3, _, L3, H3, D3 = c["q"].shape
+    bytes3 = 2 * c["bias"].numel() * 2 + c["bias"].numel() * 2 + 8 * c["q"].numel() * 2      # bias read twice, dBias written, q/k/v/o/dO/dq/dk/dv
+    out["cfg3_single_attention_L768_D24"] = {
+        "ms_forward": ms_f, "ms_backward": ms_b, "path_forward": pf, "path_backward": _lib.last_path(),
+        "tflops": 14.0 * B3 * H3 * L3 * L3 * D3 / ((ms_f + ms_b) * 1e-3) / 1e12,
+        "hbm_gbs_algorithmic": bytes3 / ((ms_f + ms_b) * 1e-3) / 1e9, "hbm_frac_of_measured": bytes3 / ((ms_f + ms_b) * 1e-3) / 1e9 / peaks["hbm"]}
+    del c, o, lse
+    # LayernormLinear 128 -> 512 on the [384*384, 128] pair representation (the projection around config 2)
+    c = {k: (v.to(dev) if v is not None else None) for k, v in workloads.layernorm_linear().items()}
+    y, mean, rstd = layernorm_linear_forward(c["x"], c["w"], c["b"], c["ln_w"], c["ln_b"])
+    pf = _lib.last_path()
+    ms_f = _time_cuda(lambda: layernorm_linear_forward(c["x"], c["w"], c["b"], c["ln_w"], c["ln_b"]), steps, 2)
+    ms_b = _time_cuda(lambda: layernorm_linear_backward(c["d_out"], c["x"], c["w"], c["ln_w"], c["ln_b"], mean, rstd, True), 2, 1)
+    M, K = c["x"].shape
+    N = c["w"].shape[1]
+    fwd_bytes = (M * K + M * N + K * N) * 2
+    out["layernorm_linear_147456x128x512"] = {
+        "ms_forward": ms_f, "ms_backward": ms_b, "path_forward": pf, "path_backward": _lib.last_path(),
+        "forward_hbm_gbs": fwd_bytes / (ms_f * 1e-3) / 1e9, "forward_hbm_frac_of_measured": fwd_bytes / (ms_f * 1e-3) / 1e9 / peaks["hbm"],
+        "forward_tflops": 2.0 * M * K * N / (ms_f * 1e-3) / 1e12}
+    del c, y, mean, rstd
+    # config 4: Transition on [512*512, 128], expansion 4
+    torch.cuda.empty_cache()
+    c = {k: v.to(dev) for k, v in workloads.transition().items()}
+    torch.cuda.reset_peak_memory_stats(dev)
+    base = torch.cuda.memory_allocated(dev)
+    y, mean, rstd = transition_forward(c["x"], c["ln_w"], c["ln_b"], c["w1"], c["w2"])
+    pf = _lib.last_path()
+    transition_backward(c["d_out"], c["x"], c["ln_w"], c["ln_b"], c["w1"], c["w2"], mean, rstd)
+    torch.cuda.synchronize()
+    peak = torch.cuda.max_memory_allocated(dev) - base
+    ms_f = _time_cuda(lambda: transition_forward(c["x"], c["ln_w"], c["ln_b"], c["w1"], c["w2"]), steps, 2)
+    ms_b = _time_cuda(lambda: transition_backward(c["d_out"], c["x"], c["ln_w"], c["ln_b"], c["w1"], c["w2"], mean, rstd), 2, 1)
+    M, dim = c["x"].shape
+    inner = c["w2"].shape[1]
+    f_fwd = 2.0 * M * dim * 2 * inner + 2.0 * M * inner * dim
+    out["cfg4_transition_512x512x128"] = {
+        "ms_forward": ms_f, "ms_backward": ms_b, "path_forward": pf, "path_backward": _lib.last_path(),
+        "forward_tflops": f_fwd / (ms_f * 1e-3) / 1e12, "forward_frac_of_measured_bf16_peak": f_fwd / (ms_f * 1e-3) / 1e12 / peaks["tflops"],
+        "fwd_bwd_tflops": 3.0 * f_fwd / ((ms_f + ms_b) * 1e-3) / 1e12,
+        "peak_extra_memory_mb_fwd_bwd": peak / 2 ** 20,
+        "note": "forward keeps the hidden activation on chip; backward recomputes it (CUDA-core path, workspace counted in the peak)"}
+    return out
 
 
 class _Null:
@@ -278,10 +380,16 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--rows", type=int, default=ROWS, help="rows (N) per GPU; smaller values give profiler-sized cases")
+    ap.add_argument("--only", default="all", choices=["all", "fwd", "bwd", "lnl", "transition"],
+                    help="run just one kernel family in the timed loop (for ncu captures); prints no JSON line")
+    ap.add_argument("--no-extras", action="store_true", help="skip the secondary workloads (cfg 3, cfg 4, LayernormLinear)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else max(args.warmup, 1)
     if args.impl == "reference":
         run_reference(args)
+    elif args.only != "all":
+        run_only(args)
     else:
         run_ours(args)
 
