@@ -8,10 +8,11 @@ or library fallback.
 from .evoattention import EvoformerAttention, TritonEvoformer, evo_attention_backward, evo_attention_forward
 from .fused_layernorm_linear import LayernormLinear, LayernormLinearFunction
 from .fused_transition import FusedSwiGLU, FusedSwiGLUFunction, FusedTransition, TransitionFunction
+from .host_pipeline import evoformer_fwd_bwd_host
 from .sharded import AllReduceGradient, row_shard, sharded_evoformer
 
 __all__ = [
     "EvoformerAttention", "TritonEvoformer", "evo_attention_forward", "evo_attention_backward",
     "LayernormLinear", "LayernormLinearFunction", "FusedSwiGLU", "FusedSwiGLUFunction", "FusedTransition",
-    "TransitionFunction", "AllReduceGradient", "row_shard", "sharded_evoformer",
+    "TransitionFunction", "AllReduceGradient", "row_shard", "sharded_evoformer", "evoformer_fwd_bwd_host",
 ]

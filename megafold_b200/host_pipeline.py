@@ -1,0 +1,110 @@
+"""Attention forward + backward for operands that live in HOST memory.
+
+``evoformer_fwd_bwd_host`` is the call for a user whose q/k/v/dO sit in pinned host buffers (a data loader, an
+off-loaded activation store): the N rows are independent in the forward pass and coupled only through the
+sum that forms d_pair_bias, so the rows are cut into chunks that flow through three CUDA streams - upload of
+chunk i+1, kernels of chunk i, download of chunk i-1 - and PCIe runs in both directions while the GPU computes.
+The results land in pinned host tensors; d_pair_bias is accumulated on the device over the chunks.
+"""
+from __future__ import annotations
+
+import torch
+
+from .evoattention import evo_attention_backward, evo_attention_forward
+
+__all__ = ["evoformer_fwd_bwd_host", "HostPipeline"]
+
+
+class HostPipeline:
+    """Reusable state (streams, device staging buffers, pinned outputs) for one problem shape."""
+
+    def __init__(self, shape, dtype, bias_shape, bias_dtype, device, chunks=8):
+        B, N, L, H, D = shape
+        self.shape, self.dtype, self.device = tuple(shape), dtype, torch.device(device)
+        self.chunks = max(1, min(chunks, N))
+        base, extra = divmod(N, self.chunks)
+        self.spans, s = [], 0
+        for i in range(self.chunks):
+            e = s + base + (1 if i < extra else 0)
+            self.spans.append((s, e))
+            s = e
+        rows = max(e - s for s, e in self.spans)
+        dev = self.device
+        self.s_in, self.s_cmp, self.s_out = (torch.cuda.Stream(dev) for _ in range(3))
+        mk = lambda: torch.empty((B, rows, L, H, D), dtype=dtype, device=dev)      # noqa: E731
+        self.dev_in = [dict(q=mk(), k=mk(), v=mk(), d_out=mk(),
+                            mask=torch.empty((B, rows, 1, 1, L), dtype=torch.bool, device=dev)) for _ in range(2)]
+        self.d_bias = torch.zeros(bias_shape, dtype=torch.float32, device=dev)
+        self.bias = torch.empty(bias_shape, dtype=bias_dtype, device=dev)
+        pin = lambda shp, dt: torch.empty(shp, dtype=dt, pin_memory=True)         # noqa: E731
+        self.out = dict(o=pin(shape, dtype), dq=pin(shape, dtype), dk=pin(shape, dtype), dv=pin(shape, dtype),
+                        d_bias=pin(bias_shape, bias_dtype))
+        self.ev_in = [torch.cuda.Event() for _ in range(2)]
+        self.ev_free = [torch.cuda.Event() for _ in range(2)]
+        self.keep = []
+
+    def run(self, q, k, v, res_mask, pair_bias, d_out):
+        """All arguments are pinned host tensors ([B,N,L,H,D], mask [B,N,1,1,L] bool, bias [B,1,H,L,L]).
+        Returns the dict of pinned host results (valid after the call: it synchronises the download stream)."""
+        host = dict(q=q, k=k, v=v, d_out=d_out, mask=res_mask)
+        cur = torch.cuda.current_stream(self.device)
+        self.s_in.wait_stream(cur)
+        self.s_cmp.wait_stream(cur)
+        self.s_out.wait_stream(cur)
+        with torch.cuda.stream(self.s_in):
+            self.bias.copy_(pair_bias, non_blocking=True)
+        self.s_cmp.wait_stream(self.s_in)
+        with torch.cuda.stream(self.s_cmp):
+            self.d_bias.zero_()
+        self.keep.clear()
+        for i, (s, e) in enumerate(self.spans):
+            slot = i & 1
+            n = e - s
+            buf = self.dev_in[slot]
+            with torch.cuda.stream(self.s_in):
+                if i >= 2:
+                    self.s_in.wait_event(self.ev_free[slot])            # kernels of chunk i-2 are done with this slot
+                for name in ("q", "k", "v", "d_out", "mask"):
+                    buf[name][:, :n].copy_(host[name][:, s:e], non_blocking=True)
+                self.ev_in[slot].record(self.s_in)
+            with torch.cuda.stream(self.s_cmp):
+                self.s_cmp.wait_event(self.ev_in[slot])
+                qd, kd, vd, gd, md = (buf[x][:, :n] for x in ("q", "k", "v", "d_out", "mask"))
+                o, lse = evo_attention_forward(qd, kd, vd, md, self.bias)
+                dq, dk, dv, db = evo_attention_backward(gd, qd, kd, vd, md, self.bias, o, lse)
+                self.d_bias.add_(db)
+                self.ev_free[slot].record(self.s_cmp)
+                done = torch.cuda.Event()
+                done.record(self.s_cmp)
+            with torch.cuda.stream(self.s_out):
+                self.s_out.wait_event(done)
+                for name, t in (("o", o), ("dq", dq), ("dk", dk), ("dv", dv)):
+                    self.out[name][:, s:e].copy_(t, non_blocking=True)
+            self.keep.append((o, dq, dk, dv, db, lse))                  # keep alive until the copies have run
+        with torch.cuda.stream(self.s_out):
+            self.s_out.wait_stream(self.s_cmp)
+            self.out["d_bias"].copy_(self.d_bias, non_blocking=True)
+        self.s_out.synchronize()
+        cur.wait_stream(self.s_cmp)
+        return self.out
+
+
+_cache = {}
+
+
+def evoformer_fwd_bwd_host(q, k, v, res_mask, pair_bias, d_out, device="cuda", chunks=8):
+    """Forward and backward of the pair-biased attention with pinned HOST operands and results.
+
+    Returns ``dict(o, dq, dk, dv, d_bias)`` of pinned host tensors; d_bias has ``pair_bias``'s dtype."""
+    for t in (q, k, v, d_out, res_mask, pair_bias):
+        if t.is_cuda:
+            raise ValueError("evoformer_fwd_bwd_host takes host tensors; use TritonEvoformer for device tensors")
+    dev = torch.device(device)
+    if dev.index is None:
+        dev = torch.device("cuda", torch.cuda.current_device())
+    key = (tuple(q.shape), q.dtype, tuple(pair_bias.shape), pair_bias.dtype, dev, chunks)
+    pipe = _cache.get(key)
+    if pipe is None:
+        _cache.clear()
+        pipe = _cache[key] = HostPipeline(q.shape, q.dtype, pair_bias.shape, pair_bias.dtype, dev, chunks)
+    return pipe.run(q, k, v, res_mask, pair_bias, d_out)
