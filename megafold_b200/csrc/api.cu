@@ -154,7 +154,7 @@ int mf_lnl_bwd(const mf_lnl_bwd_args* args, void* stream) {
   MF_REQUIRE(((uintptr_t)a.workspace & 255) == 0, MF_ERR_ALIGNMENT, "workspace must be 256-byte aligned");
   int r = check_device(); if (r) return r;
   r = lnl_bwd_simt(a, static_cast<cudaStream_t>(stream));
-  if (r == MF_OK) set_last_path("simt");
+  if (r == MF_OK) set_last_path(lnl_bwd_runs_on_tc(a) ? "tcgen05" : "simt");
   return r;
 }
 
@@ -219,7 +219,7 @@ int mf_transition_bwd(const mf_transition_bwd_args* args, void* stream) {
              a.workspace ? a.workspace_bytes : (size_t)0);
   int r = check_device(); if (r) return r;
   r = transition_bwd_simt(a, static_cast<cudaStream_t>(stream));
-  if (r == MF_OK) set_last_path("simt");
+  if (r == MF_OK) set_last_path(transition_bwd_runs_on_tc(a) ? "tcgen05" : "simt");
   return r;
 }
 

@@ -135,7 +135,9 @@ size_t evo_bwd_tc_workspace(const mf_evo_bwd_args& a);
 int lnl_fwd_simt(const mf_lnl_fwd_args& a, cudaStream_t st);
 bool lnl_fwd_tc_supported(const mf_lnl_fwd_args& a);
 int lnl_fwd_tc(const mf_lnl_fwd_args& a, cudaStream_t st);
-int lnl_bwd_simt(const mf_lnl_bwd_args& a, cudaStream_t st);
+int lnl_bwd_simt(const mf_lnl_bwd_args& a, cudaStream_t st);   // picks tensor-core GEMMs when lnl_bwd_runs_on_tc
+bool lnl_bwd_runs_on_tc(const mf_lnl_bwd_args& a);
+bool transition_bwd_runs_on_tc(const mf_transition_bwd_args& a);
 size_t lnl_bwd_simt_workspace(const mf_lnl_bwd_args& a);
 
 int transition_fwd_simt(const mf_transition_fwd_args& a, cudaStream_t st);

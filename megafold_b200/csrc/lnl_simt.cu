@@ -4,6 +4,7 @@
 // All reductions over rows (weight, gain and bias gradients) are split into slices whose partial
 // sums are added in a fixed order, so results are bit-reproducible.
 #include "gemm_simt.cuh"
+#include "gemm_tc.cuh"
 
 namespace mf {
 namespace {
@@ -136,6 +137,111 @@ __global__ void ln_bwd_rows_kernel(const float* __restrict__ dyln, const T* __re
   }
 }
 
+// Row pass of the tensor-core backward (16-bit T, K % 4 == 0, K <= 128 * KJ): one read of dyln and x gives dx,
+// LN(x) in the operand dtype (the A operand of the weight-gradient GEMM) and per-block partial column sums
+// of dyln * xhat and dyln.  part is [gridDim.x][2 * K]; the partials are added in a fixed order afterwards.
+template <typename T, int KJ>
+__global__ void __launch_bounds__(256)
+ln_bwd_rows_fused_kernel(const float* __restrict__ dyln, const T* __restrict__ x, const T* __restrict__ gain,
+                         const T* __restrict__ shift, const float* __restrict__ mean, const float* __restrict__ rstd,
+                         T* __restrict__ dx, T* __restrict__ xln, float* __restrict__ part, int64_t M, int K,
+                         int64_t rows_per_block) {
+  extern __shared__ float red[];   // [8][2 * K]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t beg = (int64_t)blockIdx.x * rows_per_block;
+  const int64_t end = beg + rows_per_block < M ? beg + rows_per_block : M;
+  float gn[KJ][4], sh[KJ][4], dgn[KJ][4], dsh[KJ][4];
+#pragma unroll
+  for (int j = 0; j < KJ; ++j) {
+    const int k = j * 128 + lane * 4;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      gn[j][e] = k + e < K ? to_f(gain[k + e]) : 0.f;
+      sh[j][e] = (shift && k + e < K) ? to_f(shift[k + e]) : 0.f;
+      dgn[j][e] = 0.f; dsh[j][e] = 0.f;
+    }
+  }
+  const float invK = 1.f / K;
+  for (int64_t m = beg + warp; m < end; m += 8) {
+    const float mu = mean[m], rs = rstd[m];
+    float xh[KJ][4], d[KJ][4];
+    float c1 = 0.f, c2 = 0.f;
+#pragma unroll
+    for (int j = 0; j < KJ; ++j) {
+      const int k = j * 128 + lane * 4;
+      if (k < K) {
+        const uint2 xr = *reinterpret_cast<const uint2*>(x + m * K + k);
+        const float4 dr = *reinterpret_cast<const float4*>(dyln + m * K + k);
+        const T* xe = reinterpret_cast<const T*>(&xr);
+        d[j][0] = dr.x; d[j][1] = dr.y; d[j][2] = dr.z; d[j][3] = dr.w;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          xh[j][e] = (to_f(xe[e]) - mu) * rs;
+          const float w = d[j][e] * gn[j][e];
+          c1 = fmaf(xh[j][e], w, c1); c2 += w;
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { xh[j][e] = 0.f; d[j][e] = 0.f; }
+      }
+    }
+    c1 = warp_sum(c1) * invK; c2 = warp_sum(c2) * invK;
+#pragma unroll
+    for (int j = 0; j < KJ; ++j) {
+      const int k = j * 128 + lane * 4;
+      if (k < K) {
+        __align__(8) T o[4]; __align__(8) T l[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float w = d[j][e] * gn[j][e];
+          o[e] = from_f<T>((w - (c1 * xh[j][e] + c2)) * rs);
+          l[e] = from_f<T>(fmaf(xh[j][e], gn[j][e], sh[j][e]));
+          dgn[j][e] = fmaf(d[j][e], xh[j][e], dgn[j][e]);
+          dsh[j][e] += d[j][e];
+        }
+        *reinterpret_cast<uint2*>(dx + m * K + k) = *reinterpret_cast<const uint2*>(o);
+        if (xln) *reinterpret_cast<uint2*>(xln + m * K + k) = *reinterpret_cast<const uint2*>(l);
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < KJ; ++j) {
+    const int k = j * 128 + lane * 4;
+    if (k < K) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) { red[warp * 2 * K + k + e] = dgn[j][e]; red[warp * 2 * K + K + k + e] = dsh[j][e]; }
+    }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < 2 * K; c += 256) {
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) t += red[w * 2 * K + c];
+    part[(int64_t)blockIdx.x * 2 * K + c] = t;
+  }
+}
+
+// xln = LN(x) from saved statistics, four elements per thread (16-bit T, K % 4 == 0)
+template <typename T>
+__global__ void ln_apply_kernel(const T* __restrict__ x, const T* __restrict__ gain, const T* __restrict__ shift,
+                                const float* __restrict__ mean, const float* __restrict__ rstd, T* __restrict__ xln,
+                                int64_t M, int K) {
+  const int64_t q = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int kq = K >> 2;
+  if (q >= M * kq) return;
+  const int64_t m = q / kq; const int k = (int)(q - m * kq) * 4;
+  const float mu = mean[m], rs = rstd[m];
+  const uint2 xr = *reinterpret_cast<const uint2*>(x + m * K + k);
+  const T* xe = reinterpret_cast<const T*>(&xr);
+  __align__(8) T o[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    float v = (to_f(xe[e]) - mu) * rs * to_f(gain[k + e]);
+    o[e] = from_f<T>(shift ? v + to_f(shift[k + e]) : v);
+  }
+  *reinterpret_cast<uint2*>(xln + m * K + k) = *reinterpret_cast<const uint2*>(o);
+}
+
 template <typename T>
 __global__ void cast_rows_kernel(const float* __restrict__ src, T* __restrict__ dst, int64_t n) {
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -206,7 +312,7 @@ __global__ void swiglu_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, in
   y[idx] = from_f<T>(b * sigmoidf_(b) * a);
 }
 template <typename T>
-__global__ void swiglu_bwd_kernel(const T* __restrict__ x, const T* __restrict__ dy, T* __restrict__ dx,
+__global__ void swiglu_bwd_kernel(const T* x, const T* __restrict__ dy, T* dx,   // dx may alias x
                                   int64_t total, int I) {
   int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
@@ -233,14 +339,52 @@ int dw_splits(int K, int N, int64_t M) {
   return pick_splits(tiles, M);
 }
 
+constexpr int kRowBlocks = 296;   // blocks of the fused row pass (two per SM)
+
+// Can the backward GEMMs of a LayernormLinear with these sizes run on the tensor cores?
+bool lnl_bwd_core_tc_ok(int64_t M, int K, int N, int dtype, bool has_ln, const void* x, const void* w, const void* dy,
+                        const void* dx, const void* dw) {
+  if (!has_ln || (dtype != MF_BF16 && dtype != MF_F16)) return false;
+  if (K % 8 || N % 8 || K > 512 || M < 1) return false;
+  const uintptr_t al = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(dy) |
+                       reinterpret_cast<uintptr_t>(dx) | reinterpret_cast<uintptr_t>(dw);
+  return (al & 15) == 0;
+}
+
 // Shared tail of LayernormLinear backward: given dy [M,N] computes dx, dw, d_ln_w, d_ln_b, db.
 // gain == nullptr: no LayerNorm (dx = dy @ w^T, dw = x^T dy).
+// tc: both GEMMs on the tensor cores (gemm_tc), with one fused row pass between them.
 template <typename T>
 int lnl_bwd_core(int64_t M, int K, int N, const T* x, const T* gain, const T* shift, const T* w, const T* dy,
                  const float* mean, const float* rstd, T* dx, float* dw, float* db, float* d_ln_w, float* d_ln_b,
-                 Carver& ws, cudaStream_t st) {
+                 Carver& ws, bool tc, int dtype, cudaStream_t st, const T* xln_ready = nullptr) {
   int r;
   float* col_scratch = ws.take<float>((size_t)kColSlices * (K > N ? K : N));
+  if constexpr (sizeof(T) == 2) {
+    if (tc) {
+      float* dyln = ws.take<float>((size_t)M * K);
+      T* xln = xln_ready ? nullptr : ws.take<T>((size_t)M * K);
+      float* part = ws.take<float>((size_t)kRowBlocks * 2 * K);
+      // dyln[M,K] = dy @ w^T  (A = dy [M,N], B = w [K,N], both with the reduction index contiguous)
+      r = gemm_tc(GemmTcArgs{dy, w, dyln, M, K, N, dtype, 0, 0, 1}, st);
+      if (r) return r;
+      int blocks = (int)((M + 63) / 64); if (blocks > kRowBlocks) blocks = kRowBlocks;
+      const int64_t rpb = (M + blocks - 1) / blocks;
+      blocks = (int)((M + rpb - 1) / rpb);
+      const size_t sm = sizeof(float) * 8 * 2 * K;
+      const int kj = (K + 127) / 128;
+#define MF_ROWS(KJ) ln_bwd_rows_fused_kernel<T, KJ><<<blocks, 256, sm, st>>>(dyln, x, gain, shift, mean, rstd, dx, xln, part, M, K, rpb)
+      if (kj == 1) MF_ROWS(1); else if (kj == 2) MF_ROWS(2); else if (kj == 3) MF_ROWS(3); else MF_ROWS(4);
+#undef MF_ROWS
+      MF_LAUNCHED("ln_bwd_rows_fused_kernel");
+      r = colsum("lnl_bwd_dgain", ColF32{part, 2 * K}, d_ln_w, col_scratch, blocks, K, st);
+      if (r) return r;
+      if (d_ln_b) { r = colsum("lnl_bwd_dshift", ColF32{part + K, 2 * K}, d_ln_b, col_scratch, blocks, K, st); if (r) return r; }
+      if (db) { r = colsum("lnl_bwd_dbias", ColT<T>{dy, N}, db, col_scratch, M, N, st); if (r) return r; }
+      // dw[K,N] = LN(x)^T @ dy: both operands are given with the reduction index (rows) outermost
+      return gemm_tc(GemmTcArgs{xln_ready ? xln_ready : xln, dy, dw, K, N, M, dtype, 1, 1, 2}, st);
+    }
+  }
   LoadLN<T> ln{x, gain, shift, mean, rstd, K};
   if (gain) {
     float* dyln = ws.take<float>((size_t)M * K);
@@ -269,12 +413,31 @@ int lnl_bwd_core(int64_t M, int K, int N, const T* x, const T* gain, const T* sh
   return MF_OK;
 }
 
-size_t lnl_bwd_core_bytes(int64_t M, int K, int N, bool has_ln) {
+size_t lnl_bwd_core_bytes(int64_t M, int K, int N, bool has_ln, bool tc, int dtype) {
   size_t b = align_up(sizeof(float) * (size_t)kColSlices * (K > N ? K : N), 256);
+  if (tc) {
+    b += align_up(sizeof(float) * (size_t)M * K, 256) + align_up(dtype_size(dtype) * (size_t)M * K, 256) +
+         align_up(sizeof(float) * (size_t)kRowBlocks * 2 * K, 256);
+    return b;
+  }
   if (has_ln) b += align_up(sizeof(float) * (size_t)M * K, 256);
   int S = dw_splits(K, N, M);
   if (S > 1) b += align_up(sizeof(float) * (size_t)S * K * N, 256);
   return b;
+}
+
+bool lnl_bwd_use_tc(const mf_lnl_bwd_args& a) {
+  return !(a.flags & MF_FLAG_FORCE_SIMT) &&
+         lnl_bwd_core_tc_ok(a.M, a.K, a.N, a.dtype, a.ln_w != nullptr, a.x, a.w, a.dy, a.dx, a.dw);
+}
+
+// The tensor-core Transition backward needs 16-byte aligned rows everywhere.
+bool transition_bwd_use_tc(const mf_transition_bwd_args& a) {
+  if ((a.flags & MF_FLAG_FORCE_SIMT) || !a.ln_w) return false;
+  if (a.inner % 8 || a.dim % 8) return false;
+  const uintptr_t al = reinterpret_cast<uintptr_t>(a.w2) | reinterpret_cast<uintptr_t>(a.dw2);
+  if (al & 15) return false;
+  return lnl_bwd_core_tc_ok(a.M, a.dim, 2 * a.inner, a.dtype, true, a.x, a.w1, a.dy, a.dx, a.dw1);
 }
 
 }  // namespace
@@ -294,14 +457,22 @@ int lnl_fwd_simt(const mf_lnl_fwd_args& a, cudaStream_t st) {
   return MF_OK;
 }
 
-size_t lnl_bwd_simt_workspace(const mf_lnl_bwd_args& a) { return lnl_bwd_core_bytes(a.M, a.K, a.N, true); }
+size_t lnl_bwd_simt_workspace(const mf_lnl_bwd_args& a) {
+  // the larger of the two paths, so that the answer does not depend on pointer alignment
+  const size_t simt = lnl_bwd_core_bytes(a.M, a.K, a.N, true, false, a.dtype);
+  const size_t tc = lnl_bwd_use_tc(a) ? lnl_bwd_core_bytes(a.M, a.K, a.N, true, true, a.dtype) : 0;
+  return simt > tc ? simt : tc;
+}
+bool lnl_bwd_runs_on_tc(const mf_lnl_bwd_args& a) { return lnl_bwd_use_tc(a); }
+bool transition_bwd_runs_on_tc(const mf_transition_bwd_args& a) { return transition_bwd_use_tc(a); }
 
 int lnl_bwd_simt(const mf_lnl_bwd_args& a, cudaStream_t st) {
   Carver ws(a.workspace);
+  const bool tc = lnl_bwd_use_tc(a);
   MF_DISPATCH_FLOAT(a.dtype, T, {
     int r = lnl_bwd_core<T>(a.M, a.K, a.N, static_cast<const T*>(a.x), static_cast<const T*>(a.ln_w),
                             static_cast<const T*>(a.ln_b), static_cast<const T*>(a.w), static_cast<const T*>(a.dy),
-                            a.mean, a.rstd, static_cast<T*>(a.dx), a.dw, a.db, a.d_ln_w, a.d_ln_b, ws, st);
+                            a.mean, a.rstd, static_cast<T*>(a.dx), a.dw, a.db, a.d_ln_w, a.d_ln_b, ws, tc, a.dtype, st);
     if (r) return r;
   });
   return MF_OK;
@@ -356,14 +527,56 @@ int transition_fwd_simt(const mf_transition_fwd_args& a, cudaStream_t st) {
 }
 
 size_t transition_bwd_simt_workspace(const mf_transition_bwd_args& a) {
-  size_t b = align_up((size_t)a.M * 2 * a.inner * dtype_size(a.dtype), 256);     // h, then dh in place
+  size_t simt = align_up((size_t)a.M * 2 * a.inner * dtype_size(a.dtype), 256);     // h, then dh in place
   int S = dw_splits(a.dim, a.inner, a.M);
-  if (S > 1) b += align_up(sizeof(float) * (size_t)S * a.dim * a.inner, 256);     // dw2 slices
-  b += lnl_bwd_core_bytes(a.M, a.dim, 2 * a.inner, a.ln_w != nullptr);
-  return b;
+  if (S > 1) simt += align_up(sizeof(float) * (size_t)S * a.dim * a.inner, 256);     // dw2 slices
+  simt += lnl_bwd_core_bytes(a.M, a.dim, 2 * a.inner, a.ln_w != nullptr, false, a.dtype);
+  size_t tc = 0;
+  if (transition_bwd_use_tc(a)) {
+    const size_t es = dtype_size(a.dtype);
+    tc = align_up((size_t)a.M * 2 * a.inner * es, 256) + 2 * align_up((size_t)a.M * a.inner * es, 256) +   // h/dh, g, dg
+         align_up((size_t)a.M * a.dim * es, 256) +                                                          // LN(x)
+         lnl_bwd_core_bytes(a.M, a.dim, 2 * a.inner, true, true, a.dtype);
+  }
+  return simt > tc ? simt : tc;
+}
+
+// Tensor-core composition: xln = LN(x) from the saved statistics; h = xln w1 (recomputed, never saved by forward);
+// g = swiglu(h); dw2 = dy^T g; dg = dy w2; dh = swiglu'(h, dg) in place; LayernormLinear backward with dy := dh.
+template <typename T>
+int transition_bwd_tc(const mf_transition_bwd_args& a, cudaStream_t st) {
+  Carver ws(a.workspace);
+  const int I = a.inner;
+  const int64_t M = a.M;
+  T* h = ws.take<T>((size_t)M * 2 * I);
+  T* g = ws.take<T>((size_t)M * I);
+  T* dg = ws.take<T>((size_t)M * I);
+  T* xln = ws.take<T>((size_t)M * a.dim);
+  {
+    const int64_t quads = M * (a.dim / 4);
+    ln_apply_kernel<T><<<(unsigned)((quads + 255) / 256), 256, 0, st>>>(
+        static_cast<const T*>(a.x), static_cast<const T*>(a.ln_w), static_cast<const T*>(a.ln_b), a.mean, a.rstd, xln, M, a.dim);
+    MF_LAUNCHED("ln_apply_kernel");
+  }
+  // h[M, 2I] = LN(x) @ w1   (w1 [dim, 2I]: the reduction index is outermost)
+  int r = gemm_tc(GemmTcArgs{xln, a.w1, h, M, 2 * I, a.dim, a.dtype, 0, 1, 0}, st);
+  if (r) return r;
+  r = swiglu_fwd(h, g, M, I, a.dtype, st);
+  if (r) return r;
+  r = gemm_tc(GemmTcArgs{a.dy, g, a.dw2, a.dim, I, M, a.dtype, 1, 1, 2}, st);
+  if (r) return r;
+  r = gemm_tc(GemmTcArgs{a.dy, a.w2, dg, M, I, a.dim, a.dtype, 0, 1, 0}, st);
+  if (r) return r;
+  r = swiglu_bwd(h, dg, h, M, I, a.dtype, st);
+  if (r) return r;
+  return lnl_bwd_core<T>(M, a.dim, 2 * I, static_cast<const T*>(a.x), static_cast<const T*>(a.ln_w),
+                         static_cast<const T*>(a.ln_b), static_cast<const T*>(a.w1), h, a.mean, a.rstd,
+                         static_cast<T*>(a.dx), a.dw1, nullptr, a.d_ln_w, a.d_ln_b, ws, true, a.dtype, st, xln);
 }
 
 int transition_bwd_simt(const mf_transition_bwd_args& a, cudaStream_t st) {
+  if (transition_bwd_use_tc(a))
+    return a.dtype == MF_BF16 ? transition_bwd_tc<__nv_bfloat16>(a, st) : transition_bwd_tc<__half>(a, st);
   Carver ws(a.workspace);
   const int I = a.inner;
   MF_DISPATCH_FLOAT(a.dtype, T, {
@@ -390,7 +603,7 @@ int transition_bwd_simt(const mf_transition_bwd_args& a, cudaStream_t st) {
     if (r) return r;
     // 4. LayernormLinear backward with dy := dh
     r = lnl_bwd_core<T>(a.M, a.dim, 2 * I, x, static_cast<const T*>(a.ln_w), static_cast<const T*>(a.ln_b), w1, h,
-                        a.mean, a.rstd, static_cast<T*>(a.dx), a.dw1, nullptr, a.d_ln_w, a.d_ln_b, ws, st);
+                        a.mean, a.rstd, static_cast<T*>(a.dx), a.dw1, nullptr, a.d_ln_w, a.d_ln_b, ws, false, a.dtype, st);
     if (r) return r;
   });
   return MF_OK;

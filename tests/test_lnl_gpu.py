@@ -7,6 +7,7 @@ import torch
 
 import cases
 import megafold_b200 as mfb
+from megafold_b200 import _lib
 from oracle import pairformer_oracle as orc
 from util import assert_close_fp32, assert_close_lowp
 
@@ -171,4 +172,34 @@ def test_transition_bf16_against_fp32_oracle(M, dim, ef):
     r = [t.to(torch.bfloat16).float() for t in (x, ln_w, ln_b, w1, w2, dy)]
     ref = orc.transition_fwd_bwd(*r)
     for g_, r_, n in zip(got, ref, T_NAMES):
+        assert_close_lowp(g_, r_, n)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("M,N,K", [(20000, 512, 128), (1001, 72, 200), (9000, 1024, 128), (130, 8, 8)])
+def test_lnl_backward_tensor_core_path(M, N, K, dtype):
+    """Split reduction over many CTAs, ragged tiles in every dimension, both 16-bit types."""
+    x, ln_w, ln_b, w, b, dy = [t.to(DEV, dtype) for t in _lnl_case(M, N, K, seed=7)]
+    dy = dy / 8
+    _, mean, rstd = mfb.layernorm_linear_forward(x, w, b, ln_w, ln_b)
+    got = mfb.layernorm_linear_backward(dy, x, w, ln_w, ln_b, mean, rstd, True)
+    assert _lib.last_path() == "tcgen05"
+    ref = orc.layernorm_linear_fwd_bwd(*[t.float().cpu() for t in (x, ln_w, ln_b, w, b, dy)])
+    _, dx, dlw, dlb, dw, db = ref
+    for g_, r_, n in zip(got, (dx, dw, db, dlw, dlb), ("dx", "dw", "db", "d_ln_w", "d_ln_b")):
+        assert_close_lowp(g_, r_, n)
+    simt = mfb.layernorm_linear_backward(dy, x, w, ln_w, ln_b, mean, rstd, True, flags=_lib.MF_FLAG_FORCE_SIMT)
+    assert _lib.last_path() == "simt"
+    for g_, r_, n in zip(got, simt, ("dx", "dw", "db", "d_ln_w", "d_ln_b")):
+        assert_close_lowp(g_, r_.float(), n + " vs CUDA cores")
+
+
+@pytest.mark.parametrize("M,dim,ef", [(12000, 128, 4), (777, 64, 2), (300, 384, 4)])
+def test_transition_backward_tensor_core_path(M, dim, ef):
+    x, ln_w, ln_b, w1, w2, dy = [t.to(DEV, torch.bfloat16) for t in _transition_case(M, dim, ef, seed=3)]
+    _, mean, rstd = mfb.transition_forward(x, ln_w, ln_b, w1, w2)
+    got = mfb.transition_backward(dy, x, ln_w, ln_b, w1, w2, mean, rstd)
+    assert _lib.last_path() == "tcgen05"
+    ref = orc.transition_fwd_bwd(*[t.float().cpu() for t in (x, ln_w, ln_b, w1, w2, dy)])
+    for g_, r_, n in zip(got, ref[1:], ("dx", "d_ln_w", "d_ln_b", "dw1", "dw2")):
         assert_close_lowp(g_, r_, n)
