@@ -368,7 +368,7 @@ def extras(dev, steps=5):
         "forward_tflops": f_fwd / (ms_f * 1e-3) / 1e12, "forward_frac_of_measured_bf16_peak": f_fwd / (ms_f * 1e-3) / 1e12 / peaks["tflops"],
         "fwd_bwd_tflops": 3.0 * f_fwd / ((ms_f + ms_b) * 1e-3) / 1e12,
         "peak_extra_memory_mb_fwd_bwd": peak / 2 ** 20,
-        "note": "forward keeps the hidden activation on chip; backward recomputes it (CUDA-core path, workspace counted in the peak)"}
+        "note": "forward keeps the hidden activation on chip; backward recomputes it (workspace counted in the peak)"}
     return out
 
 

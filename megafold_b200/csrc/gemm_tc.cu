@@ -25,6 +25,7 @@ constexpr int kStageBytes = 2 * 128 * 128;       // A slab 16 KB + B slab 16 KB
 
 struct GemmP {
   int m_tiles, n_tiles, k_splits, slabs_total, slabs_per_split;
+  int n_cols;
   int a_mn, b_mn, out_kind;     // out_kind: 0 = 16-bit store, 1 = fp32 store, 2 = fp32 add-reduction
   uint32_t ab_fmt;
   int* status;
@@ -174,10 +175,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap ma, const __grid_constant__ C
       if (tid == 128) {
         if (p.out_kind == 0) {
           tma_store_2d(&mc, sOut, nt * kBN, mt * kBM);
-          tma_store_2d(&mc, sOut + 16384, nt * kBN + 64, mt * kBM);
+          if (nt * kBN + 64 < p.n_cols) tma_store_2d(&mc, sOut + 16384, nt * kBN + 64, mt * kBM);
         } else {
 #pragma unroll
           for (int cb = 0; cb < 4; ++cb) {
+            if (nt * kBN + cb * 32 >= p.n_cols) break;       // never start a store past the last column
             if (p.out_kind == 2) tma_reduce_add_2d(&mc, sOut + cb * 16384, nt * kBN + cb * 32, mt * kBM);
             else tma_store_2d(&mc, sOut + cb * 16384, nt * kBN + cb * 32, mt * kBM);
           }
@@ -241,6 +243,7 @@ int gemm_tc(const GemmTcArgs& g, cudaStream_t st) {
   }
   p.slabs_per_split = (p.slabs_total + splits - 1) / splits;
   p.k_splits = (p.slabs_total + p.slabs_per_split - 1) / p.slabs_per_split;
+  p.n_cols = (int)g.N;
   p.a_mn = g.a_mn; p.b_mn = g.b_mn; p.out_kind = g.out_kind;
   p.ab_fmt = g.dtype == MF_BF16 ? 1u : 0u;
   p.status = status_word();
