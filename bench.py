@@ -291,8 +291,8 @@ def run_only(args):
     """One kernel family in a loop on a (small) case: the command ncu captures are taken from."""
     import megafold_b200 as mfb
     from megafold_b200 import workloads
-    from megafold_b200.fused_layernorm_linear import layernorm_linear_forward
-    from megafold_b200.fused_transition import transition_forward
+    from megafold_b200.fused_layernorm_linear import layernorm_linear_backward, layernorm_linear_forward
+    from megafold_b200.fused_transition import transition_backward, transition_forward
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     if args.only in ("fwd", "bwd"):
@@ -302,12 +302,18 @@ def run_only(args):
             fn = lambda: mfb.evo_attention_forward(c["q"], c["k"], c["v"], c["mask"], c["bias"])            # noqa: E731
         else:
             fn = lambda: mfb.evo_attention_backward(c["d_out"], c["q"], c["k"], c["v"], c["mask"], c["bias"], o, lse)  # noqa: E731
-    elif args.only == "lnl":
+    elif args.only in ("lnl", "lnl_bwd"):
         c = {k: (v.to(dev) if v is not None else None) for k, v in workloads.layernorm_linear(M=args.rows * L).items()}
         fn = lambda: layernorm_linear_forward(c["x"], c["w"], c["b"], c["ln_w"], c["ln_b"])                   # noqa: E731
+        if args.only == "lnl_bwd":
+            _, mean, rstd = fn()
+            fn = lambda: layernorm_linear_backward(c["d_out"], c["x"], c["w"], c["ln_w"], c["ln_b"], mean, rstd, True)  # noqa: E731
     else:
         c = {k: v.to(dev) for k, v in workloads.transition(M=args.rows * L).items()}
         fn = lambda: transition_forward(c["x"], c["ln_w"], c["ln_b"], c["w1"], c["w2"])                       # noqa: E731
+        if args.only == "transition_bwd":
+            _, mean, rstd = fn()
+            fn = lambda: transition_backward(c["d_out"], c["x"], c["ln_w"], c["ln_b"], c["w1"], c["w2"], mean, rstd)  # noqa: E731
     ms = _time_cuda(fn, args.steps, args.warmup)
     print(f"{args.only}: rows={args.rows} {ms * 1e3:.1f} us per call")
 
@@ -387,7 +393,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--rows", type=int, default=ROWS, help="rows (N) per GPU; smaller values give profiler-sized cases")
-    ap.add_argument("--only", default="all", choices=["all", "fwd", "bwd", "lnl", "transition"],
+    ap.add_argument("--only", default="all", choices=["all", "fwd", "bwd", "lnl", "lnl_bwd", "transition", "transition_bwd"],
                     help="run just one kernel family in the timed loop (for ncu captures); prints no JSON line")
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary workloads (cfg 3, cfg 4, LayernormLinear)")
     args = ap.parse_args()

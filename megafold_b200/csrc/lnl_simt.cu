@@ -323,6 +323,74 @@ __global__ void swiglu_bwd_kernel(const T* x, const T* __restrict__ dy, T* dx,  
   dx[m * 2 * I + I + c] = from_f<T>(g * (sl * (1.f - sg) + sg) * a);
 }
 
+// 16-bit SwiGLU, eight elements per thread (I % 8 == 0): full 16-byte accesses on both halves of the row
+template <typename T>
+__global__ void swiglu_fwd_vec_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t total8, int I8) {
+  const int64_t q = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (q >= total8) return;
+  const int64_t m = q / I8; const int c = (int)(q - m * I8) * 8;
+  const int I = I8 * 8;
+  const uint4 av = *reinterpret_cast<const uint4*>(x + m * 2 * I + c);
+  const uint4 bv = *reinterpret_cast<const uint4*>(x + m * 2 * I + I + c);
+  const T* a = reinterpret_cast<const T*>(&av); const T* b = reinterpret_cast<const T*>(&bv);
+  __align__(16) T o[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) { const float bf = to_f(b[e]); o[e] = from_f<T>(bf * sigmoidf_(bf) * to_f(a[e])); }
+  *reinterpret_cast<uint4*>(y + m * I + c) = *reinterpret_cast<const uint4*>(o);
+}
+template <typename T>
+__global__ void swiglu_bwd_vec_kernel(const T* x, const T* __restrict__ dy, T* dx, int64_t total8, int I8) {   // dx may alias x
+  const int64_t q = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (q >= total8) return;
+  const int64_t m = q / I8; const int c = (int)(q - m * I8) * 8;
+  const int I = I8 * 8;
+  const uint4 av = *reinterpret_cast<const uint4*>(x + m * 2 * I + c);
+  const uint4 bv = *reinterpret_cast<const uint4*>(x + m * 2 * I + I + c);
+  const uint4 gv = *reinterpret_cast<const uint4*>(dy + m * I + c);
+  const T* a = reinterpret_cast<const T*>(&av); const T* b = reinterpret_cast<const T*>(&bv);
+  const T* g = reinterpret_cast<const T*>(&gv);
+  __align__(16) T da[8]; __align__(16) T db[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const float bf = to_f(b[e]), gf = to_f(g[e]);
+    const float sg = sigmoidf_(bf), sl = bf * sg;
+    da[e] = from_f<T>(gf * sl);
+    db[e] = from_f<T>(gf * (sl * (1.f - sg) + sg) * to_f(a[e]));
+  }
+  *reinterpret_cast<uint4*>(dx + m * 2 * I + c) = *reinterpret_cast<const uint4*>(da);
+  *reinterpret_cast<uint4*>(dx + m * 2 * I + I + c) = *reinterpret_cast<const uint4*>(db);
+}
+
+// Column sums of a 16-bit [M, N] matrix (N % 8 == 0, N <= 2048): thread = (row lane, 8-column chunk), 16-byte loads,
+// one partial row of sums per block; part is [gridDim.x][N].
+template <typename T>
+__global__ void __launch_bounds__(256)
+colsum16_partial_kernel(const T* __restrict__ p, float* __restrict__ part, int64_t M, int N, int64_t rows_per_block) {
+  extern __shared__ float red[];       // [row lanes][N]
+  const int chunks = N >> 3;
+  const int lanes = 256 / chunks;      // row lanes per block (chunks <= 256)
+  const int rl = threadIdx.x / chunks, ch = threadIdx.x - rl * chunks;
+  const int64_t beg = (int64_t)blockIdx.x * rows_per_block;
+  const int64_t end = beg + rows_per_block < M ? beg + rows_per_block : M;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (rl < lanes) {
+    for (int64_t m = beg + rl; m < end; m += lanes) {
+      const uint4 v = *reinterpret_cast<const uint4*>(p + m * N + ch * 8);
+      const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] += to_f(e[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) red[rl * N + ch * 8 + i] = acc[i];
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < N; c += 256) {
+    float t = 0.f;
+    for (int l = 0; l < lanes; ++l) t += red[l * N + c];
+    part[(int64_t)blockIdx.x * N + c] = t;
+  }
+}
+
 // workspace carving ------------------------------------------------------------------------------
 struct Carver {
   char* base; size_t off = 0;
@@ -380,7 +448,21 @@ int lnl_bwd_core(int64_t M, int K, int N, const T* x, const T* gain, const T* sh
       r = colsum("lnl_bwd_dgain", ColF32{part, 2 * K}, d_ln_w, col_scratch, blocks, K, st);
       if (r) return r;
       if (d_ln_b) { r = colsum("lnl_bwd_dshift", ColF32{part + K, 2 * K}, d_ln_b, col_scratch, blocks, K, st); if (r) return r; }
-      if (db) { r = colsum("lnl_bwd_dbias", ColT<T>{dy, N}, db, col_scratch, M, N, st); if (r) return r; }
+      if (db) {
+        if (N <= 2048) {
+          int cb = (int)((M + 63) / 64); if (cb > kRowBlocks) cb = kRowBlocks;
+          const int64_t rows = (M + cb - 1) / cb;
+          cb = (int)((M + rows - 1) / rows);
+          float* dpart = ws.take<float>((size_t)kRowBlocks * N);
+          const int lanes = 256 / (N / 8);
+          colsum16_partial_kernel<T><<<cb, 256, sizeof(float) * lanes * N, st>>>(dy, dpart, M, N, rows);
+          MF_LAUNCHED("colsum16_partial_kernel");
+          r = colsum("lnl_bwd_dbias", ColF32{dpart, N}, db, col_scratch, cb, N, st);
+        } else {
+          r = colsum("lnl_bwd_dbias", ColT<T>{dy, N}, db, col_scratch, M, N, st);
+        }
+        if (r) return r;
+      }
       // dw[K,N] = LN(x)^T @ dy: both operands are given with the reduction index (rows) outermost
       return gemm_tc(GemmTcArgs{xln_ready ? xln_ready : xln, dy, dw, K, N, M, dtype, 1, 1, 2}, st);
     }
@@ -417,7 +499,7 @@ size_t lnl_bwd_core_bytes(int64_t M, int K, int N, bool has_ln, bool tc, int dty
   size_t b = align_up(sizeof(float) * (size_t)kColSlices * (K > N ? K : N), 256);
   if (tc) {
     b += align_up(sizeof(float) * (size_t)M * K, 256) + align_up(dtype_size(dtype) * (size_t)M * K, 256) +
-         align_up(sizeof(float) * (size_t)kRowBlocks * 2 * K, 256);
+         align_up(sizeof(float) * (size_t)kRowBlocks * 2 * K, 256) + align_up(sizeof(float) * (size_t)kRowBlocks * N, 256);
     return b;
   }
   if (has_ln) b += align_up(sizeof(float) * (size_t)M * K, 256);
@@ -482,6 +564,15 @@ int lnl_bwd_simt(const mf_lnl_bwd_args& a, cudaStream_t st) {
 int swiglu_fwd(const void* x, void* y, int64_t M, int inner, int dtype, cudaStream_t st) {
   const int64_t total = M * inner;
   if (total == 0) return MF_OK;
+  if (dtype != MF_F32 && inner % 8 == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0) {
+    const int64_t t8 = total / 8;
+    if (dtype == MF_BF16)
+      swiglu_fwd_vec_kernel<__nv_bfloat16><<<(unsigned)((t8 + 255) / 256), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), t8, inner / 8);
+    else
+      swiglu_fwd_vec_kernel<__half><<<(unsigned)((t8 + 255) / 256), 256, 0, st>>>(static_cast<const __half*>(x), static_cast<__half*>(y), t8, inner / 8);
+    MF_LAUNCHED("swiglu_fwd_vec_kernel");
+    return MF_OK;
+  }
   MF_DISPATCH_FLOAT(dtype, T, {
     swiglu_fwd_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(static_cast<const T*>(x), static_cast<T*>(y), total, inner);
     MF_LAUNCHED("swiglu_fwd_kernel");
@@ -491,6 +582,18 @@ int swiglu_fwd(const void* x, void* y, int64_t M, int inner, int dtype, cudaStre
 int swiglu_bwd(const void* x, const void* dy, void* dx, int64_t M, int inner, int dtype, cudaStream_t st) {
   const int64_t total = M * inner;
   if (total == 0) return MF_OK;
+  if (dtype != MF_F32 && inner % 8 == 0 &&
+      ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(dx)) & 15) == 0) {
+    const int64_t t8 = total / 8;
+    if (dtype == MF_BF16)
+      swiglu_bwd_vec_kernel<__nv_bfloat16><<<(unsigned)((t8 + 255) / 256), 256, 0, st>>>(
+          static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(dy), static_cast<__nv_bfloat16*>(dx), t8, inner / 8);
+    else
+      swiglu_bwd_vec_kernel<__half><<<(unsigned)((t8 + 255) / 256), 256, 0, st>>>(
+          static_cast<const __half*>(x), static_cast<const __half*>(dy), static_cast<__half*>(dx), t8, inner / 8);
+    MF_LAUNCHED("swiglu_bwd_vec_kernel");
+    return MF_OK;
+  }
   MF_DISPATCH_FLOAT(dtype, T, {
     swiglu_bwd_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(
         static_cast<const T*>(x), static_cast<const T*>(dy), static_cast<T*>(dx), total, inner);
