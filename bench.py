@@ -33,6 +33,11 @@ L, H, D, ROWS = 384, 4, 32, 384
 METRIC, UNIT = "triangle_attention_fwd_bwd_throughput", "TFLOP/s"
 
 
+# DRAM bytes per launch (read + write) of evo_fwd_tc_kernel / evo_bwd_tc_kernel at 384 rows, L = 384, H = 4, D = 32, bf16:
+# one ncu --set full capture each, summarised under profiles/ in the files named for these kernels
+NCU_DRAM_BYTES = {"forward": 140071168 + 21487872, "backward": 160271104 + 76499456}
+
+
 def flops_per_step(rows):
     return 14.0 * rows * H * L * L * D          # 2 matmuls forward + 5 backward, 2*rows*H*L*L*D each
 
@@ -262,7 +267,10 @@ def run_ours(args):
         "gpu_launches": int(launches),
         "roofline": {"bound": "tensor", "kernel": f"attention {dom} ({path_bwd if dom == 'backward' else path_fwd})",
                      "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["tflops"],
-                     "traffic": None, "peak_source": peaks["src"] + " bf16 burst"},
+                     # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the main kernel of that call at this
+                     # size, from the ncu captures summarised under profiles/ (not measured in this run)
+                     "traffic": (NCU_DRAM_BYTES[dom] if ROWS == 384 else None), "traffic_unit": "bytes per launch",
+                     "peak_source": peaks["src"] + " bf16 burst"},
         "cpu_baseline": cpu_baseline() if world == 1 else None,
     }
     if world == 1 and not args.no_extras:
