@@ -25,6 +25,7 @@ import threading
 import time
 
 import torch
+import torch.distributed as dist
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
@@ -316,6 +317,24 @@ def run_only(args):
         if args.only == "lnl_bwd":
             _, mean, rstd = fn()
             fn = lambda: layernorm_linear_backward(c["d_out"], c["x"], c["w"], c["ln_w"], c["ln_b"], mean, rstd, True)  # noqa: E731
+    elif args.only == "block":
+        # strong scaling of the long-crop block: rows of the pair representation sharded over the ranks
+        world = int(os.environ.get("WORLD_SIZE", "1"))
+        if world > 1:
+            dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+            torch.cuda.set_device(dev)
+            dist.init_process_group("nccl", device_id=dev)
+        ms = block_bench(dev, args.L, args.steps, args.warmup)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t)
+        if int(os.environ.get("RANK", "0")) == 0:
+            print(json.dumps({"workload": f"cfg5_pairformer_block_L{args.L}", "n_gpus": world, "scaling": "strong",
+                              "ms_fwd_bwd": ms, "tflops": block_flops(args.L) / (ms * 1e-3) / 1e12}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
     else:
         c = {k: v.to(dev) for k, v in workloads.transition(M=args.rows * L).items()}
         fn = lambda: transition_forward(c["x"], c["ln_w"], c["ln_b"], c["w1"], c["w2"])                       # noqa: E731
@@ -383,7 +402,49 @@ def extras(dev, steps=5):
         "fwd_bwd_tflops": 3.0 * f_fwd / ((ms_f + ms_b) * 1e-3) / 1e12,
         "peak_extra_memory_mb_fwd_bwd": peak / 2 ** 20,
         "note": "forward keeps the hidden activation on chip; backward recomputes it (workspace counted in the peak)"}
+    del c, y, mean, rstd
+    torch.cuda.empty_cache()
+    # config 5 on one GPU: the whole block at L = 768
+    ms_blk = block_bench(dev, 768)
+    out["cfg5_pairformer_block_L768_1gpu"] = {
+        "ms_fwd_bwd": ms_blk, "tflops": block_flops(768) / (ms_blk * 1e-3) / 1e12,
+        "note": "fused operators + torch glue (gating, output projections, residuals); rows shard over ranks with --only block"}
     return out
+
+
+def block_flops(Lb):
+    """Algorithmic fwd+bwd FLOPs of the long-crop block: attention 14*N*H*L^2*D, GEMMs 3 * 2*M*K*N."""
+    M = Lb * Lb
+    tri = 14.0 * Lb * 4 * Lb * Lb * 32 + 6.0 * M * 128 * (512 + 4 + 128)
+    single = 14.0 * 16 * Lb * Lb * 24 + 6.0 * M * 128 * 16 + 6.0 * Lb * 384 * (4 * 384 + 384)
+    return 2 * tri + 6.0 * M * 128 * (1024 + 512) + single
+
+
+def block_bench(dev, Lb=768, steps=3, warmup=2, group=None):
+    """BASELINE configuration 5: one Pairformer block (two triangle attentions, pair transition, single attention with
+    pair bias) forward + backward in bf16 on this rank's rows of a [L, L, 128] pair representation (rows sharded
+    over the process group, 5 % padding at the tail).  Returns ms per step (max over ranks is the caller's job)."""
+    from megafold_b200 import row_shard
+    from megafold_b200.pairformer_block import PairformerBlock
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    torch.manual_seed(0)
+    m = PairformerBlock(device=dev, dtype=torch.bfloat16, group=group)
+    g = torch.Generator().manual_seed(1)
+    a, b = row_shard(Lb, rank, world)
+    pair = torch.randn(Lb, Lb, 128, generator=g)[a:b].to(dev, torch.bfloat16).requires_grad_(True)
+    single = torch.randn(Lb, 384, generator=g).to(dev, torch.bfloat16).requires_grad_(True)
+    mask = torch.ones(Lb, dtype=torch.bool, device=dev)
+    mask[Lb - (Lb + 19) // 20:] = False
+    d_pair = torch.randn(b - a, Lb, 128, device=dev, dtype=torch.bfloat16)
+    d_single = torch.randn(Lb, 384, device=dev, dtype=torch.bfloat16)
+
+    def step():
+        for t in (pair, single, *m.parameters()):
+            t.grad = None
+        x, s2 = m(pair, single, mask)
+        torch.autograd.backward([x, s2], [d_pair, d_single])
+    return _time_cuda(step, steps, warmup)
 
 
 class _Null:
@@ -401,8 +462,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--rows", type=int, default=ROWS, help="rows (N) per GPU; smaller values give profiler-sized cases")
-    ap.add_argument("--only", default="all", choices=["all", "fwd", "bwd", "lnl", "lnl_bwd", "transition", "transition_bwd"],
+    ap.add_argument("--only", default="all", choices=["all", "fwd", "bwd", "lnl", "lnl_bwd", "transition", "transition_bwd", "block"],
                     help="run just one kernel family in the timed loop (for ncu captures); prints no JSON line")
+    ap.add_argument("--L", type=int, default=768, help="crop length of --only block")
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary workloads (cfg 3, cfg 4, LayernormLinear)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else max(args.warmup, 1)

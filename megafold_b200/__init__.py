@@ -11,11 +11,12 @@ from .fused_layernorm_linear import (LayernormLinear, LayernormLinearFunction, l
 from .fused_transition import (FusedSwiGLU, FusedSwiGLUFunction, FusedTransition, TransitionFunction,
                                transition_backward, transition_forward)
 from .host_pipeline import evoformer_fwd_bwd_host
+from .pairformer_block import PairformerBlock
 from .sharded import AllReduceGradient, row_shard, sharded_evoformer
 
 __all__ = [
     "EvoformerAttention", "TritonEvoformer", "evo_attention_forward", "evo_attention_backward",
     "LayernormLinear", "LayernormLinearFunction", "FusedSwiGLU", "FusedSwiGLUFunction", "FusedTransition",
     "TransitionFunction", "layernorm_linear_forward", "layernorm_linear_backward", "transition_forward",
-    "transition_backward", "AllReduceGradient", "row_shard", "sharded_evoformer", "evoformer_fwd_bwd_host",
+    "transition_backward", "AllReduceGradient", "row_shard", "sharded_evoformer", "evoformer_fwd_bwd_host", "PairformerBlock",
 ]
