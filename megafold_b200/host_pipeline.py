@@ -5,6 +5,11 @@ off-loaded activation store): the N rows are independent in the forward pass and
 sum that forms d_pair_bias, so the rows are cut into chunks that flow through three CUDA streams - upload of
 chunk i+1, kernels of chunk i, download of chunk i-1 - and PCIe runs in both directions while the GPU computes.
 The results land in pinned host tensors; d_pair_bias is accumulated on the device over the chunks.
+
+A step issues a few hundred copies and launches, which costs the CPU more than the GPU work takes once the chunks
+are small.  So the second call with the same host buffers records the whole three-stream schedule into a CUDA
+graph and every later call replays it (one launch); a call with other buffers, or a failed capture, runs the
+schedule directly.
 """
 from __future__ import annotations
 
@@ -15,19 +20,31 @@ from .evoattention import evo_attention_backward, evo_attention_forward
 __all__ = ["evoformer_fwd_bwd_host", "HostPipeline"]
 
 
+def _row_spans(n_rows, chunks):
+    """Row chunks for the pipeline: about ``chunks`` full-size chunks in the middle, and short ones at both ends,
+    because the first upload and the last compute + download are the only parts that nothing overlaps."""
+    big = -(-n_rows // chunks)
+    ramp = [r for r in (big // 8, big // 4, big // 2) if r >= 1] if n_rows >= 4 * chunks and big >= 8 else []
+    left = n_rows - 2 * sum(ramp)
+    n_mid = -(-left // big)
+    mid = [left // n_mid + (1 if i < left % n_mid else 0) for i in range(n_mid)]
+    sizes = ramp + mid + ramp[::-1]
+    spans, s = [], 0
+    for n in sizes:
+        spans.append((s, s + n))
+        s += n
+    assert s == n_rows
+    return spans
+
+
 class HostPipeline:
     """Reusable state (streams, device staging buffers, pinned outputs) for one problem shape."""
 
-    def __init__(self, shape, dtype, bias_shape, bias_dtype, device, chunks=8):
+    def __init__(self, shape, dtype, bias_shape, bias_dtype, device, chunks=4):
         B, N, L, H, D = shape
         self.shape, self.dtype, self.device = tuple(shape), dtype, torch.device(device)
-        self.chunks = max(1, min(chunks, N))
-        base, extra = divmod(N, self.chunks)
-        self.spans, s = [], 0
-        for i in range(self.chunks):
-            e = s + base + (1 if i < extra else 0)
-            self.spans.append((s, e))
-            s = e
+        self.spans = _row_spans(N, max(1, min(chunks, N)))
+        self.chunks = len(self.spans)
         rows = max(e - s for s, e in self.spans)
         dev = self.device
         self.s_in, self.s_cmp, self.s_out = (torch.cuda.Stream(dev) for _ in range(3))
@@ -39,43 +56,70 @@ class HostPipeline:
         pin = lambda shp, dt: torch.empty(shp, dtype=dt, pin_memory=True)         # noqa: E731
         self.out = dict(o=pin(shape, dtype), dq=pin(shape, dtype), dk=pin(shape, dtype), dv=pin(shape, dtype),
                         d_bias=pin(bias_shape, bias_dtype))
-        self.ev_in = [torch.cuda.Event() for _ in range(2)]
-        self.ev_free = [torch.cuda.Event() for _ in range(2)]
         self.keep = []
+        self.graph, self.graph_key, self.calls, self.use_graph = None, None, 0, True
+        self.s_cap = torch.cuda.Stream(dev)
 
     def run(self, q, k, v, res_mask, pair_bias, d_out):
         """All arguments are pinned host tensors ([B,N,L,H,D], mask [B,N,1,1,L] bool, bias [B,1,H,L,L]).
-        Returns the dict of pinned host results (valid after the call: it synchronises the download stream)."""
-        host = dict(q=q, k=k, v=v, d_out=d_out, mask=res_mask)
+        Returns the dict of pinned host results (valid after the call: it waits for the downloads)."""
+        host = dict(q=q, k=k, v=v, d_out=d_out, mask=res_mask, bias=pair_bias)
+        key = tuple(t.data_ptr() for t in host.values())
         cur = torch.cuda.current_stream(self.device)
+        if self.graph is not None and key == self.graph_key:
+            self.graph.replay()                      # on the current stream
+            cur.synchronize()
+            return self.out
+        self.calls += 1
+        if self.use_graph and self.calls >= 2 and all(t.is_pinned() for t in host.values()):
+            try:
+                self.s_cap.wait_stream(cur)
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=self.s_cap):
+                    self._schedule(host, self.s_cap)
+                self.graph, self.graph_key = g, key
+                cur.wait_stream(self.s_cap)
+                return self.run(q, k, v, res_mask, pair_bias, d_out)
+            except Exception:                        # capture not possible here: keep the direct schedule
+                self.use_graph = False
+                self.graph = None
+                torch.cuda.synchronize(self.device)
+        self._schedule(host, cur)
+        cur.synchronize()
+        return self.out
+
+    def _schedule(self, host, cur):
+        """Enqueue one step: the three streams fork from ``cur`` and join it again at the end."""
         self.s_in.wait_stream(cur)
         self.s_cmp.wait_stream(cur)
         self.s_out.wait_stream(cur)
         with torch.cuda.stream(self.s_in):
-            self.bias.copy_(pair_bias, non_blocking=True)
+            self.bias.copy_(host["bias"], non_blocking=True)
         self.s_cmp.wait_stream(self.s_in)
         with torch.cuda.stream(self.s_cmp):
             self.d_bias.zero_()
         self.keep.clear()
+        ev_free = [None, None]
         for i, (s, e) in enumerate(self.spans):
             slot = i & 1
             n = e - s
             buf = self.dev_in[slot]
             with torch.cuda.stream(self.s_in):
-                if i >= 2:
-                    self.s_in.wait_event(self.ev_free[slot])            # kernels of chunk i-2 are done with this slot
+                if ev_free[slot] is not None:
+                    self.s_in.wait_event(ev_free[slot])                 # kernels of chunk i-2 are done with this slot
                 for name in ("q", "k", "v", "d_out", "mask"):
                     buf[name][:, :n].copy_(host[name][:, s:e], non_blocking=True)
-                self.ev_in[slot].record(self.s_in)
+                ev_in = torch.cuda.Event()
+                ev_in.record(self.s_in)
             with torch.cuda.stream(self.s_cmp):
-                self.s_cmp.wait_event(self.ev_in[slot])
+                self.s_cmp.wait_event(ev_in)
                 qd, kd, vd, gd, md = (buf[x][:, :n] for x in ("q", "k", "v", "d_out", "mask"))
                 o, lse = evo_attention_forward(qd, kd, vd, md, self.bias)
                 dq, dk, dv, db = evo_attention_backward(gd, qd, kd, vd, md, self.bias, o, lse)
                 self.d_bias.add_(db)
-                self.ev_free[slot].record(self.s_cmp)
                 done = torch.cuda.Event()
                 done.record(self.s_cmp)
+                ev_free[slot] = done
             with torch.cuda.stream(self.s_out):
                 self.s_out.wait_event(done)
                 for name, t in (("o", o), ("dq", dq), ("dk", dk), ("dv", dv)):
@@ -84,15 +128,15 @@ class HostPipeline:
         with torch.cuda.stream(self.s_out):
             self.s_out.wait_stream(self.s_cmp)
             self.out["d_bias"].copy_(self.d_bias, non_blocking=True)
-        self.s_out.synchronize()
+        cur.wait_stream(self.s_in)
         cur.wait_stream(self.s_cmp)
-        return self.out
+        cur.wait_stream(self.s_out)
 
 
 _cache = {}
 
 
-def evoformer_fwd_bwd_host(q, k, v, res_mask, pair_bias, d_out, device="cuda", chunks=8):
+def evoformer_fwd_bwd_host(q, k, v, res_mask, pair_bias, d_out, device="cuda", chunks=4):
     """Forward and backward of the pair-biased attention with pinned HOST operands and results.
 
     Returns ``dict(o, dq, dk, dv, d_bias)`` of pinned host tensors; d_bias has ``pair_bias``'s dtype."""

@@ -166,11 +166,21 @@ def _no_bounded_wait_expired():
 
 
 def test_host_pipeline_matches_device_call():
-    """evoformer_fwd_bwd_host (row chunks over three streams) gives what the device-resident operator gives."""
+    """evoformer_fwd_bwd_host (row chunks over three streams; replayed as a CUDA graph from the second call with the
+    same host buffers on) gives what the device-resident operator gives, also after the buffers' contents change."""
     c = make_case(1, 10, 96, 4, 32, seed=21)
     pin = {k: (v.bfloat16() if v.is_floating_point() else v).pin_memory() for k, v in c.items()}
-    out = mfb.evoformer_fwd_bwd_host(pin["q"], pin["k"], pin["v"], pin["mask"], pin["bias"], pin["d_out"], chunks=3)
-    ref = run_gpu(c, dtype=torch.bfloat16)
-    for n, r_ in zip(("o", "dq", "dk", "dv"), ref[:4]):
-        assert torch.equal(out[n], r_.cpu()), n                      # rows are independent: chunking changes nothing
-    assert_close_lowp(out["d_bias"].float(), ref[4].float().cpu(), "d_bias", tol=1e-2)   # summed per chunk, then over chunks
+    for rep in range(4):
+        if rep:
+            fresh = make_case(1, 10, 96, 4, 32, seed=21 + rep)
+            for k in pin:                                                # same pinned buffers, new contents
+                pin[k].copy_(fresh[k].bfloat16() if fresh[k].is_floating_point() else fresh[k])
+            c = fresh
+        out = mfb.evoformer_fwd_bwd_host(pin["q"], pin["k"], pin["v"], pin["mask"], pin["bias"], pin["d_out"], chunks=3)
+        ref = run_gpu(c, dtype=torch.bfloat16)
+        for n, r_ in zip(("o", "dq", "dk", "dv"), ref[:4]):
+            assert torch.equal(out[n], r_.cpu()), (rep, n)               # rows are independent: chunking changes nothing
+        assert_close_lowp(out["d_bias"].float(), ref[4].float().cpu(), f"d_bias (call {rep})", tol=1e-2)   # summed per chunk, then over chunks
+    from megafold_b200 import host_pipeline
+    pipe = next(iter(host_pipeline._cache.values()))
+    assert pipe.graph is not None, "the three-stream schedule was not captured into a CUDA graph"
