@@ -3,17 +3,18 @@
 // The operator is bound by HBM traffic (K = 128 gives 64-140 FLOP per byte), so the kernel is organised around
 // touching X and Y exactly once with full-line accesses; the tensor pipe has slack.
 //
-// Persistent CTA per SM, 128-row tiles of X:
-//   warps 0-7   workers.  Prologue: a warp normalises 16 rows - coalesced 8-byte loads of X, two-pass mean /
-//               variance with warp shuffles in fp32, gain and shift, 16-bit result written straight into the
-//               K-major, 128B-swizzled A tile in shared memory (double buffered); mean and rstd go to global memory
-//               for the backward pass.  Epilogue: thread (row, column half) reads 64 accumulator columns from
-//               TMEM, adds the linear bias, packs to 16 bit and writes a swizzled staging tile that one thread
-//               hands to a TMA store (full 128-byte lines, clipped at the edges of Y).
-//   warp 8      tcgen05.mma issuer: per 128-column tile of W, K/16 MMAs (M = 128, N = 128) into one of two TMEM
+// Persistent CTA per SM, 128-row tiles of X, four warpgroups with fixed roles:
+//   warps 8-11  normalise.  The raw rows of X arrive by TMA in the layout the MMA wants (ring of three tiles); a
+//               thread owns one row: two-pass mean / variance in fp32, gain and shift, 16-bit result written back
+//               over the raw row; mean and rstd go to global memory for the backward pass.  These warps run
+//               ahead of the MMAs as far as the ring allows.
+//   warps 0-7   epilogue.  Thread (row, column half) reads 64 accumulator columns from TMEM, adds the linear bias,
+//               packs to 16 bit and writes a swizzled staging tile that one thread hands to a TMA store (full
+//               128-byte lines, clipped at the edges of Y).
+//   warp 12     tcgen05.mma issuer: per 128-column tile of W, K/16 MMAs (M = 128, N = 128) into one of two TMEM
 //               accumulators, so the epilogue of one tile overlaps the MMAs of the next.
-//   warp 9      TMA producer of W tiles ([K rows][64 columns] boxes, MN-major B operand), re-streamed from L2
-//               for every row tile.
+//   warp 13     TMA producer of X tiles and W tiles ([K rows][64 columns] boxes, MN-major B operand; W is
+//               re-streamed from L2 for every row tile).
 // Every wait is bounded; on expiry the CTA raises a flag, drains and reports through mf_async_status().
 #include <type_traits>
 
@@ -26,7 +27,8 @@ using namespace tcx;
 constexpr int kRows = 128;          // rows of X per tile = TMEM lanes
 constexpr int kNT = 128;            // output columns per MMA group
 constexpr int kWorkers = 256;
-constexpr int kThreads = kWorkers + 128;
+constexpr int kNormWarps = 4;         // warps 8-11 normalise rows; warp 12 issues MMAs, warp 13 TMA loads
+constexpr int kThreads = 512;          // four warpgroups: two of epilogue warps, one of normalising warps, one of issuers
 constexpr int kWStages = 2;
 constexpr int kAStages = 3;         // X tiles in flight (TMA prefetch two tiles ahead)
 
@@ -85,23 +87,26 @@ lnl_fwd_tc_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant_
     mbar_fence_init();
     prefetch_tmap(&mw); prefetch_tmap(&my); prefetch_tmap(&mx);
   }
+  for (int k = tid; k < K; k += kThreads) {
+    gam_s[k] = to_f(static_cast<const T*>(p.gamma)[k]);
+    bet_s[k] = p.beta ? to_f(static_cast<const T*>(p.beta)[k]) : 0.f;
+  }
   if (warp == 0) { tmem_alloc(&tmem_base_s, 256); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   volatile int* abort_flag = &abort_s;
   const uint32_t tm0 = tmem_base_s;
+  // Register re-partition (the CTA is launched with 128 per thread): the issuer warpgroup keeps 40, the epilogue
+  // warpgroups get 152 and the normalising warpgroup 168; 256 * 152 + 128 * 168 + 128 * 40 = 512 * 128 exactly.
+  static_assert(256 * 152 + 128 * 168 + 128 * 40 <= kThreads * 128, "setmaxnreg budget");
+  // (each setmaxnreg sits inside its role's branch: the compiler allocates registers per region)
   const int my_tiles = p.n_mt > (int)blockIdx.x ? (p.n_mt - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
 
-  if (warp < 8) {
-    // ------------------------------------------------------------------------------------ workers
-    const T* x = static_cast<const T*>(p.x);
-    for (int k = tid; k < K; k += kWorkers) {
-      gam_s[k] = to_f(static_cast<const T*>(p.gamma)[k]);
-      bet_s[k] = p.beta ? to_f(static_cast<const T*>(p.beta)[k]) : 0.f;
-    }
-    named_sync(2, kWorkers);
-    const int row_l = (warp & 3) * 32 + lane;        // epilogue: my TMEM lane
+  if (warp < 8 + kNormWarps) {
+    // ------------------------------------------------------------------------------------ epilogue warps 0-7,
+    // normalising warps 8-11
+    const int row_l = (warp & 3) * 32 + lane;        // my row of the tile (= my TMEM lane in the epilogue)
     const int half = warp >> 2;                      // epilogue: my 64-column half of the 128-column tile
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
     uint32_t acc_cnt = 0;                            // accumulator tiles consumed (buffer = acc_cnt & 1)
@@ -157,10 +162,14 @@ lnl_fwd_tc_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant_
       if (lane == 0) mbar_arrive(&bar.a_full[buf]);
     };
 
+    if (warp >= 8) {
+      // the normalising warps run ahead of the MMAs as far as the ring of X tiles allows
+      asm volatile("setmaxnreg.inc.sync.aligned.u32 168;");
+      for (int t = 0; t < my_tiles && !*abort_flag; ++t) normalise(t);
+    } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 152;");
     bool dead = false;
-    if (warp < 4 && my_tiles > 0) normalise(0);
     for (int t = 0; t < my_tiles && !dead; ++t) {
-      if (warp < 4 && t + 1 < my_tiles) normalise(t + 1);      // next tile's A: its MMAs overlap this tile's epilogue
       const int64_t row0 = ((int64_t)blockIdx.x + (int64_t)t * gridDim.x) * kRows;
       for (int nt = 0; nt < p.n_nt; ++nt, ++acc_cnt) {
         const int ab = acc_cnt & 1;
@@ -213,7 +222,10 @@ lnl_fwd_tc_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant_
       }
     }
     if (tid == 0) bulk_wait_group<0>();
-  } else if (warp == 8 && lane == 0) {
+    }
+  } else {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+  if (warp == 8 + kNormWarps && lane == 0) {
     // ------------------------------------------------------------------------------------ MMA issuer
     const uint32_t idesc = idesc_f16(128, kNT, p.ab_fmt, 0, 1);     // A K-major, B MN-major
     uint32_t acc_cnt = 0, w_cnt = 0;
@@ -237,8 +249,8 @@ lnl_fwd_tc_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant_
       }
       tc_commit(&bar.a_empty[buf]);
     }
-  } else if (warp == 9 && lane == 0) {
-    // ------------------------------------------------------------------------------------ TMA producer of W tiles
+  } else if (warp == 9 + kNormWarps && lane == 0) {
+    // ------------------------------------------------------------------------------------ TMA producer of X and W tiles
     uint32_t w_cnt = 0;
     auto load_x = [&](int t_local) {
       const int buf = t_local % kAStages;
@@ -261,6 +273,7 @@ lnl_fwd_tc_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant_
         tma_load_2d(sW + ws * W_BYTES + K * 128, &mw, &bar.w_full[ws], nt * kNT + 64, 0);
       }
     }
+  }
   }
 
   tc_fence_before();
