@@ -6,7 +6,8 @@
 //   TMA warp     X tile (raw rows, K-major, 128B swizzle) two tiles ahead; per chunk the two W1 column blocks
 //                (value half and gate half, [dim rows][64 columns], MN-major B operands) and the W2 block
 //                ([dim rows][64 hidden], K-major B operand).
-//   row threads  (warps 0-3) LayerNorm of the next tile in place in shared memory, as in the LayernormLinear kernel.
+//   row threads  (warps 8-11, a warpgroup of their own) LayerNorm of the next tile in place in shared memory, as in
+//                the LayernormLinear kernel, ahead of the MMAs by as much as the ring of X tiles allows.
 //   MMA thread   GEMM1 of chunk c: H_a, H_g = A W1 blocks (2 x dim/16 MMAs, N = 64) into one of two TMEM buffers;
 //                GEMM2 of chunk c-1: Y += G W2-block^T (4 MMAs, N = dim) once the workers have written G.
 //   workers      (warps 0-7) thread (row, half): 32 columns of H_a and H_g from TMEM, g = silu(gate) * value with
@@ -26,7 +27,7 @@ using namespace tcx;
 constexpr int kRows = 128;
 constexpr int kHC = 64;             // hidden columns per chunk
 constexpr int kWorkers = 256;
-constexpr int kThreads = kWorkers + 128;
+constexpr int kThreads = 512;          // warpgroups: 0-1 SwiGLU / output workers, 2 normalising warps, 3 issuers (warp 12 MMA, warp 13 TMA)
 constexpr int kAStages = 2;
 constexpr int kWStages = 2;
 
@@ -101,6 +102,10 @@ transition_fwd_tc_kernel(const __grid_constant__ CUtensorMap mx, const __grid_co
     mbar_fence_init();
     prefetch_tmap(&mx); prefetch_tmap(&mw1); prefetch_tmap(&mw2); prefetch_tmap(&my);
   }
+  for (int k = tid; k < K; k += kThreads) {
+    gam_s[k] = p.has_ln ? to_f(static_cast<const T*>(p.gamma)[k]) : 1.f;
+    bet_s[k] = (p.has_ln && p.beta) ? to_f(static_cast<const T*>(p.beta)[k]) : 0.f;
+  }
   if (warp == 0) { tmem_alloc(&tmem_base_s, 512); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
@@ -111,13 +116,12 @@ transition_fwd_tc_kernel(const __grid_constant__ CUtensorMap mx, const __grid_co
   const int my_tiles = p.n_mt > (int)blockIdx.x ? (p.n_mt - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
   const int nch = p.n_ch;
 
-  if (warp < 8) {
-    // ------------------------------------------------------------------------------------ workers
-    for (int k = tid; k < K; k += kWorkers) {
-      gam_s[k] = p.has_ln ? to_f(static_cast<const T*>(p.gamma)[k]) : 1.f;
-      bet_s[k] = (p.has_ln && p.beta) ? to_f(static_cast<const T*>(p.beta)[k]) : 0.f;
-    }
-    named_sync(2, kWorkers);
+  // Register re-partition (launched with 128 per thread): issuers keep 40, workers get 152, the normalising
+  // warpgroup 168; 256 * 152 + 128 * 168 + 128 * 40 = 512 * 128.  Each setmaxnreg sits inside its role's branch.
+  static_assert(256 * 152 + 128 * 168 + 128 * 40 <= kThreads * 128, "setmaxnreg budget");
+  if (warp < 12) {
+    // ------------------------------------------------------------------------------------ workers (warps 0-7),
+    // normalising warps (8-11)
     const int row_l = (warp & 3) * 32 + lane;
     const int half = warp >> 2;
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
@@ -173,10 +177,14 @@ transition_fwd_tc_kernel(const __grid_constant__ CUtensorMap mx, const __grid_co
       if (lane == 0) mbar_arrive(&bar.a_full[buf]);
     };
 
+    if (warp >= 8) {
+      // the normalising warps run ahead of the MMAs as far as the ring of X tiles allows
+      asm volatile("setmaxnreg.inc.sync.aligned.u32 168;");
+      for (int t = 0; t < my_tiles && !*abort_flag; ++t) normalise(t);
+    } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 152;");
     bool dead = false;
-    if (warp < 4 && my_tiles > 0) normalise(0);
     for (int t = 0; t < my_tiles && !dead; ++t) {
-      if (warp < 4 && t + 1 < my_tiles) normalise(t + 1);
       const int row0 = (int)(((int64_t)blockIdx.x + (int64_t)t * gridDim.x) * kRows);
       for (int c = 0; c < nch; ++c, ++ch_cnt) {
         const int hb = ch_cnt & 1;
@@ -240,7 +248,10 @@ transition_fwd_tc_kernel(const __grid_constant__ CUtensorMap mx, const __grid_co
       }
     }
     if (tid == 0) bulk_wait_group<0>();
-  } else if (warp == 8 && lane == 0) {
+    }
+  } else {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+  if (warp == 12 && lane == 0) {
     // ------------------------------------------------------------------------------------ MMA issuer
     const uint32_t id1 = idesc_f16(128, kHC, p.ab_fmt, 0, 1);     // GEMM1: A K-major, B (W1 block) MN-major, N = 64
     const uint32_t id2 = idesc_f16(128, K, p.ab_fmt, 0, 0);       // GEMM2: A (G) K-major, B (W2 block) K-major, N = dim
@@ -287,7 +298,7 @@ transition_fwd_tc_kernel(const __grid_constant__ CUtensorMap mx, const __grid_co
       tc_commit(&bar.y_full);
       tc_commit(&bar.a_empty[buf]);
     }
-  } else if (warp == 9 && lane == 0) {
+  } else if (warp == 13 && lane == 0) {
     // ------------------------------------------------------------------------------------ TMA producer
     uint32_t ch_cnt = 0;
     auto load_x = [&](int t_local) {
@@ -317,6 +328,7 @@ transition_fwd_tc_kernel(const __grid_constant__ CUtensorMap mx, const __grid_co
         tma_load_2d(w + 2 * W1B, &mw2, &bar.w2_full[ws], c * kHC, 0);          // W2[:, chunk]
       }
     }
+  }
   }
 
   tc_fence_before();
