@@ -44,6 +44,8 @@ template <int DP> struct Cfg {
 struct BwdP {
   int B, N, L, H, D;
   int n_t, n_items, lpad;
+  int ksplit;            // work items per (b, n, h): the key tiles are split into this many ranges
+  float* dq_acc;         // fp32 [B,N,L,H,D] accumulator of dQ when ksplit > 1
   float c1, scale, inv_L;
   uint32_t ab_fmt;
   const void* bias; int64_t bs[4];
@@ -289,14 +291,18 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
   static_assert(kComputeWarps * 32 * 112 + 128 * 32 <= kThreads * 96, "setmaxnreg budget");
   asm volatile("setmaxnreg.inc.sync.aligned.u32 112;");
   for (int item = blockIdx.x; item < p.n_items && !dead; item += gridDim.x) {
-    const int h = item % p.H, bn = item / p.H, n = bn % p.N, b = bn / p.N;
+    // work item = (b, n, h, range of key tiles); with one range per (b, n, h) the dQ rows are complete at the end of
+    // the item, otherwise they are partial sums that go to an fp32 accumulator
+    const int bnh = item / p.ksplit, sp = item - bnh * p.ksplit;
+    const int jt0 = sp * nt / p.ksplit, jt1 = (sp + 1) * nt / p.ksplit;
+    const int h = bnh % p.H, bn = bnh / p.H, n = bn % p.N, b = bn / p.N;
     // ---- per-item statistics (lse in base 2, delta; queries beyond L get lse = +inf so that P = 0) live in two
     // buffers: the current item's were stored while the previous item was running.  One CTA-wide rendezvous per item
     // (bounded mbarrier wait, one arrival per warp): everybody has left the previous item, so the other buffer may be
     // refilled, and everybody's earlier stores to this buffer are visible.
     auto load_stats = [&](int item2, int buf, int stamp) {
       if (item2 >= p.n_items) return;
-      const int64_t row2 = (int64_t)item2 / p.H * p.H * p.L + (int64_t)(item2 % p.H) * p.L;   // ((b*N+n)*H + h) * L
+      const int64_t row2 = (int64_t)(item2 / p.ksplit) * p.L;   // ((b*N+n)*H + h) * L
       for (int i = tid; i < p.lpad; i += kComputeWarps * 32) {
         float l2 = INFINITY, dl = 0.f;
         if (i < p.L) {
@@ -324,7 +330,7 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
     ++item_no;
     float mask2_next = -INFINITY;
     {
-      const int j0r = r;
+      const int j0r = jt0 * kT + r;
       if (j0r < p.L) {
         const int64_t mi = b * p.ms[0] + n * p.ms[1] + (int64_t)j0r * p.ms[2];
         mask2_next = p.mask_dtype == MF_U8 ? (static_cast<const uint8_t*>(p.mask)[mi] ? 0.f : -FLT_MAX)
@@ -332,11 +338,11 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
       }
     }
 
-    for (int jt = 0; jt < nt && !dead; ++jt) {
+    for (int jt = jt0; jt < jt1 && !dead; ++jt) {
       const int j = jt * kT + r;
       const bool j_ok = j < p.L;
       const float mask2 = mask2_next;          // fetched one key tile ahead
-      if (jt + 1 < nt) {
+      if (jt + 1 < jt1) {
         const int jn = (jt + 1) * kT + r;
         mask2_next = -INFINITY;
         if (jn < p.L) {
@@ -450,7 +456,15 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
 #pragma unroll
       for (int cb = 0; cb < DP / 32; ++cb) tmem_ld32(tDQ + it * DP + lane_addr + cb * 32, *reinterpret_cast<uint32_t (*)[32]>(o32 + cb * 32));
       tmem_ld_wait();
-      if (i < p.L && !*abort_flag) {
+      if (i < p.L && !*abort_flag && p.ksplit > 1) {
+        float* arow = p.dq_acc + ((((int64_t)b * p.N + n) * p.L + i) * p.H + h) * p.D;
+#pragma unroll
+        for (int d4 = 0; d4 < DP / 4; ++d4)
+          if (d4 * 4 < p.D)
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(arow + d4 * 4),
+                         "f"(__uint_as_float(o32[d4 * 4]) * p.scale), "f"(__uint_as_float(o32[d4 * 4 + 1]) * p.scale),
+                         "f"(__uint_as_float(o32[d4 * 4 + 2]) * p.scale), "f"(__uint_as_float(o32[d4 * 4 + 3]) * p.scale) : "memory");
+      } else if (i < p.L && !*abort_flag) {
         T* orow = static_cast<T*>(p.dq) + ((((int64_t)b * p.N + n) * p.L + i) * p.H + h) * p.D;
 #pragma unroll
         for (int d8 = 0; d8 < DP / 8; ++d8) {
@@ -476,7 +490,8 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
     // accumulations of each block, as soon as its P^T / dS^T tiles have been written
     uint32_t g = 0, kv = 0;
     for (int item = blockIdx.x; item < p.n_items && !*abort_flag; item += gridDim.x) {
-      for (int jt = 0; jt < nt && !*abort_flag; ++jt) {
+      const int sp = item % p.ksplit, jt0 = sp * nt / p.ksplit, jt1 = (sp + 1) * nt / p.ksplit;
+      for (int jt = jt0; jt < jt1 && !*abort_flag; ++jt) {
         for (int it = 0; it < nt; ++it, ++g) {
           MF_TL(43);
           wait_or_flag(&bar.written, g & 1, abort_flag);
@@ -496,7 +511,7 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks)      // dQ_i += dS K_j   (A = dS^T tile read MN-major: M = queries)
             mma_ss(tDQ + it * DP, smem_desc(smem_u32(sDS) + ks * 2048, 16384, 1024, kSw128),
-                   smem_desc(kvb + ks * 16 * C::ROWB, 16, C::SBO, C::SW), id_q, jt > 0 || ks > 0);
+                   smem_desc(kvb + ks * 16 * C::ROWB, 16, C::SBO, C::SW), id_q, jt > jt0 || ks > 0);
           MF_TL(45);
           tc_commit(&bar.acc_done);
           // the stages are also read by this block's score MMAs, which completed before its tiles were written
@@ -515,10 +530,11 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
     if (!*abort_flag) issue_scores(0, 0);
     for (int item = blockIdx.x; item < p.n_items && !*abort_flag; item += gridDim.x) {
       const bool last_item = item + (int)gridDim.x >= p.n_items;
-      for (int jt = 0; jt < nt && !*abort_flag; ++jt) {
+      const int sp = item % p.ksplit, jt0 = sp * nt / p.ksplit, jt1 = (sp + 1) * nt / p.ksplit;
+      for (int jt = jt0; jt < jt1 && !*abort_flag; ++jt) {
         for (int it = 0; it < nt; ++it, ++g) {
           const bool new_j = (it == nt - 1);
-          if (last_item && (jt == nt - 1) && new_j) break;
+          if (last_item && (jt == jt1 - 1) && new_j) break;
           wait_or_flag(&bar.loaded, g & 1, abort_flag);
           const uint32_t kc = new_j ? kv + 1 : kv;
           if (new_j) wait_or_flag(&bar.kv_full[kc & 1], (kc >> 1) & 1, abort_flag);
@@ -534,8 +550,10 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
     // ---------------------------------------------------------------- TMA producer, in order of need
     uint32_t g = 0, kv = 0;
     for (int item = blockIdx.x; item < p.n_items && !*abort_flag; item += gridDim.x) {
-      const int h = item % p.H, bn = item / p.H, n = bn % p.N, b = bn / p.N;
-      for (int jt = 0; jt < nt && !*abort_flag; ++jt) {
+      const int bnh = item / p.ksplit, sp = item - bnh * p.ksplit;
+      const int jt0 = sp * nt / p.ksplit, jt1 = (sp + 1) * nt / p.ksplit;
+      const int h = bnh % p.H, bn = bnh / p.H, n = bn % p.N, b = bn / p.N;
+      for (int jt = jt0; jt < jt1 && !*abort_flag; ++jt) {
         if (kv >= 2) wait_or_flag(&bar.kv_empty[kv & 1], ((kv >> 1) - 1) & 1, abort_flag);
         if (*abort_flag) break;
         load_kv(kv, jt, h, n, b);
@@ -555,6 +573,22 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
   if (warp == 0) tmem_dealloc(tmem_base_s, 512);
 }
 
+// With few (b, n, h) triples (single-representation attention: N = 1) the key tiles of each are spread over several
+// CTAs so that the whole GPU works; the partial dQ rows then meet in an fp32 accumulator.  B200: 148 SMs.
+int bwd_ksplit(int64_t bnh, int nt) {
+  const int64_t sms = 148;
+  if (bnh >= sms || nt < 2) return 1;
+  int64_t k = sms / bnh;                 // as many ranges as keep every CTA at one work item
+  if (k > nt) k = nt;
+  return k < 1 ? 1 : (int)k;
+}
+
+template <typename T>
+__global__ void cast_scaled_rows_kernel(const float* __restrict__ src, T* __restrict__ dst, int64_t n) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) dst[i] = from_f<T>(src[i]);
+}
+
 template <int DP, typename T, typename TB>
 int launch_bwd(const mf_evo_bwd_args& a, cudaStream_t st) {
   using C = Cfg<DP>;
@@ -568,7 +602,8 @@ int launch_bwd(const mf_evo_bwd_args& a, cudaStream_t st) {
   BwdP p{};
   p.B = a.B; p.N = a.N; p.L = a.L; p.H = a.H; p.D = a.D;
   p.n_t = (a.L + kT - 1) / kT;
-  p.n_items = a.B * a.N * a.H;
+  p.ksplit = bwd_ksplit((int64_t)a.B * a.N * a.H, (a.L + kT - 1) / kT);
+  p.n_items = a.B * a.N * a.H * p.ksplit;
   p.lpad = p.n_t * kT;
   p.scale = 1.0f / sqrtf((float)a.D);
   p.c1 = kLog2e * p.scale;
@@ -600,7 +635,11 @@ int launch_bwd(const mf_evo_bwd_args& a, cudaStream_t st) {
     const int box[4] = {32, 16, 1, 1};
     if ((r = make_tiled_map(&mdb, dbias, MF_F32, 4, dims, str, box, 0))) return r;
   }
-  TB* biasT = reinterpret_cast<TB*>(static_cast<char*>(a.workspace) + delta_bytes + acc_bytes);
+  const int64_t n_dq = (int64_t)a.B * a.N * a.L * a.H * a.D;
+  const size_t dq_bytes = p.ksplit > 1 ? align_up(sizeof(float) * (size_t)n_dq, 256) : 0;
+  p.dq_acc = reinterpret_cast<float*>(static_cast<char*>(a.workspace) + delta_bytes + acc_bytes);
+  if (p.ksplit > 1) MF_CUDA(cudaMemsetAsync(p.dq_acc, 0, sizeof(float) * (size_t)n_dq, st));
+  TB* biasT = reinterpret_cast<TB*>(static_cast<char*>(a.workspace) + delta_bytes + acc_bytes + dq_bytes);
   p.biasT_ = biasT;
   {
     MF_CUDA(cudaMemsetAsync(biasT, 0, sizeof(TB) * (size_t)a.B * a.H * a.L * p.lpad, st));
@@ -621,6 +660,10 @@ int launch_bwd(const mf_evo_bwd_args& a, cudaStream_t st) {
   if (grid > p.n_items) grid = p.n_items;
   kern<<<grid, kThreads, smem, st>>>(mq, mk, mv, mg, mdb, p);
   MF_LAUNCHED("evo_bwd_tc_kernel");
+  if (p.ksplit > 1) {
+    cast_scaled_rows_kernel<T><<<(unsigned)((n_dq + 255) / 256), 256, 0, st>>>(p.dq_acc, static_cast<T*>(a.dq), n_dq);
+    MF_LAUNCHED("cast_scaled_rows_kernel");
+  }
   if (!direct) {
     const int64_t rows_b = (int64_t)a.B * a.H * a.L, n_out = rows_b * a.L;
     if (a.dbias_dtype == MF_F32)
@@ -649,6 +692,8 @@ size_t evo_bwd_tc_workspace(const mf_evo_bwd_args& a) {
   const size_t lp4 = (size_t)(a.L + 3) / 4 * 4;
   if (!(a.dbias_dtype == MF_F32 && lp4 == (size_t)a.L)) b += align_up(sizeof(float) * (size_t)a.B * a.H * a.L * lp4, 256);
   const size_t lpad = (size_t)((a.L + kT - 1) / kT) * kT;
+  if (bwd_ksplit((int64_t)a.B * a.N * a.H, (a.L + kT - 1) / kT) > 1)
+    b += align_up(sizeof(float) * (size_t)a.B * a.N * a.L * a.H * a.D, 256);         // fp32 dQ accumulator
   b += align_up(dtype_size(a.bias_dtype) * (size_t)a.B * a.H * a.L * lpad, 256);     // transposed bias copy
   return b;
 }
