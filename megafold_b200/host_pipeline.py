@@ -57,13 +57,18 @@ class HostPipeline:
         self.out = dict(o=pin(shape, dtype), dq=pin(shape, dtype), dk=pin(shape, dtype), dv=pin(shape, dtype),
                         d_bias=pin(bias_shape, bias_dtype))
         self.keep = []
-        self.graph, self.graph_key, self.calls, self.use_graph = None, None, 0, True
+        self.graph, self.graph_key, self.calls, self.use_graph, self.group = None, None, 0, True, None
         self.s_cap = torch.cuda.Stream(dev)
 
-    def run(self, q, k, v, res_mask, pair_bias, d_out):
+    def run(self, q, k, v, res_mask, pair_bias, d_out, group=None):
         """All arguments are pinned host tensors ([B,N,L,H,D], mask [B,N,1,1,L] bool, bias [B,1,H,L,L]).
-        Returns the dict of pinned host results (valid after the call: it waits for the downloads)."""
+        Returns the dict of pinned host results (valid after the call: it waits for the downloads).
+        With ``group`` the tensors hold this rank's rows and d_pair_bias is all-reduced over the group on the device
+        before it is downloaded (the schedule is then issued directly, not replayed from a graph)."""
         host = dict(q=q, k=k, v=v, d_out=d_out, mask=res_mask, bias=pair_bias)
+        self.group = group
+        if group is not None:
+            self.use_graph = False
         key = tuple(t.data_ptr() for t in host.values())
         cur = torch.cuda.current_stream(self.device)
         if self.graph is not None and key == self.graph_key:
@@ -125,6 +130,10 @@ class HostPipeline:
                 for name, t in (("o", o), ("dq", dq), ("dk", dk), ("dv", dv)):
                     self.out[name][:, s:e].copy_(t, non_blocking=True)
             self.keep.append((o, dq, dk, dv, db, lse))                  # keep alive until the copies have run
+        if self.group is not None:
+            import torch.distributed as dist
+            with torch.cuda.stream(self.s_cmp):
+                dist.all_reduce(self.d_bias, group=self.group)
         with torch.cuda.stream(self.s_out):
             self.s_out.wait_stream(self.s_cmp)
             self.out["d_bias"].copy_(self.d_bias, non_blocking=True)
@@ -136,10 +145,11 @@ class HostPipeline:
 _cache = {}
 
 
-def evoformer_fwd_bwd_host(q, k, v, res_mask, pair_bias, d_out, device="cuda", chunks=4):
+def evoformer_fwd_bwd_host(q, k, v, res_mask, pair_bias, d_out, device="cuda", chunks=4, group=None):
     """Forward and backward of the pair-biased attention with pinned HOST operands and results.
 
-    Returns ``dict(o, dq, dk, dv, d_bias)`` of pinned host tensors; d_bias has ``pair_bias``'s dtype."""
+    Returns ``dict(o, dq, dk, dv, d_bias)`` of pinned host tensors; d_bias has ``pair_bias``'s dtype.  ``group``: a
+    process group over which the rows are sharded (each rank passes its own rows; d_bias comes back summed)."""
     for t in (q, k, v, d_out, res_mask, pair_bias):
         if t.is_cuda:
             raise ValueError("evoformer_fwd_bwd_host takes host tensors; use TritonEvoformer for device tensors")
@@ -151,4 +161,4 @@ def evoformer_fwd_bwd_host(q, k, v, res_mask, pair_bias, d_out, device="cuda", c
     if pipe is None:
         _cache.clear()
         pipe = _cache[key] = HostPipeline(q.shape, q.dtype, pair_bias.shape, pair_bias.dtype, dev, chunks)
-    return pipe.run(q, k, v, res_mask, pair_bias, d_out)
+    return pipe.run(q, k, v, res_mask, pair_bias, d_out, group)
