@@ -9,8 +9,9 @@
 //               over the raw row; mean and rstd go to global memory for the backward pass.  These warps run
 //               ahead of the MMAs as far as the ring allows.
 //   warps 0-7   epilogue.  Thread (row, column half) reads 64 accumulator columns from TMEM, adds the linear bias,
-//               packs to 16 bit and writes a swizzled staging tile that one thread hands to a TMA store (full
-//               128-byte lines, clipped at the edges of Y).
+//               packs to 16 bit and writes a swizzled staging slab ([32 rows][64 columns] per warp) that the warp's
+//               lane 0 hands to a TMA store (full 128-byte lines, clipped at the edges of Y); no barrier between
+//               the epilogue warps.
 //   warp 12     tcgen05.mma issuer: per 128-column tile of W, K/16 MMAs (M = 128, N = 128) into one of two TMEM
 //               accumulators, so the epilogue of one tile overlaps the MMAs of the next.
 //   warp 13     TMA producer of X tiles and W tiles ([K rows][64 columns] boxes, MN-major B operand; W is
@@ -183,11 +184,11 @@ lnl_fwd_tc_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant_
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bar.acc_empty[ab]);
-        // staging buffer `ab` was handed to a TMA store two tiles ago: make sure it has been read
+        // Every warp stages and stores its own [32 rows][64 columns] slab, so the epilogue warps never wait for each
+        // other.  Slab `ab` was handed to a TMA store by this warp two tiles ago: make sure it has been read.
         uint8_t* ys = sY + ab * Y_BYTES + half * (kRows * 128);
-        if (tid == 0) bulk_wait_group_read<1>();
-        // group barrier that also agrees on giving up (a bounded wait expired somewhere in the CTA)
-        if (named_sync_or(2, kWorkers, *abort_flag)) { dead = true; break; }
+        if (lane == 0) bulk_wait_group_read<1>();
+        if (__any_sync(0xffffffffu, *abort_flag)) { dead = true; break; }
         const T* bias = static_cast<const T*>(p.bias);
         const bool bias_vec = bias && (n0 + 64 <= p.N) && ((reinterpret_cast<uintptr_t>(bias) & 15) == 0);
 #pragma unroll
@@ -212,16 +213,15 @@ lnl_fwd_tc_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant_
           *reinterpret_cast<uint4*>(ys + swz_offset(row_l, ch, 128)) = v;
         }
         fence_async_smem();
-        named_sync(2, kWorkers);
-        if (tid == 0) {
-          // two [64 columns][128 rows] boxes; TMA clips rows >= M and columns >= N
-          tma_store_2d(&my, sY + ab * Y_BYTES, nt * kNT, (int)row0);
-          if (nt * kNT + 64 < p.N) tma_store_2d(&my, sY + ab * Y_BYTES + kRows * 128, nt * kNT + 64, (int)row0);
+        __syncwarp();
+        if (lane == 0) {
+          // [64 columns][32 rows] box; TMA clips rows >= M and columns >= N (a slab wholly beyond N is skipped)
+          if (n0 < p.N) tma_store_2d(&my, ys + (warp & 3) * (32 * 128), n0, (int)row0 + (warp & 3) * 32);
           bulk_commit_group();
         }
       }
     }
-    if (tid == 0) bulk_wait_group<0>();
+    if (lane == 0) bulk_wait_group<0>();
     }
   } else {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
@@ -298,7 +298,7 @@ int launch_lnl(const mf_lnl_fwd_args& a, cudaStream_t st) {
   }
   {
     const int64_t dims[2] = {a.N, a.M}, str[2] = {1, a.N};
-    const int box[2] = {64, kRows};
+    const int box[2] = {64, 32};                 // one epilogue warp's slab
     if ((r = make_tiled_map(&my, a.y, a.dtype, 2, dims, str, box, 128))) return r;
   }
   LnlP p{};
