@@ -138,6 +138,9 @@ int lnl_fwd_tc(const mf_lnl_fwd_args& a, cudaStream_t st);
 int lnl_bwd_simt(const mf_lnl_bwd_args& a, cudaStream_t st);   // picks tensor-core GEMMs when lnl_bwd_runs_on_tc
 bool lnl_bwd_runs_on_tc(const mf_lnl_bwd_args& a);
 bool transition_bwd_runs_on_tc(const mf_transition_bwd_args& a);
+bool transition_bwd_fused_ok(const mf_transition_bwd_args& a);
+int transition_bwd_fused(const mf_transition_bwd_args& a, void* g, void* dh, float* dyln, cudaStream_t st);
+int unpermute_dw1(const float* src, float* dst, int dim, int inner, cudaStream_t st);
 size_t lnl_bwd_simt_workspace(const mf_lnl_bwd_args& a);
 
 int transition_fwd_simt(const mf_transition_fwd_args& a, cudaStream_t st);

@@ -8,8 +8,8 @@
 //
 // Persistent CTAs walk work items (128 x 128 output tile, slice of the reduction).  A 4-stage TMA ring feeds
 // 64-deep slabs of A and B (128B-swizzled boxes), one thread issues 4 tcgen05.mma (M = N = 128, K = 16) per slab
-// into one of two TMEM accumulators, and four epilogue warps move finished tiles TMEM -> registers -> swizzled
-// staging -> TMA store (16-bit or fp32) or TMA add-reduction (fp32, when the reduction is split over CTAs; the
+// into one of two TMEM accumulators, and four epilogue warps move finished tiles (each its own 32 rows) TMEM ->
+// registers -> swizzled staging -> TMA store (16-bit or fp32) or TMA add-reduction (fp32, when the reduction is split over CTAs; the
 // output must then be zero on entry).  All waits are bounded.
 #include "evo_tc_common.cuh"
 #include "gemm_tc.cuh"
@@ -25,7 +25,7 @@ constexpr int kStageBytes = 2 * 128 * 128;       // A slab 16 KB + B slab 16 KB
 
 struct GemmP {
   int m_tiles, n_tiles, k_splits, slabs_total, slabs_per_split;
-  int n_cols;
+  int n_cols; int64_t n_rows;
   int a_mn, b_mn, out_kind;     // out_kind: 0 = 16-bit store, 1 = fp32 store, 2 = fp32 add-reduction
   uint32_t ab_fmt;
   int* status;
@@ -142,8 +142,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap ma, const __grid_constant__ C
       const int ab = acc_cnt & 1;
       wait_or_flag(&bar.acc_full[ab], (acc_cnt >> 1) & 1, abort_flag);
       tc_fence_after();
-      if (tid == 128) bulk_wait_group_read<0>();            // the staging buffer is free again
-      if (named_sync_or(3, 128, *abort_flag)) break;
+      // every epilogue warp stages and stores its own 32-row slab: no barrier between them
+      if (lane == 0) bulk_wait_group_read<0>();             // my slab has been read by my previous store
+      if (__any_sync(0xffffffffu, *abort_flag)) break;
 #pragma unroll
       for (int cb = 0; cb < 4; ++cb) {
         uint32_t v[32];
@@ -171,23 +172,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap ma, const __grid_constant__ C
       __syncwarp();
       if (lane == 0) mbar_arrive(&bar.acc_empty[ab]);
       fence_async_smem();
-      named_sync(3, 128);
-      if (tid == 128) {
+      __syncwarp();
+      if (lane == 0 && (int64_t)mt * kBM + ew * 32 < p.n_rows) {     // never start a store past the last row
+        const int r0 = mt * kBM + ew * 32;
+        const uint8_t* slab = sOut + ew * (32 * 128);
         if (p.out_kind == 0) {
-          tma_store_2d(&mc, sOut, nt * kBN, mt * kBM);
-          if (nt * kBN + 64 < p.n_cols) tma_store_2d(&mc, sOut + 16384, nt * kBN + 64, mt * kBM);
+          tma_store_2d(&mc, slab, nt * kBN, r0);
+          if (nt * kBN + 64 < p.n_cols) tma_store_2d(&mc, slab + 16384, nt * kBN + 64, r0);
         } else {
 #pragma unroll
           for (int cb = 0; cb < 4; ++cb) {
             if (nt * kBN + cb * 32 >= p.n_cols) break;       // never start a store past the last column
-            if (p.out_kind == 2) tma_reduce_add_2d(&mc, sOut + cb * 16384, nt * kBN + cb * 32, mt * kBM);
-            else tma_store_2d(&mc, sOut + cb * 16384, nt * kBN + cb * 32, mt * kBM);
+            if (p.out_kind == 2) tma_reduce_add_2d(&mc, slab + cb * 16384, nt * kBN + cb * 32, r0);
+            else tma_store_2d(&mc, slab + cb * 16384, nt * kBN + cb * 32, r0);
           }
         }
         bulk_commit_group();
       }
     }
-    if (tid == 128) bulk_wait_group<0>();
+    if (lane == 0) bulk_wait_group<0>();
   }
 
   tc_fence_before();
@@ -224,7 +227,7 @@ int gemm_tc(const GemmTcArgs& g, cudaStream_t st) {
   }
   {
     const int64_t dims[2] = {g.N, g.M}, str[2] = {1, g.N};
-    const int box[2] = {g.out_kind == 0 ? 64 : 32, 128};
+    const int box[2] = {g.out_kind == 0 ? 64 : 32, 32};      // one epilogue warp's slab
     if ((r = make_tiled_map(&mc, g.c, g.out_kind == 0 ? g.dtype : MF_F32, 2, dims, str, box, 128))) return r;
   }
   GemmP p{};
@@ -243,7 +246,7 @@ int gemm_tc(const GemmTcArgs& g, cudaStream_t st) {
   }
   p.slabs_per_split = (p.slabs_total + splits - 1) / splits;
   p.k_splits = (p.slabs_total + p.slabs_per_split - 1) / p.slabs_per_split;
-  p.n_cols = (int)g.N;
+  p.n_cols = (int)g.N; p.n_rows = g.M;
   p.a_mn = g.a_mn; p.b_mn = g.b_mn; p.out_kind = g.out_kind;
   p.ab_fmt = g.dtype == MF_BF16 ? 1u : 0u;
   p.status = status_word();

@@ -425,17 +425,20 @@ bool lnl_bwd_core_tc_ok(int64_t M, int K, int N, int dtype, bool has_ln, const v
 template <typename T>
 int lnl_bwd_core(int64_t M, int K, int N, const T* x, const T* gain, const T* shift, const T* w, const T* dy,
                  const float* mean, const float* rstd, T* dx, float* dw, float* db, float* d_ln_w, float* d_ln_b,
-                 Carver& ws, bool tc, int dtype, cudaStream_t st, const T* xln_ready = nullptr) {
+                 Carver& ws, bool tc, int dtype, cudaStream_t st, const T* xln_ready = nullptr,
+                 const float* dyln_ready = nullptr) {
   int r;
   float* col_scratch = ws.take<float>((size_t)kColSlices * (K > N ? K : N));
   if constexpr (sizeof(T) == 2) {
     if (tc) {
-      float* dyln = ws.take<float>((size_t)M * K);
+      float* dyln = dyln_ready ? const_cast<float*>(dyln_ready) : ws.take<float>((size_t)M * K);
       T* xln = xln_ready ? nullptr : ws.take<T>((size_t)M * K);
       float* part = ws.take<float>((size_t)kRowBlocks * 2 * K);
-      // dyln[M,K] = dy @ w^T  (A = dy [M,N], B = w [K,N], both with the reduction index contiguous)
-      r = gemm_tc(GemmTcArgs{dy, w, dyln, M, K, N, dtype, 0, 0, 1}, st);
-      if (r) return r;
+      if (!dyln_ready) {
+        // dyln[M,K] = dy @ w^T  (A = dy [M,N], B = w [K,N], both with the reduction index contiguous)
+        r = gemm_tc(GemmTcArgs{dy, w, dyln, M, K, N, dtype, 0, 0, 1}, st);
+        if (r) return r;
+      }
       int blocks = (int)((M + 63) / 64); if (blocks > kRowBlocks) blocks = kRowBlocks;
       const int64_t rpb = (M + blocks - 1) / blocks;
       blocks = (int)((M + rpb - 1) / rpb);
@@ -637,6 +640,10 @@ size_t transition_bwd_simt_workspace(const mf_transition_bwd_args& a) {
   size_t tc = 0;
   if (transition_bwd_use_tc(a)) {
     const size_t es = dtype_size(a.dtype);
+    const size_t fused = align_up((size_t)a.M * a.inner * es, 256) + align_up((size_t)a.M * 2 * a.inner * es, 256) +   // g, dh
+                         align_up(sizeof(float) * (size_t)a.M * a.dim, 256) + align_up(sizeof(float) * (size_t)a.dim * 2 * a.inner, 256) +
+                         lnl_bwd_core_bytes(a.M, a.dim, 2 * a.inner, true, true, a.dtype);
+    if (fused > simt) simt = fused;
     tc = align_up((size_t)a.M * 2 * a.inner * es, 256) + 2 * align_up((size_t)a.M * a.inner * es, 256) +   // h/dh, g, dg
          align_up((size_t)a.M * a.dim * es, 256) +                                                          // LN(x)
          lnl_bwd_core_bytes(a.M, a.dim, 2 * a.inner, true, true, a.dtype);
@@ -677,9 +684,34 @@ int transition_bwd_tc(const mf_transition_bwd_args& a, cudaStream_t st) {
                          static_cast<T*>(a.dx), a.dw1, nullptr, a.d_ln_w, a.d_ln_b, ws, true, a.dtype, st, xln);
 }
 
+// Fused composition (dim = 128): one kernel recomputes h on chip and leaves g, dh (chunk-ordered columns) and dyln in
+// HBM; then the LayerNorm row pass and the two weight-gradient GEMMs.
+template <typename T>
+int transition_bwd_fused_path(const mf_transition_bwd_args& a, cudaStream_t st) {
+  Carver ws(a.workspace);
+  const int I = a.inner;
+  const int64_t M = a.M;
+  T* g = ws.take<T>((size_t)M * I);
+  T* dh = ws.take<T>((size_t)M * 2 * I);
+  float* dyln = ws.take<float>((size_t)M * a.dim);
+  float* dw1p = ws.take<float>((size_t)a.dim * 2 * I);
+  int r = transition_bwd_fused(a, g, dh, dyln, st);
+  if (r) return r;
+  r = gemm_tc(GemmTcArgs{a.dy, g, a.dw2, a.dim, I, M, a.dtype, 1, 1, 2}, st);
+  if (r) return r;
+  r = lnl_bwd_core<T>(M, a.dim, 2 * I, static_cast<const T*>(a.x), static_cast<const T*>(a.ln_w),
+                      static_cast<const T*>(a.ln_b), static_cast<const T*>(a.w1), dh, a.mean, a.rstd,
+                      static_cast<T*>(a.dx), dw1p, nullptr, a.d_ln_w, a.d_ln_b, ws, true, a.dtype, st, nullptr, dyln);
+  if (r) return r;
+  return unpermute_dw1(dw1p, a.dw1, a.dim, I, st);
+}
+
 int transition_bwd_simt(const mf_transition_bwd_args& a, cudaStream_t st) {
-  if (transition_bwd_use_tc(a))
+  if (transition_bwd_use_tc(a)) {
+    if (transition_bwd_fused_ok(a))
+      return a.dtype == MF_BF16 ? transition_bwd_fused_path<__nv_bfloat16>(a, st) : transition_bwd_fused_path<__half>(a, st);
     return a.dtype == MF_BF16 ? transition_bwd_tc<__nv_bfloat16>(a, st) : transition_bwd_tc<__half>(a, st);
+  }
   Carver ws(a.workspace);
   const int I = a.inner;
   MF_DISPATCH_FLOAT(a.dtype, T, {

@@ -216,7 +216,7 @@ lnl_fwd_tc_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant_
         __syncwarp();
         if (lane == 0) {
           // [64 columns][32 rows] box; TMA clips rows >= M and columns >= N (a slab wholly beyond N is skipped)
-          if (n0 < p.N) tma_store_2d(&my, ys + (warp & 3) * (32 * 128), n0, (int)row0 + (warp & 3) * 32);
+          if (n0 < p.N && row0 + (warp & 3) * 32 < p.M) tma_store_2d(&my, ys + (warp & 3) * (32 * 128), n0, (int)row0 + (warp & 3) * 32);
           bulk_commit_group();
         }
       }
