@@ -245,14 +245,13 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
     tma_load_5d(sKV + (kc & 1) * 2 * C::TILEB + C::TILEB, &mv, fb, 0, h, jt2 * kT, n, b);
   };
   auto issue_scores = [&](uint32_t gg, uint32_t kc) {     // S^T = K Q^T and dP^T = V dO^T of block gg
-    const uint32_t ka = smem_u32(sKV + (kc & 1) * 2 * C::TILEB), va = ka + C::TILEB;
-    const uint32_t qa = smem_u32(qd_stage(gg)), ga = qa + C::TILEB;
+    const uint32_t ka = smem_u32(sKV + (kc & 1) * 2 * C::TILEB), qa = smem_u32(qd_stage(gg));
+    const uint32_t k_lo = desc_lo(ka, 16), v_lo = desc_lo(ka + C::TILEB, 16), q_lo = desc_lo(qa, 16), g_lo = desc_lo(qa + C::TILEB, 16);
+    constexpr uint32_t hi = desc_hi(C::SBO, C::SW);
 #pragma unroll
-    for (int ks = 0; ks < DP / 16; ++ks)
-      mma_ss(tST, smem_desc(ka + ks * 32, 16, C::SBO, C::SW), smem_desc(qa + ks * 32, 16, C::SBO, C::SW), id_s, ks > 0);
+    for (int ks = 0; ks < DP / 16; ++ks) mma_ss_lh(tST, k_lo + ks * 2, hi, q_lo + ks * 2, hi, id_s, ks > 0);
 #pragma unroll
-    for (int ks = 0; ks < DP / 16; ++ks)
-      mma_ss(tDP, smem_desc(va + ks * 32, 16, C::SBO, C::SW), smem_desc(ga + ks * 32, 16, C::SBO, C::SW), id_s, ks > 0);
+    for (int ks = 0; ks < DP / 16; ++ks) mma_ss_lh(tDP, v_lo + ks * 2, hi, g_lo + ks * 2, hi, id_s, ks > 0);
     tc_commit(&bar.sd_ready);
   };
 
@@ -500,18 +499,20 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
           if (*abort_flag) break;
           const uint32_t kvb = smem_u32(sKV + (kv & 1) * 2 * C::TILEB);
           const uint32_t qdb = smem_u32(qd_stage(g));
+          // descriptor low words (address field in units of 16 bytes); the high words are constants
+          const uint32_t p_lo = desc_lo(smem_u32(sP), 16), ds_lo = desc_lo(smem_u32(sDS), 16), dst_lo = desc_lo(smem_u32(sDS), 16384);
+          const uint32_t q_lo = desc_lo(qdb, 16), do_lo = desc_lo(qdb + C::TILEB, 16), k_lo = desc_lo(kvb, 16);
+          constexpr uint32_t hi_t = desc_hi(1024, kSw128), hi_o = desc_hi(C::SBO, C::SW);
+          constexpr uint32_t kstep = 16 * C::ROWB / 16;      // 16 rows of an MN-major operand tile
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks)      // dV_j += P^T dO_i
-            mma_ss(tDV_of(kv), smem_desc(smem_u32(sP) + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024, kSw128),
-                   smem_desc(qdb + C::TILEB + ks * 16 * C::ROWB, 16, C::SBO, C::SW), id_kv, it > 0 || ks > 0);
+            mma_ss_lh(tDV_of(kv), p_lo + (ks >> 2) * (16384 / 16) + (ks & 3) * 2, hi_t, do_lo + ks * kstep, hi_o, id_kv, it > 0 || ks > 0);
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks)      // dK_j += dS^T Q_i
-            mma_ss(tDK_of(kv), smem_desc(smem_u32(sDS) + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024, kSw128),
-                   smem_desc(qdb + ks * 16 * C::ROWB, 16, C::SBO, C::SW), id_kv, it > 0 || ks > 0);
+            mma_ss_lh(tDK_of(kv), ds_lo + (ks >> 2) * (16384 / 16) + (ks & 3) * 2, hi_t, q_lo + ks * kstep, hi_o, id_kv, it > 0 || ks > 0);
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks)      // dQ_i += dS K_j   (A = dS^T tile read MN-major: M = queries)
-            mma_ss(tDQ + it * DP, smem_desc(smem_u32(sDS) + ks * 2048, 16384, 1024, kSw128),
-                   smem_desc(kvb + ks * 16 * C::ROWB, 16, C::SBO, C::SW), id_q, jt > jt0 || ks > 0);
+            mma_ss_lh(tDQ + it * DP, dst_lo + ks * (2048 / 16), hi_t, k_lo + ks * kstep, hi_o, id_q, jt > jt0 || ks > 0);
           MF_TL(45);
           tc_commit(&bar.acc_done);
           // the stages are also read by this block's score MMAs, which completed before its tiles were written

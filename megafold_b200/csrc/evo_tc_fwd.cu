@@ -212,17 +212,17 @@ evo_fwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
     }
   };
   auto issue_s = [&](int g) {     // S(g) = Q K(g)^T
-    const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + (g % C::KS) * C::TILEB);
+    const uint32_t q_lo = desc_lo(smem_u32(sQ), 16), k_lo = desc_lo(smem_u32(sK + (g % C::KS) * C::TILEB), 16);
 #pragma unroll
     for (int ks = 0; ks < DP / 16; ++ks)
-      mma_ss(tS0, smem_desc(qa + ks * 32, 16, C::SBO, C::SW), smem_desc(ka + ks * 32, 16, C::SBO, C::SW), id_s, ks > 0);
+      mma_ss_lh(tS0, q_lo + ks * 2, desc_hi(C::SBO, C::SW), k_lo + ks * 2, desc_hi(C::SBO, C::SW), id_s, ks > 0);
     tc_commit(&bar.s_ready);
   };
   auto issue_pv = [&](int g) {    // O_tile(g) = P V(g)
-    const uint32_t va = smem_u32(sV + (g % kVS) * C::TILEB);
+    const uint32_t v_lo = desc_lo(smem_u32(sV + (g % kVS) * C::TILEB), 16);
 #pragma unroll
     for (int ks = 0; ks < kKT / 16; ++ks)
-      mma_ts(tS0 + 192, tS0 + 128 + ks * 8, smem_desc(va + ks * 16 * C::ROWB, 16, C::SBO, C::SW), id_o, ks > 0);
+      mma_ts_lh(tS0 + 192, tS0 + 128 + ks * 8, v_lo + ks * (16 * C::ROWB / 16), desc_hi(C::SBO, C::SW), id_o, ks > 0);
     tc_commit(&bar.pv_done);
   };
 

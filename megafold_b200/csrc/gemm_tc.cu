@@ -121,12 +121,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap ma, const __grid_constant__ C
         tc_fence_after();
         if (*abort_flag) break;
         const uint32_t a0 = smem_u32(sStage + st * kStageBytes), b0 = a0 + 16384;
+        // descriptor low words stepped by (bytes >> 4) per k-step: 16 rows of 128 B for MN-major, 32 B for K-major
+        const uint32_t a_lo = p.a_mn ? desc_lo(a0, 8192) : desc_lo(a0, 16), a_step = p.a_mn ? 128u : 2u;
+        const uint32_t b_lo = p.b_mn ? desc_lo(b0, 8192) : desc_lo(b0, 16), b_step = p.b_mn ? 128u : 2u;
 #pragma unroll
-        for (int ks = 0; ks < kBK / 16; ++ks) {
-          const uint64_t ad = p.a_mn ? smem_desc(a0 + ks * 2048, 8192, 1024, kSw128) : smem_desc(a0 + ks * 32, 16, 1024, kSw128);
-          const uint64_t bd = p.b_mn ? smem_desc(b0 + ks * 2048, 8192, 1024, kSw128) : smem_desc(b0 + ks * 32, 16, 1024, kSw128);
-          mma_ss(tm0 + ab * kBN, ad, bd, idesc, s > s0 || ks > 0);
-        }
+        for (int ks = 0; ks < kBK / 16; ++ks)
+          mma_ss_lh(tm0 + ab * kBN, a_lo + ks * a_step, desc_hi(1024, kSw128), b_lo + ks * b_step, desc_hi(1024, kSw128), idesc, s > s0 || ks > 0);
         tc_commit(&bar.empty[st]);
       }
       tc_commit(&bar.acc_full[ab]);

@@ -232,18 +232,18 @@ lnl_fwd_tc_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant_
     for (int t = 0; t < my_tiles && !*abort_flag; ++t) {
       const int buf = t % kAStages;
       wait_or_flag(&bar.a_full[buf], (t / kAStages) & 1, abort_flag);
-      const uint32_t a0 = smem_u32(sA + buf * A_BYTES);
+      const uint32_t a_lo = desc_lo(smem_u32(sA + buf * A_BYTES), 16);
       for (int nt = 0; nt < p.n_nt; ++nt, ++acc_cnt, ++w_cnt) {
         const int ab = acc_cnt & 1, ws = w_cnt % kWStages;
         wait_or_flag(&bar.w_full[ws], (w_cnt / kWStages) & 1, abort_flag);
         if (acc_cnt >= 2) wait_or_flag(&bar.acc_empty[ab], ((acc_cnt >> 1) - 1) & 1, abort_flag);
         tc_fence_after();
         if (*abort_flag) break;
-        const uint32_t w0 = smem_u32(sW + ws * W_BYTES);
+        const uint32_t w_lo = desc_lo(smem_u32(sW + ws * W_BYTES), K * 128);
 #pragma unroll
         for (int ks = 0; ks < K / 16; ++ks)
-          mma_ss(tm0 + ab * kNT, smem_desc(a0 + (ks >> 2) * (kRows * 128) + (ks & 3) * 32, 16, 1024, kSw128),
-                 smem_desc(w0 + ks * 2048, K * 128, 1024, kSw128), idesc, ks > 0);
+          mma_ss_lh(tm0 + ab * kNT, a_lo + (ks >> 2) * (kRows * 128 / 16) + (ks & 3) * 2, desc_hi(1024, kSw128),
+                    w_lo + ks * (2048 / 16), desc_hi(1024, kSw128), idesc, ks > 0);
         tc_commit(&bar.acc_full[ab]);
         tc_commit(&bar.w_empty[ws]);
       }

@@ -254,12 +254,12 @@ transition_bwd_tc_kernel(const __grid_constant__ CUtensorMap mx, const __grid_co
         if (first_of_tile && t > 0) wait_or_flag(&bar.acc_empty, (t - 1) & 1, abort_flag);
         tc_fence_after();
         if (*abort_flag) return;
-        const uint32_t dh = smem_u32(sDH + hb * DH_BYTES), w = smem_u32(sW + hb * W_BYTES);
+        const uint32_t dh_lo = desc_lo(smem_u32(sDH + hb * DH_BYTES), 16), w_lo = desc_lo(smem_u32(sW + hb * W_BYTES), 16);
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) {
           // k-step ks covers dh columns ks*16 .. +15: value (ks even) or gate (ks odd) columns (ks / 2) * 16 .. of the chunk
-          const uint32_t wb = w + (ks & 1) * WB + (ks >> 1) * 32;
-          mma_ss(tACC, smem_desc(dh + ks * 32, 16, 1024, kSw128), smem_desc(wb, 16, 512, kSw64), id_a, !first_of_tile || ks > 0);
+          mma_ss_lh(tACC, dh_lo + ((ks * 32) >> 4), desc_hi(1024, kSw128), w_lo + (((ks & 1) * WB + (ks >> 1) * 32) >> 4), desc_hi(512, kSw64),
+                    id_a, !first_of_tile || ks > 0);
         }
         tc_commit(&bar.dh_empty[hb]);
         tc_commit(&bar.w_empty[hb]);
@@ -268,7 +268,7 @@ transition_bwd_tc_kernel(const __grid_constant__ CUtensorMap mx, const __grid_co
         const int buf = t & 1;
         wait_or_flag(&bar.a_full[buf], (t >> 1) & 1, abort_flag);
         wait_or_flag(&bar.dy_full, t & 1, abort_flag);
-        const uint32_t a0 = smem_u32(sA + buf * A_BYTES), y0 = smem_u32(sDY);
+        const uint32_t a_lo = desc_lo(smem_u32(sA + buf * A_BYTES), 16), y_lo = desc_lo(smem_u32(sDY), 16);
         for (int c = 0; c < nch && !*abort_flag; ++c, ++ch_cnt) {
           const int hb = ch_cnt & 1;
           wait_or_flag(&bar.w_full[hb], (ch_cnt >> 1) & 1, abort_flag);
@@ -276,14 +276,15 @@ transition_bwd_tc_kernel(const __grid_constant__ CUtensorMap mx, const __grid_co
           tc_fence_after();
           if (*abort_flag) break;
           const uint32_t w = smem_u32(sW + hb * W_BYTES);
+          const uint32_t wh_lo = desc_lo(w, WB), wg_lo = desc_lo(w + 2 * WB, 16);
 #pragma unroll
           for (int ks = 0; ks < K / 16; ++ks)      // H value | gate: the two blocks are the two atoms along N (LBO = WB)
-            mma_ss(tHD + hb * 128, smem_desc(a0 + (ks >> 2) * (kRows * 128) + (ks & 3) * 32, 16, 1024, kSw128),
-                   smem_desc(w + ks * 1024, WB, 512, kSw64), id_h, ks > 0);
+            mma_ss_lh(tHD + hb * 128, a_lo + (((ks >> 2) * (kRows * 128) + (ks & 3) * 32) >> 4), desc_hi(1024, kSw128),
+                      wh_lo + ((ks * 1024) >> 4), desc_hi(512, kSw64), id_h, ks > 0);
 #pragma unroll
           for (int ks = 0; ks < K / 16; ++ks)      // DG
-            mma_ss(tHD + hb * 128 + 64, smem_desc(y0 + (ks >> 2) * (kRows * 128) + (ks & 3) * 32, 16, 1024, kSw128),
-                   smem_desc(w + 2 * WB + ks * 1024, 16, 512, kSw64), id_g, ks > 0);
+            mma_ss_lh(tHD + hb * 128 + 64, y_lo + (((ks >> 2) * (kRows * 128) + (ks & 3) * 32) >> 4), desc_hi(1024, kSw128),
+                      wg_lo + ((ks * 1024) >> 4), desc_hi(512, kSw64), id_g, ks > 0);
           tc_commit(&bar.hd_full[hb]);
           if (c > 0) acc_gemm(ch_cnt - 1, c == 1, t);
         }

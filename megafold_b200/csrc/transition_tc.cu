@@ -263,32 +263,32 @@ transition_fwd_tc_kernel(const __grid_constant__ CUtensorMap mx, const __grid_co
       if (first_of_tile && t > 0) wait_or_flag(&bar.y_empty, (t - 1) & 1, abort_flag);
       tc_fence_after();
       if (*abort_flag) return;
-      const uint32_t g0 = smem_u32(sG + gb * G_BYTES), w2 = smem_u32(sW + ws * W_BYTES + 2 * W1B);
+      const uint32_t g_lo = desc_lo(smem_u32(sG + gb * G_BYTES), 16), w2_lo = desc_lo(smem_u32(sW + ws * W_BYTES + 2 * W1B), 16);
 #pragma unroll
       for (int ks = 0; ks < kHC / 16; ++ks)
-        mma_ss(tY, smem_desc(g0 + ks * 32, 16, 1024, kSw128), smem_desc(w2 + ks * 32, 16, 1024, kSw128), id2, !first_of_tile || ks > 0);
+        mma_ss_lh(tY, g_lo + ks * 2, desc_hi(1024, kSw128), w2_lo + ks * 2, desc_hi(1024, kSw128), id2, !first_of_tile || ks > 0);
       tc_commit(&bar.g_empty[gb]);
       tc_commit(&bar.w2_empty[ws]);
     };
     for (int t = 0; t < my_tiles && !*abort_flag; ++t) {
       const int buf = t % kAStages;
       wait_or_flag(&bar.a_full[buf], (t / kAStages) & 1, abort_flag);
-      const uint32_t a0 = smem_u32(sA + buf * A_BYTES);
+      const uint32_t a_lo = desc_lo(smem_u32(sA + buf * A_BYTES), 16);
       for (int c = 0; c < nch && !*abort_flag; ++c, ++ch_cnt) {
         const int hb = ch_cnt & 1, ws = ch_cnt % kWStages;
         wait_or_flag(&bar.w1_full[ws], (ch_cnt / kWStages) & 1, abort_flag);
         if (ch_cnt >= 2) wait_or_flag(&bar.h_empty[hb], ((ch_cnt >> 1) - 1) & 1, abort_flag);
         tc_fence_after();
         if (*abort_flag) break;
-        const uint32_t w1 = smem_u32(sW + ws * W_BYTES);
+        const uint32_t w1v_lo = desc_lo(smem_u32(sW + ws * W_BYTES), 16), w1g_lo = desc_lo(smem_u32(sW + ws * W_BYTES + W1B), 16);
 #pragma unroll
         for (int ks = 0; ks < K / 16; ++ks)      // value half
-          mma_ss(tH + hb * 128, smem_desc(a0 + (ks >> 2) * (kRows * 128) + (ks & 3) * 32, 16, 1024, kSw128),
-                 smem_desc(w1 + ks * 2048, 16, 1024, kSw128), id1, ks > 0);
+          mma_ss_lh(tH + hb * 128, a_lo + (ks >> 2) * (kRows * 128 / 16) + (ks & 3) * 2, desc_hi(1024, kSw128),
+                    w1v_lo + ks * (2048 / 16), desc_hi(1024, kSw128), id1, ks > 0);
 #pragma unroll
         for (int ks = 0; ks < K / 16; ++ks)      // gate half
-          mma_ss(tH + hb * 128 + 64, smem_desc(a0 + (ks >> 2) * (kRows * 128) + (ks & 3) * 32, 16, 1024, kSw128),
-                 smem_desc(w1 + W1B + ks * 2048, 16, 1024, kSw128), id1, ks > 0);
+          mma_ss_lh(tH + hb * 128 + 64, a_lo + (ks >> 2) * (kRows * 128 / 16) + (ks & 3) * 2, desc_hi(1024, kSw128),
+                    w1g_lo + ks * (2048 / 16), desc_hi(1024, kSw128), id1, ks > 0);
         tc_commit(&bar.h_full[hb]);
         tc_commit(&bar.w1_empty[ws]);
         if (c > 0) gemm2(ch_cnt - 1, c == 1, t);

@@ -194,9 +194,13 @@ def test_lnl_backward_tensor_core_path(M, N, K, dtype):
         assert_close_lowp(g_, r_.float(), n + " vs CUDA cores")
 
 
-@pytest.mark.parametrize("M,dim,ef", [(12000, 128, 4), (777, 64, 2), (300, 384, 4)])
-def test_transition_backward_tensor_core_path(M, dim, ef):
-    x, ln_w, ln_b, w1, w2, dy = [t.to(DEV, torch.bfloat16) for t in _transition_case(M, dim, ef, seed=3)]
+@pytest.mark.parametrize("M,dim,ef,dtype", [(12000, 128, 4, torch.bfloat16), (777, 64, 2, torch.bfloat16),
+                                            (300, 384, 4, torch.bfloat16), (1000, 128, 2, torch.float16),
+                                            (129, 128, 0.25, torch.bfloat16)])
+def test_transition_backward_tensor_core_path(M, dim, ef, dtype):
+    """dim = 128 takes the fused backward core (hidden activation recomputed on chip), the other sizes the composition
+    of tensor-core GEMMs and row passes; inner = 32 is a single hidden chunk."""
+    x, ln_w, ln_b, w1, w2, dy = [t.to(DEV, dtype) for t in _transition_case(M, dim, ef, seed=3)]
     _, mean, rstd = mfb.transition_forward(x, ln_w, ln_b, w1, w2)
     got = mfb.transition_backward(dy, x, ln_w, ln_b, w1, w2, mean, rstd)
     assert _lib.last_path() == "tcgen05"
