@@ -40,6 +40,8 @@ constexpr int WB = K * 64;                       // 8 KB: one [128 rows][32 colu
 constexpr int W_BYTES = 3 * WB;                  // W1 value | W1 gate | W2
 constexpr int DH_BYTES = kRows * 128;            // [128 rows][64 columns] 16 bit
 constexpr int G_BYTES = kRows * 64;              // [128 rows][32 columns] 16 bit
+constexpr int kWS = 3;                           // weight stages: a stage is released only by the dyln GEMM of its chunk,
+                                                 // one chunk after its H / DG GEMMs, so two stages would stall the TMA refill
 
 struct TbP {
   int64_t M; int inner, n_mt, n_ch;
@@ -52,7 +54,7 @@ struct TbP {
 
 struct Bars {
   uint64_t x_full[2], a_full[2], a_empty[2], dy_full, dy_empty;
-  uint64_t w_full[2], w_empty[2];
+  uint64_t w_full[kWS], w_empty[kWS];
   uint64_t hd_full[2], hd_empty[2], dh_full[2], dh_empty[2], acc_full, acc_empty;
 };
 
@@ -82,8 +84,8 @@ transition_bwd_tc_kernel(const __grid_constant__ CUtensorMap mx, const __grid_co
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* sA = smem;                          // [2] X tiles, normalised in place
   uint8_t* sDY = sA + 2 * A_BYTES;             // dY tile
-  uint8_t* sW = sDY + A_BYTES;                 // [2] weight stages
-  uint8_t* sDH = sW + 2 * W_BYTES;             // [2] dh tiles
+  uint8_t* sW = sDY + A_BYTES;                 // [kWS] weight stages
+  uint8_t* sDH = sW + kWS * W_BYTES;           // [2] dh tiles
   uint8_t* sG = sDH + 2 * DH_BYTES;            // [2] g tiles
 
   __shared__ Bars bar;
@@ -95,10 +97,10 @@ transition_bwd_tc_kernel(const __grid_constant__ CUtensorMap mx, const __grid_co
     abort_s = 0;
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bar.x_full[i], 1); mbar_init(&bar.a_full[i], 4); mbar_init(&bar.a_empty[i], 1);
-      mbar_init(&bar.w_full[i], 1); mbar_init(&bar.w_empty[i], 1);
       mbar_init(&bar.hd_full[i], 1); mbar_init(&bar.hd_empty[i], 8);
       mbar_init(&bar.dh_full[i], 8); mbar_init(&bar.dh_empty[i], 1);
     }
+    for (int i = 0; i < kWS; ++i) { mbar_init(&bar.w_full[i], 1); mbar_init(&bar.w_empty[i], 1); }
     mbar_init(&bar.dy_full, 1); mbar_init(&bar.dy_empty, 1);
     mbar_init(&bar.acc_full, 1); mbar_init(&bar.acc_empty, 8);
     mbar_fence_init();
@@ -254,7 +256,7 @@ transition_bwd_tc_kernel(const __grid_constant__ CUtensorMap mx, const __grid_co
         if (first_of_tile && t > 0) wait_or_flag(&bar.acc_empty, (t - 1) & 1, abort_flag);
         tc_fence_after();
         if (*abort_flag) return;
-        const uint32_t dh_lo = desc_lo(smem_u32(sDH + hb * DH_BYTES), 16), w_lo = desc_lo(smem_u32(sW + hb * W_BYTES), 16);
+        const uint32_t dh_lo = desc_lo(smem_u32(sDH + hb * DH_BYTES), 16), w_lo = desc_lo(smem_u32(sW + (cc % kWS) * W_BYTES), 16);
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) {
           // k-step ks covers dh columns ks*16 .. +15: value (ks even) or gate (ks odd) columns (ks / 2) * 16 .. of the chunk
@@ -262,7 +264,7 @@ transition_bwd_tc_kernel(const __grid_constant__ CUtensorMap mx, const __grid_co
                     id_a, !first_of_tile || ks > 0);
         }
         tc_commit(&bar.dh_empty[hb]);
-        tc_commit(&bar.w_empty[hb]);
+        tc_commit(&bar.w_empty[cc % kWS]);
       };
       for (int t = 0; t < my_tiles && !*abort_flag; ++t) {
         const int buf = t & 1;
@@ -270,12 +272,12 @@ transition_bwd_tc_kernel(const __grid_constant__ CUtensorMap mx, const __grid_co
         wait_or_flag(&bar.dy_full, t & 1, abort_flag);
         const uint32_t a_lo = desc_lo(smem_u32(sA + buf * A_BYTES), 16), y_lo = desc_lo(smem_u32(sDY), 16);
         for (int c = 0; c < nch && !*abort_flag; ++c, ++ch_cnt) {
-          const int hb = ch_cnt & 1;
-          wait_or_flag(&bar.w_full[hb], (ch_cnt >> 1) & 1, abort_flag);
+          const int hb = ch_cnt & 1, ws = ch_cnt % kWS;
+          wait_or_flag(&bar.w_full[ws], (ch_cnt / kWS) & 1, abort_flag);
           if (ch_cnt >= 2) wait_or_flag(&bar.hd_empty[hb], ((ch_cnt >> 1) - 1) & 1, abort_flag);
           tc_fence_after();
           if (*abort_flag) break;
-          const uint32_t w = smem_u32(sW + hb * W_BYTES);
+          const uint32_t w = smem_u32(sW + ws * W_BYTES);
           const uint32_t wh_lo = desc_lo(w, WB), wg_lo = desc_lo(w + 2 * WB, 16);
 #pragma unroll
           for (int ks = 0; ks < K / 16; ++ks)      // H value | gate: the two blocks are the two atoms along N (LBO = WB)
@@ -315,9 +317,9 @@ transition_bwd_tc_kernel(const __grid_constant__ CUtensorMap mx, const __grid_co
         tma_load_2d(sDY + kRows * 128, &mdy, &bar.dy_full, 64, row0);
         if (t + 1 < my_tiles) load_x(t + 1);
         for (int c = 0; c < nch; ++c, ++ch_cnt) {
-          const int ws = ch_cnt & 1;
+          const int ws = ch_cnt % kWS;
           uint8_t* w = sW + ws * W_BYTES;
-          if (ch_cnt >= 2) wait_or_flag(&bar.w_empty[ws], ((ch_cnt >> 1) - 1) & 1, abort_flag);
+          if (ch_cnt >= kWS) wait_or_flag(&bar.w_empty[ws], ((ch_cnt / kWS) - 1) & 1, abort_flag);
           if (*abort_flag) break;
           mbar_expect_tx(&bar.w_full[ws], W_BYTES);
           tma_load_2d(w, &mw1, &bar.w_full[ws], c * kHC, 0);                    // value columns of W1
@@ -396,7 +398,7 @@ int transition_bwd_fused(const mf_transition_bwd_args& a, void* g, void* dh, flo
   p.status = status_word();
   MF_REQUIRE(p.status, MF_ERR_CUDA, "could not allocate the device status word");
   MF_REQUIRE(tc_async_status() == 0, MF_ERR_CUDA, "an earlier tensor-core kernel gave up on a bounded wait; results are invalid");
-  const size_t smem = 1024 + 3 * (size_t)A_BYTES + 2 * (size_t)W_BYTES + 2 * (size_t)DH_BYTES + 2 * (size_t)G_BYTES;
+  const size_t smem = 1024 + 3 * (size_t)A_BYTES + kWS * (size_t)W_BYTES + 2 * (size_t)DH_BYTES + 2 * (size_t)G_BYTES;
   int grid = sm_count();
   if (grid > p.n_mt) grid = p.n_mt;
   if (a.dtype == MF_BF16) {
