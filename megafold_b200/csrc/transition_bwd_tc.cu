@@ -9,8 +9,9 @@
 // of dyln are separate, streaming kernels.
 //
 // Persistent CTA per SM, 128-row tiles, the hidden dimension walked in chunks of 32 (value) + 32 (gate) columns:
-//   warp 13      TMA: X tile (two stages), dY tile, per chunk the W1 value / gate blocks and the W2 block
-//                ([128 rows][32 columns], 64-byte swizzle).
+//   warp 13      TMA loads: X tile (two stages), dY tile, per chunk the W1 value / gate blocks and the W2 block
+//                ([128 rows][32 columns], 64-byte swizzle; three stages).
+//   warp 14      TMA stores of the dh and g tiles of every chunk.
 //   warps 8-11   LayerNorm of the X tile in place (thread per row), one tile ahead.
 //   warp 12      MMAs.  Per chunk c: H(c) = A W1blocks (8 x N=64, the two blocks as the two swizzle atoms of one
 //                MN-major B operand) and DG(c) = dY W2block (8 x N=32) into one of two TMEM buffers; then, once the
@@ -19,7 +20,7 @@
 //   warps 0-7    workers, thread (row, half): 16 value, 16 gate, 16 dg columns from TMEM; g, dh in registers with one
 //                MUFU op per element; 16-bit tiles to shared memory: dh as the K-major A operand of the dyln GEMM
 //                (column order inside a chunk: [value 0-15 | gate 0-15 | value 16-31 | gate 16-31]) and both as
-//                sources of TMA stores (one 32-row slab per pair of warps).  After the last chunk: dyln TMEM ->
+//                sources of the TMA stores.  After the last chunk: dyln TMEM ->
 //                registers -> global (fp32).
 // dh is stored chunk by chunk in that column order ([M][inner/32][64]); dW1 computed from it has its columns in the same
 // order and is put back by a small kernel.
@@ -55,7 +56,7 @@ struct TbP {
 struct Bars {
   uint64_t x_full[2], a_full[2], a_empty[2], dy_full, dy_empty;
   uint64_t w_full[kWS], w_empty[kWS];
-  uint64_t hd_full[2], hd_empty[2], dh_full[2], dh_empty[2], acc_full, acc_empty;
+  uint64_t hd_full[2], hd_empty[2], dh_full[2], dh_empty[2], st_done[2], acc_full, acc_empty;
 };
 
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, const void* src, int c0, int c1) {
@@ -98,7 +99,7 @@ transition_bwd_tc_kernel(const __grid_constant__ CUtensorMap mx, const __grid_co
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bar.x_full[i], 1); mbar_init(&bar.a_full[i], 4); mbar_init(&bar.a_empty[i], 1);
       mbar_init(&bar.hd_full[i], 1); mbar_init(&bar.hd_empty[i], 8);
-      mbar_init(&bar.dh_full[i], 8); mbar_init(&bar.dh_empty[i], 1);
+      mbar_init(&bar.dh_full[i], 8); mbar_init(&bar.dh_empty[i], 1); mbar_init(&bar.st_done[i], 1);
     }
     for (int i = 0; i < kWS; ++i) { mbar_init(&bar.w_full[i], 1); mbar_init(&bar.w_empty[i], 1); }
     mbar_init(&bar.dy_full, 1); mbar_init(&bar.dy_empty, 1);
@@ -160,8 +161,8 @@ transition_bwd_tc_kernel(const __grid_constant__ CUtensorMap mx, const __grid_co
     } else {
       // -------------------------------------------------------------------------------- workers
       asm volatile("setmaxnreg.inc.sync.aligned.u32 152;");
-      const int half = warp >> 2, quarter = warp & 3;
-      const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+      const int half = warp >> 2;
+      const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
       uint32_t ch_cnt = 0;
       bool dead = false;
       for (int t = 0; t < my_tiles && !dead; ++t) {
@@ -193,11 +194,13 @@ transition_bwd_tc_kernel(const __grid_constant__ CUtensorMap mx, const __grid_co
             }
             gp[e] = Pack2<T>::pack(go[0], go[1]); dv[e] = Pack2<T>::pack(dvo[0], dvo[1]); db[e] = Pack2<T>::pack(dbo[0], dbo[1]);
           }
-          // tile buffer hb: the dyln MMAs of two chunks ago have read it (mbarrier), and so has the TMA store that the
-          // first lane of this pair of warps issued then (bulk group); the pair meets at a 64-thread barrier
-          if (ch_cnt >= 2) wait_or_flag(&bar.dh_empty[hb], ((ch_cnt >> 1) - 1) & 1, abort_flag);
-          if (half == 0 && lane == 0) bulk_wait_group_read<1>();
-          if (named_sync_or(4 + quarter, 64, *abort_flag)) { dead = true; break; }
+          // tile buffer hb: the dyln MMAs of two chunks ago have read it, and so has the TMA store of that chunk (which
+          // the store warp issues and reports)
+          if (ch_cnt >= 2) {
+            wait_or_flag(&bar.dh_empty[hb], ((ch_cnt >> 1) - 1) & 1, abort_flag);
+            wait_or_flag(&bar.st_done[hb], ((ch_cnt >> 1) - 1) & 1, abort_flag);
+          }
+          if (__any_sync(0xffffffffu, *abort_flag)) { dead = true; break; }
           uint8_t* dh = sDH + hb * DH_BYTES;
           uint8_t* g = sG + hb * G_BYTES;
           // dh row (128 B): [value 0-15 | gate 0-15 | value 16-31 | gate 16-31]; my 16 + 16 columns are chunks half*4 .. +3
@@ -211,15 +214,6 @@ transition_bwd_tc_kernel(const __grid_constant__ CUtensorMap mx, const __grid_co
           fence_async_smem();
           __syncwarp();
           if (lane == 0) mbar_arrive(&bar.dh_full[hb]);
-          named_sync(4 + quarter, 64);
-          if (half == 0 && lane == 0) {
-            const int r0 = row0 + quarter * 32;
-            if (r0 < p.M) {
-              tma_store_2d(&mdh, dh + quarter * (32 * 128), c * 64, r0);
-              tma_store_2d(&mg, g + quarter * (32 * 64), c * kHC, r0);
-            }
-            bulk_commit_group();
-          }
         }
         if (dead) break;
         // ---- dyln of this tile: TMEM -> registers -> global (fp32), thread (row, half) = 64 columns
@@ -240,7 +234,6 @@ transition_bwd_tc_kernel(const __grid_constant__ CUtensorMap mx, const __grid_co
             dst[i] = make_float4(__uint_as_float(acc[4 * i]), __uint_as_float(acc[4 * i + 1]), __uint_as_float(acc[4 * i + 2]), __uint_as_float(acc[4 * i + 3]));
         }
       }
-      if (half == 0 && lane == 0) bulk_wait_group<0>();
     }
   } else {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
@@ -296,6 +289,23 @@ transition_bwd_tc_kernel(const __grid_constant__ CUtensorMap mx, const __grid_co
         acc_gemm(ch_cnt - 1, nch == 1, t);
         tc_commit(&bar.acc_full);
       }
+    } else if (warp == 14 && lane == 0) {
+      // -------------------------------------------------------------------------------- TMA stores of the dh / g tiles
+      uint32_t ch_cnt = 0;
+      for (int t = 0; t < my_tiles && !*abort_flag; ++t) {
+        const int row0 = (int)(((int64_t)blockIdx.x + (int64_t)t * gridDim.x) * kRows);
+        for (int c = 0; c < nch && !*abort_flag; ++c, ++ch_cnt) {
+          const int hb = ch_cnt & 1;
+          wait_or_flag(&bar.dh_full[hb], (ch_cnt >> 1) & 1, abort_flag);      // written and fenced by all eight worker warps
+          if (*abort_flag) break;
+          tma_store_2d(&mdh, sDH + hb * DH_BYTES, c * 64, row0);               // rows >= M are clipped
+          tma_store_2d(&mg, sG + hb * G_BYTES, c * kHC, row0);
+          bulk_commit_group();
+          bulk_wait_group_read<0>();
+          mbar_arrive(&bar.st_done[hb]);
+        }
+      }
+      bulk_wait_group<0>();
     } else if (warp == 13 && lane == 0) {
       // -------------------------------------------------------------------------------- TMA producer
       uint32_t ch_cnt = 0;
@@ -380,12 +390,12 @@ int transition_bwd_fused(const mf_transition_bwd_args& a, void* g, void* dh, flo
   }
   {
     const int64_t dims[2] = {2 * (int64_t)a.inner, a.M}, str[2] = {1, 2 * (int64_t)a.inner};
-    const int box[2] = {64, 32};
+    const int box[2] = {64, kRows};
     if ((r = make_tiled_map(&mdh, dh, a.dtype, 2, dims, str, box, 128))) return r;
   }
   {
     const int64_t dims[2] = {a.inner, a.M}, str[2] = {1, a.inner};
-    const int box[2] = {kHC, 32};
+    const int box[2] = {kHC, kRows};
     if ((r = make_tiled_map(&mg, g, a.dtype, 2, dims, str, box, 64))) return r;
   }
   TbP p{};
