@@ -45,7 +45,8 @@ struct BwdP {
   int B, N, L, H, D;
   int n_t, n_items, lpad;
   int ksplit;            // work items per (b, n, h): the key tiles are split into this many ranges
-  float* dq_acc;         // fp32 [B,N,L,H,D] accumulator of dQ when ksplit > 1
+  float* dq_acc;         // fp32 [B,N,L,H,D] accumulator of dQ when ksplit > 1 or dq_stream
+  int dq_stream;         // more query tiles than dQ accumulators fit in TMEM: dQ leaves the SM block by block
   float c1, scale, inv_L;
   uint32_t ab_fmt;
   const void* bias; int64_t bs[4];
@@ -213,7 +214,9 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
   const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
   // dK/dV accumulators are double-buffered over the key tiles when the dQ accumulators leave room for it: their
   // write-out is then deferred by one block and no longer stalls the pipeline at the end of a key tile
-  const bool dbuf = p.n_t <= (512 - 256 - 4 * DP) / DP;
+  const bool dbuf = p.dq_stream || p.n_t <= (512 - 256 - 4 * DP) / DP;
+  // dQ: one accumulator per query tile, complete at the end of the item; or (dq_stream) two accumulators used in turn
+  // by successive blocks, each block's product added to the fp32 accumulator in global memory by the compute warps
   const uint32_t tST = tm0, tDP = tm0 + 128, tKV = tm0 + 256, tDQ = tm0 + 256 + (dbuf ? 4 : 2) * DP;
   auto tDK_of = [&](uint32_t kc) { return tKV + (dbuf ? (kc & 1) * 2 * DP : 0); };
   auto tDV_of = [&](uint32_t kc) { return tDK_of(kc) + DP; };
@@ -281,6 +284,29 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
       }
     }
     tc_fence_before();
+  };
+
+  // dq_stream: the dQ product of block gg (query tile it2) sits in accumulator gg & 1; the four warps of query
+  // quarter gg & 3 add it, scaled, to the fp32 dQ rows in global memory
+  auto stream_dq = [&](uint32_t gg, int it2, int b, int n, int h) {
+    if (w != (int)(gg & 3)) return;
+    tc_fence_after();
+    uint32_t o32[DP];
+#pragma unroll
+    for (int cb = 0; cb < DP / 32; ++cb)
+      tmem_ld32(tDQ + (gg & 1) * DP + lane_addr + cb * 32, *reinterpret_cast<uint32_t (*)[32]>(o32 + cb * 32));
+    tmem_ld_wait();
+    tc_fence_before();
+    const int i = it2 * kT + r;
+    if (i < p.L && !*abort_flag) {
+      float* arow = p.dq_acc + ((((int64_t)b * p.N + n) * p.L + i) * p.H + h) * p.D;
+#pragma unroll
+      for (int d4 = 0; d4 < DP / 4; ++d4)
+        if (d4 * 4 < p.D)
+          asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(arow + d4 * 4),
+                       "f"(__uint_as_float(o32[d4 * 4]) * p.scale), "f"(__uint_as_float(o32[d4 * 4 + 1]) * p.scale),
+                       "f"(__uint_as_float(o32[d4 * 4 + 2]) * p.scale), "f"(__uint_as_float(o32[d4 * 4 + 3]) * p.scale) : "memory");
+    }
   };
 
   if (warp < kComputeWarps) {
@@ -419,6 +445,7 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
         MF_TL(26);
         // the MMAs of the previous block have finished reading the P^T / dS^T tiles?
         if (g > 0) wait_or_flag(&bar.acc_done, (g - 1) & 1, abort_flag);
+        if (p.dq_stream && !(jt == jt0 && it == 0)) stream_dq(g - 1, it == 0 ? nt - 1 : it - 1, b, n, h);
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch) {
           const uint32_t off = (w >> 1) * 16384 + swz_offset(r, (w & 1) * 4 + ch, 128);
@@ -449,7 +476,8 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
     wait_or_flag(&bar.acc_done, (g - 1) & 1, abort_flag);
     if (pend_j >= 0) { store_kv(pend_kc, pend_j, pend_b, pend_n, pend_h); pend_j = -1; }
     tc_fence_after();
-    for (int it = w; it < nt; it += 4) {
+    if (p.dq_stream) stream_dq(g - 1, nt - 1, b, n, h);     // the last block of the item
+    for (int it = w; it < nt && !p.dq_stream; it += 4) {
       const int i = it * kT + r;
       uint32_t o32[DP];
 #pragma unroll
@@ -512,7 +540,8 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
             mma_ss_lh(tDK_of(kv), ds_lo + (ks >> 2) * (16384 / 16) + (ks & 3) * 2, hi_t, q_lo + ks * kstep, hi_o, id_kv, it > 0 || ks > 0);
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks)      // dQ_i += dS K_j   (A = dS^T tile read MN-major: M = queries)
-            mma_ss_lh(tDQ + it * DP, dst_lo + ks * (2048 / 16), hi_t, k_lo + ks * kstep, hi_o, id_q, jt > jt0 || ks > 0);
+            mma_ss_lh(tDQ + (p.dq_stream ? (g & 1) : it) * DP, dst_lo + ks * (2048 / 16), hi_t, k_lo + ks * kstep, hi_o, id_q,
+                      p.dq_stream ? ks > 0 : (jt > jt0 || ks > 0));
           MF_TL(45);
           tc_commit(&bar.acc_done);
           // the stages are also read by this block's score MMAs, which completed before its tiles were written
@@ -637,9 +666,11 @@ int launch_bwd(const mf_evo_bwd_args& a, cudaStream_t st) {
     if ((r = make_tiled_map(&mdb, dbias, MF_F32, 4, dims, str, box, 0))) return r;
   }
   const int64_t n_dq = (int64_t)a.B * a.N * a.L * a.H * a.D;
-  const size_t dq_bytes = p.ksplit > 1 ? align_up(sizeof(float) * (size_t)n_dq, 256) : 0;
+  p.dq_stream = (a.L + kT - 1) / kT > Cfg<DP>::MAX_QT;
+  const bool dq_fp32 = p.ksplit > 1 || p.dq_stream;
+  const size_t dq_bytes = dq_fp32 ? align_up(sizeof(float) * (size_t)n_dq, 256) : 0;
   p.dq_acc = reinterpret_cast<float*>(static_cast<char*>(a.workspace) + delta_bytes + acc_bytes);
-  if (p.ksplit > 1) MF_CUDA(cudaMemsetAsync(p.dq_acc, 0, sizeof(float) * (size_t)n_dq, st));
+  if (dq_fp32) MF_CUDA(cudaMemsetAsync(p.dq_acc, 0, sizeof(float) * (size_t)n_dq, st));
   TB* biasT = reinterpret_cast<TB*>(static_cast<char*>(a.workspace) + delta_bytes + acc_bytes + dq_bytes);
   p.biasT_ = biasT;
   {
@@ -661,7 +692,7 @@ int launch_bwd(const mf_evo_bwd_args& a, cudaStream_t st) {
   if (grid > p.n_items) grid = p.n_items;
   kern<<<grid, kThreads, smem, st>>>(mq, mk, mv, mg, mdb, p);
   MF_LAUNCHED("evo_bwd_tc_kernel");
-  if (p.ksplit > 1) {
+  if (dq_fp32) {
     cast_scaled_rows_kernel<T><<<(unsigned)((n_dq + 255) / 256), 256, 0, st>>>(p.dq_acc, static_cast<T*>(a.dq), n_dq);
     MF_LAUNCHED("cast_scaled_rows_kernel");
   }
@@ -685,7 +716,9 @@ extern "C" __attribute__((visibility("default"))) void mf_debug_set_timeline_bwd
 bool evo_bwd_tc_shape_ok(int L, int D) {
   const int nt = (L + kT - 1) / kT;
   // head sizes above 32 would need more shared memory than an SM has with this tiling: CUDA-core path
-  return D <= 32 && nt <= Cfg<32>::MAX_QT;
+  // up to MAX_QT query tiles keep their dQ accumulators in TMEM; longer rows stream dQ through global memory, up to
+  // the length whose row statistics still fit the shared memory (L <= 1024)
+  return D <= 32 && nt <= 8;
 }
 
 size_t evo_bwd_tc_workspace(const mf_evo_bwd_args& a) {
@@ -693,7 +726,7 @@ size_t evo_bwd_tc_workspace(const mf_evo_bwd_args& a) {
   const size_t lp4 = (size_t)(a.L + 3) / 4 * 4;
   if (!(a.dbias_dtype == MF_F32 && lp4 == (size_t)a.L)) b += align_up(sizeof(float) * (size_t)a.B * a.H * a.L * lp4, 256);
   const size_t lpad = (size_t)((a.L + kT - 1) / kT) * kT;
-  if (bwd_ksplit((int64_t)a.B * a.N * a.H, (a.L + kT - 1) / kT) > 1)
+  if (bwd_ksplit((int64_t)a.B * a.N * a.H, (a.L + kT - 1) / kT) > 1 || (a.L + kT - 1) / kT > Cfg<32>::MAX_QT)
     b += align_up(sizeof(float) * (size_t)a.B * a.N * a.L * a.H * a.D, 256);         // fp32 dQ accumulator
   b += align_up(dtype_size(a.bias_dtype) * (size_t)a.B * a.H * a.L * lpad, 256);     // transposed bias copy
   return b;

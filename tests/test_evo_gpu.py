@@ -184,3 +184,16 @@ def test_host_pipeline_matches_device_call():
     from megafold_b200 import host_pipeline
     pipe = next(iter(host_pipeline._cache.values()))
     assert pipe.graph is not None, "the three-stream schedule was not captured into a CUDA graph"
+
+
+@pytest.mark.parametrize("B,N,L,H,D", [(1, 2, 1000, 2, 32), (1, 150, 800, 1, 32), (1, 3, 1024, 1, 24)])
+def test_long_rows_stream_dq(B, N, L, H, D):
+    """More than six query tiles: the backward kernel no longer keeps every dQ accumulator on chip but adds each block's
+    product to an fp32 accumulator in global memory (with and without the key tiles spread over CTAs)."""
+    c = make_case(B, N, L, H, D, seed=L + N)
+    got = run_gpu(c, dtype=torch.bfloat16)
+    assert _lib.last_path() == "tcgen05"
+    r = rounded(c, torch.bfloat16)
+    ref = orc.evo_attention_fwd_bwd(r["q"], r["k"], r["v"], r["mask"], r["bias"], r["d_out"])
+    for g_, r_, n in zip(got, ref, NAMES):
+        assert_close_lowp(g_, r_, n)
