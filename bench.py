@@ -312,14 +312,15 @@ def run_only(args):
             dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
             torch.cuda.set_device(dev)
             dist.init_process_group("nccl", device_id=dev)
-        ms = block_bench(dev, args.L, args.steps, args.warmup)
+        ms = block_bench(dev, args.L, args.steps, args.warmup, graphed=not args.no_graph)
         if world > 1:
             t = torch.tensor([ms], device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = float(t)
         if int(os.environ.get("RANK", "0")) == 0:
             print(json.dumps({"workload": f"cfg5_pairformer_block_L{args.L}", "n_gpus": world, "scaling": "strong",
-                              "ms_fwd_bwd": ms, "tflops": block_flops(args.L) / (ms * 1e-3) / 1e12}))
+                              "ms_fwd_bwd": ms, "tflops": block_flops(args.L) / (ms * 1e-3) / 1e12,
+                              "cuda_graph": bool(getattr(block_bench, "graphed", False))}))
         if world > 1:
             dist.destroy_process_group()
         return
@@ -395,7 +396,7 @@ def extras(dev, steps=5):
     # config 5 on one GPU: the whole block at L = 768
     ms_blk = block_bench(dev, 768)
     out["cfg5_pairformer_block_L768_1gpu"] = {
-        "ms_fwd_bwd": ms_blk, "tflops": block_flops(768) / (ms_blk * 1e-3) / 1e12,
+        "ms_fwd_bwd": ms_blk, "tflops": block_flops(768) / (ms_blk * 1e-3) / 1e12, "cuda_graph": bool(getattr(block_bench, "graphed", False)),
         "note": "fused operators + torch glue (gating, output projections, residuals); rows shard over ranks with --only block"}
     return out
 
@@ -408,7 +409,7 @@ def block_flops(Lb):
     return 2 * tri + 6.0 * M * 128 * (1024 + 512) + single
 
 
-def block_bench(dev, Lb=768, steps=3, warmup=2, group=None):
+def block_bench(dev, Lb=768, steps=3, warmup=2, group=None, graphed=True):
     """BASELINE configuration 5: one Pairformer block (two triangle attentions, pair transition, single attention with
     pair bias) forward + backward in bf16 on this rank's rows of a [L, L, 128] pair representation (rows sharded
     over the process group, 5 % padding at the tail).  Returns ms per step (max over ranks is the caller's job)."""
@@ -432,7 +433,35 @@ def block_bench(dev, Lb=768, steps=3, warmup=2, group=None):
             t.grad = None
         x, s2 = m(pair, single, mask)
         torch.autograd.backward([x, s2], [d_pair, d_single])
-    return _time_cuda(step, steps, warmup)
+
+    # A block is a few hundred launches and a handful of collectives; with the rows spread over 8 GPUs the host
+    # issues them more slowly than the GPUs run them.  So the step is recorded once into a CUDA graph (kernels of the
+    # library, torch glue and NCCL collectives alike) and the timed steps replay it; if the capture is refused the
+    # step is issued directly.
+    graph = None
+    if graphed:
+        try:
+            side = torch.cuda.Stream(dev)
+            side.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(side):
+                for _ in range(2):
+                    step()
+            torch.cuda.current_stream(dev).wait_stream(side)
+            torch.cuda.synchronize(dev)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                step()
+        except Exception as e:          # noqa: BLE001
+            graph = None
+            torch.cuda.synchronize(dev)
+            print(f"[bench] CUDA graph capture of the block failed ({type(e).__name__}: {e}); issuing the step directly", file=sys.stderr)
+    ok = torch.tensor([1 if graph is not None else 0], device=dev)
+    if world > 1:
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)         # every rank replays, or none
+    if not int(ok):
+        graph = None
+    block_bench.graphed = graph is not None
+    return _time_cuda(graph.replay if graph is not None else step, steps, warmup)
 
 
 class _Null:
@@ -453,6 +482,7 @@ def main():
     ap.add_argument("--only", default="all", choices=["all", "fwd", "bwd", "lnl", "lnl_bwd", "transition", "transition_bwd", "block"],
                     help="run just one kernel family in the timed loop (for ncu captures); prints no JSON line")
     ap.add_argument("--L", type=int, default=768, help="crop length of --only block")
+    ap.add_argument("--no-graph", action="store_true", help="--only block: issue the step directly instead of replaying a CUDA graph")
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary workloads (cfg 3, cfg 4, LayernormLinear)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else max(args.warmup, 1)
