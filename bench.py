@@ -236,7 +236,7 @@ def run_ours(args):
     e2e_value = flops_per_step(total_rows) / (ms_e2e * 1e-3) / 1e12
     h2d = sum(v.numel() * v.element_size() for v in pinned.values())
     d2h = sum(t.numel() * t.element_size() for t in out_host)
-    # dominant kernel family = the slower of the two calls; roofline per BASELINE: tensor pipe
+    # dominant kernel family = the slower of the two calls; the roofline that bounds it: the tensor pipe
     dom = "backward" if ms_bwd >= ms_fwd else "forward"
     dom_ms = max(ms_bwd, ms_fwd)
     dom_flops = (10.0 if dom == "backward" else 4.0) * ROWS * H * L * L * D
@@ -335,7 +335,7 @@ def run_only(args):
 
 
 def extras(dev, steps=5):
-    """Secondary workloads of the path (BASELINE configs 3 and 4 and the LayernormLinear around config 2):
+    """Secondary workloads of the path (benchmark configurations 3 and 4 and the LayernormLinear around configuration 2):
     CUDA-event timings with inputs resident in HBM, a few repetitions each."""
     import megafold_b200 as mfb
     from megafold_b200 import _lib, workloads
@@ -410,7 +410,7 @@ def block_flops(Lb):
 
 
 def block_bench(dev, Lb=768, steps=3, warmup=2, group=None, graphed=True):
-    """BASELINE configuration 5: one Pairformer block (two triangle attentions, pair transition, single attention with
+    """Benchmark configuration 5: one Pairformer block (two triangle attentions, pair transition, single attention with
     pair bias) forward + backward in bf16 on this rank's rows of a [L, L, 128] pair representation (rows sharded
     over the process group, 5 % padding at the tail).  Returns ms per step (max over ranks is the caller's job)."""
     from megafold_b200 import row_shard

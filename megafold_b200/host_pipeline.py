@@ -13,6 +13,8 @@ schedule directly.
 """
 from __future__ import annotations
 
+import warnings
+
 import torch
 
 from .evoattention import evo_attention_backward, evo_attention_forward
@@ -85,7 +87,8 @@ class HostPipeline:
                 self.graph, self.graph_key = g, key
                 cur.wait_stream(self.s_cap)
                 return self.run(q, k, v, res_mask, pair_bias, d_out)
-            except Exception:                        # capture not possible here: keep the direct schedule
+            except Exception as e:                   # capture not possible here: keep the direct schedule
+                warnings.warn(f"CUDA graph capture of the host pipeline failed ({type(e).__name__}: {e}); issuing the schedule directly")
                 self.use_graph = False
                 self.graph = None
                 torch.cuda.synchronize(self.device)

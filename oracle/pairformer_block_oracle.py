@@ -1,7 +1,7 @@
 """CPU restatement of the long-crop benchmark block, unsharded and in plain torch.  TEST INFRASTRUCTURE ONLY:
 nothing in the product imports this file.
 
-Composition (BASELINE configuration 5): pair += TriangleAttention(starting node); pair += TriangleAttention(ending
+Composition (benchmark configuration 5, the long-crop block): pair += TriangleAttention(starting node); pair += TriangleAttention(ending
 node); pair += Transition; single += AttentionPairBias - each attention following the reference's
 ``Attention.forward`` (megafold/model/attention.py:158-210: q/k/v/gate projections of the normalised input, the
 default branch of ``Attend.forward`` :500-539 with the pair bias added and masked keys filled with -finfo.max,
