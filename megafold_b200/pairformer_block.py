@@ -107,6 +107,13 @@ class TransposeShards(torch.autograd.Function):
         if world == 1:
             return x.transpose(0, 1).contiguous()
         n = x.shape[1]
+        if n % world == 0 and dist.get_backend(group) == "nccl":
+            # equal shards: one packing copy, one all-to-all on a single buffer, one transposing copy
+            mine = n // world
+            send = x.view(mine, world, mine, *x.shape[2:]).transpose(0, 1).contiguous()      # [their rank, my i, their j]
+            recv = torch.empty_like(send)                                                    # [their rank, their i, my j]
+            dist.all_to_all_single(recv, send, group=group)
+            return recv.permute(2, 0, 1, *range(3, recv.dim())).reshape(mine, n, *x.shape[2:]).contiguous()
         spans = [row_shard(n, r, world) for r in range(world)]
         mine = spans[rank][1] - spans[rank][0]
         send = [x[:, a:b].contiguous() for a, b in spans]                       # [my i, their j]

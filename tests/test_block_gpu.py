@@ -45,3 +45,69 @@ def test_block_bf16_matches_plain_torch_block(L):
         ref = params["transition"][name[3:]].grad if name.startswith("tr_") else params[head][leaf].grad
         err = (p.grad.float().cpu() - ref).norm()
         assert err <= 3e-2 * ref.norm() + 0.05 * ref.numel() ** 0.5, f"{name}: error norm {float(err):.3g} vs {float(ref.norm()):.3g}"
+
+
+def _nccl_worker(rank, world, port, L, out):
+    import os
+    import torch.distributed as dist
+    from megafold_b200 import row_shard
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        torch.manual_seed(3)
+        m = PairformerBlock(device=dev, dtype=torch.bfloat16)
+        g = torch.Generator().manual_seed(L)
+        pair = torch.randn(L, L, 128, generator=g).to(torch.bfloat16)
+        single = torch.randn(L, 384, generator=g).to(torch.bfloat16)
+        mask = torch.ones(L, dtype=torch.bool)
+        mask[-3:] = False
+        d_pair = (torch.randn(L, L, 128, generator=g) / 4).to(torch.bfloat16)
+        d_single = (torch.randn(L, 384, generator=g) / 4).to(torch.bfloat16)
+        a, b = row_shard(L, rank, world)
+        rows = pair[a:b].to(dev).requires_grad_(True)
+        sg = single.to(dev).requires_grad_(True)
+        x, s = m(rows, sg, mask.to(dev))
+        torch.autograd.backward([x, s], [d_pair[a:b].to(dev), d_single.to(dev)])
+        torch.cuda.synchronize()
+        torch.save(dict(x=x.detach().cpu(), s=s.detach().cpu(), dpair=rows.grad.cpu(), dsingle=sg.grad.cpu(), span=(a, b)),
+                   f"{out}/r{rank}.pt")
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_block_sharded_over_two_gpus_matches_one_gpu(tmp_path):
+    """Rows of the pair representation over two GPUs (NCCL all-gather, all-to-all, all-reduce) against the same block on
+    one GPU: outputs and input gradients of every row."""
+    import os
+    import torch.multiprocessing as mp
+    L = 160
+    torch.manual_seed(3)
+    dev = "cuda"
+    m = PairformerBlock(device=dev, dtype=torch.bfloat16)
+    g = torch.Generator().manual_seed(L)
+    pair = torch.randn(L, L, 128, generator=g).to(torch.bfloat16)
+    single = torch.randn(L, 384, generator=g).to(torch.bfloat16)
+    mask = torch.ones(L, dtype=torch.bool)
+    mask[-3:] = False
+    d_pair = (torch.randn(L, L, 128, generator=g) / 4).to(torch.bfloat16)
+    d_single = (torch.randn(L, 384, generator=g) / 4).to(torch.bfloat16)
+    rows = pair.to(dev).requires_grad_(True)
+    sg = single.to(dev).requires_grad_(True)
+    x, s = m(rows, sg, mask.to(dev))
+    torch.autograd.backward([x, s], [d_pair.to(dev), d_single.to(dev)])
+    torch.cuda.synchronize()
+    port = 32500 + os.getpid() % 2000
+    mp.spawn(_nccl_worker, args=(2, port, L, str(tmp_path)), nprocs=2, join=True)
+    for r in range(2):
+        got = torch.load(os.path.join(tmp_path, f"r{r}.pt"))
+        a, b = got["span"]
+        assert_close_lowp(got["x"], x[a:b].detach().float().cpu(), f"pair out rank {r}")
+        assert_close_lowp(got["s"], s.detach().float().cpu(), f"single out rank {r}")
+        assert_close_lowp(got["dpair"], rows.grad[a:b].float().cpu(), f"d pair rank {r}")
+    # the single-track gradient is complete on every rank only for its own path; the contribution through the pair bias of the
+    # single attention flows into the pair rows, so d single is identical on both ranks and equals the one-GPU value
+    got0 = torch.load(os.path.join(tmp_path, "r0.pt"))
+    assert_close_lowp(got0["dsingle"], sg.grad.float().cpu(), "d single")
