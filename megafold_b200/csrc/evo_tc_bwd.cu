@@ -169,7 +169,7 @@ template <int N> __device__ __forceinline__ void bulk_wait() {
   asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
 }
 
-template <int DP, typename T, typename TB>
+template <int DP, typename T, typename TB, bool DQS>      // DQS: dQ streamed block by block (more query tiles than TMEM holds)
 __global__ void __launch_bounds__(kThreads, 1)
 evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mk,
                   const __grid_constant__ CUtensorMap mv, const __grid_constant__ CUtensorMap mg,
@@ -214,7 +214,7 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
   const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
   // dK/dV accumulators are double-buffered over the key tiles when the dQ accumulators leave room for it: their
   // write-out is then deferred by one block and no longer stalls the pipeline at the end of a key tile
-  const bool dbuf = p.dq_stream || p.n_t <= (512 - 256 - 4 * DP) / DP;
+  const bool dbuf = DQS || p.n_t <= (512 - 256 - 4 * DP) / DP;
   // dQ: one accumulator per query tile, complete at the end of the item; or (dq_stream) two accumulators used in turn
   // by successive blocks, each block's product added to the fp32 accumulator in global memory by the compute warps
   const uint32_t tST = tm0, tDP = tm0 + 128, tKV = tm0 + 256, tDQ = tm0 + 256 + (dbuf ? 4 : 2) * DP;
@@ -445,7 +445,7 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
         MF_TL(26);
         // the MMAs of the previous block have finished reading the P^T / dS^T tiles?
         if (g > 0) wait_or_flag(&bar.acc_done, (g - 1) & 1, abort_flag);
-        if (p.dq_stream && !(jt == jt0 && it == 0)) stream_dq(g - 1, it == 0 ? nt - 1 : it - 1, b, n, h);
+        if constexpr (DQS) { if (!(jt == jt0 && it == 0)) stream_dq(g - 1, it == 0 ? nt - 1 : it - 1, b, n, h); }
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch) {
           const uint32_t off = (w >> 1) * 16384 + swz_offset(r, (w & 1) * 4 + ch, 128);
@@ -476,8 +476,8 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
     wait_or_flag(&bar.acc_done, (g - 1) & 1, abort_flag);
     if (pend_j >= 0) { store_kv(pend_kc, pend_j, pend_b, pend_n, pend_h); pend_j = -1; }
     tc_fence_after();
-    if (p.dq_stream) stream_dq(g - 1, nt - 1, b, n, h);     // the last block of the item
-    for (int it = w; it < nt && !p.dq_stream; it += 4) {
+    if constexpr (DQS) stream_dq(g - 1, nt - 1, b, n, h);     // the last block of the item
+    for (int it = w; it < nt && !DQS; it += 4) {
       const int i = it * kT + r;
       uint32_t o32[DP];
 #pragma unroll
@@ -540,8 +540,8 @@ evo_bwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
             mma_ss_lh(tDK_of(kv), ds_lo + (ks >> 2) * (16384 / 16) + (ks & 3) * 2, hi_t, q_lo + ks * kstep, hi_o, id_kv, it > 0 || ks > 0);
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks)      // dQ_i += dS K_j   (A = dS^T tile read MN-major: M = queries)
-            mma_ss_lh(tDQ + (p.dq_stream ? (g & 1) : it) * DP, dst_lo + ks * (2048 / 16), hi_t, k_lo + ks * kstep, hi_o, id_q,
-                      p.dq_stream ? ks > 0 : (jt > jt0 || ks > 0));
+            mma_ss_lh(tDQ + (DQS ? (g & 1) : it) * DP, dst_lo + ks * (2048 / 16), hi_t, k_lo + ks * kstep, hi_o, id_q,
+                      DQS ? ks > 0 : (jt > jt0 || ks > 0));
           MF_TL(45);
           tc_commit(&bar.acc_done);
           // the stages are also read by this block's score MMAs, which completed before its tiles were written
@@ -686,11 +686,17 @@ int launch_bwd(const mf_evo_bwd_args& a, cudaStream_t st) {
   MF_LAUNCHED("evo_delta_tc_kernel");
   MF_CUDA(cudaMemsetAsync(dbias, 0, sizeof(float) * nb, st));
   const size_t smem = 1024 + 2 * kTileP + 10 * (size_t)C::TILEB + 4 * sizeof(float) * p.lpad + 16 * 4096;
-  auto kern = evo_bwd_tc_kernel<DP, T, TB>;
-  MF_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int grid = sm_count();
   if (grid > p.n_items) grid = p.n_items;
-  kern<<<grid, kThreads, smem, st>>>(mq, mk, mv, mg, mdb, p);
+  if (p.dq_stream) {
+    auto kern = evo_bwd_tc_kernel<DP, T, TB, true>;
+    MF_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kern<<<grid, kThreads, smem, st>>>(mq, mk, mv, mg, mdb, p);
+  } else {
+    auto kern = evo_bwd_tc_kernel<DP, T, TB, false>;
+    MF_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kern<<<grid, kThreads, smem, st>>>(mq, mk, mv, mg, mdb, p);
+  }
   MF_LAUNCHED("evo_bwd_tc_kernel");
   if (dq_fp32) {
     cast_scaled_rows_kernel<T><<<(unsigned)((n_dq + 255) / 256), 256, 0, st>>>(p.dq_acc, static_cast<T*>(a.dq), n_dq);
