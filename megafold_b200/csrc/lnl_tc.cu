@@ -175,6 +175,16 @@ lnl_fwd_tc_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant_
       for (int nt = 0; nt < p.n_nt; ++nt, ++acc_cnt) {
         const int ab = acc_cnt & 1;
         const int n0 = nt * kNT + half * 64;
+        // the linear bias of my 64 columns, requested before the wait for the accumulator so that its latency is hidden
+        // (loaded inside the conversion loop, each of the eight loads exposed its full latency: 1300 of the 2400 cycles
+        // an epilogue warp spent per tile)
+        const T* bias = static_cast<const T*>(p.bias);
+        const bool bias_vec = bias && (n0 + 64 <= p.N) && ((reinterpret_cast<uintptr_t>(bias) & 15) == 0);
+        uint4 braw[8];
+        if (bias_vec) {
+#pragma unroll
+          for (int ch = 0; ch < 8; ++ch) braw[ch] = __ldg(reinterpret_cast<const uint4*>(bias + n0 + ch * 8));
+        }
         wait_or_flag(&bar.acc_full[ab], (acc_cnt >> 1) & 1, abort_flag);
         tc_fence_after();
         uint32_t acc[64];
@@ -189,13 +199,11 @@ lnl_fwd_tc_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant_
         uint8_t* ys = sY + ab * Y_BYTES + half * (kRows * 128);
         if (lane == 0) bulk_wait_group_read<1>();
         if (__any_sync(0xffffffffu, *abort_flag)) { dead = true; break; }
-        const T* bias = static_cast<const T*>(p.bias);
-        const bool bias_vec = bias && (n0 + 64 <= p.N) && ((reinterpret_cast<uintptr_t>(bias) & 15) == 0);
 #pragma unroll
         for (int ch = 0; ch < 8; ++ch) {
           float b8[8];
           if (bias_vec) {
-            const uint4 u = __ldg(reinterpret_cast<const uint4*>(bias + n0 + ch * 8));
+            const uint4 u = braw[ch];
             const float2 f0 = Pack2<T>::unpack(u.x), f1 = Pack2<T>::unpack(u.y), f2 = Pack2<T>::unpack(u.z), f3 = Pack2<T>::unpack(u.w);
             b8[0] = f0.x; b8[1] = f0.y; b8[2] = f1.x; b8[3] = f1.y; b8[4] = f2.x; b8[5] = f2.y; b8[6] = f3.x; b8[7] = f3.y;
           } else {
