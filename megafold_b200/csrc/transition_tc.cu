@@ -8,7 +8,7 @@
 //                ([dim rows][64 hidden], K-major B operand).
 //   row threads  (warps 8-11, a warpgroup of their own) LayerNorm of the next tile in place in shared memory, as in
 //                the LayernormLinear kernel, ahead of the MMAs by as much as the ring of X tiles allows.
-//   MMA thread   GEMM1 of chunk c: H_a, H_g = A W1 blocks (2 x dim/16 MMAs, N = 64) into one of two TMEM buffers;
+//   MMA threads  (warp 12 and warp 14, one GEMM each) GEMM1 of chunk c: H_a, H_g = A W1 blocks (2 x dim/16 MMAs, N = 64) into one of two TMEM buffers;
 //                GEMM2 of chunk c-1: Y += G W2-block^T (4 MMAs, N = dim) once the workers have written G.
 //   workers      (warps 0-7) thread (row, half): 32 columns of H_a and H_g from TMEM, g = silu(gate) * value with
 //                one MUFU op per element (silu(x) = x/2 * (1 + tanh(x/2))), packed 16-bit G tile to shared memory
@@ -254,22 +254,7 @@ transition_fwd_tc_kernel(const __grid_constant__ CUtensorMap mx, const __grid_co
   if (warp == 12 && lane == 0) {
     // ------------------------------------------------------------------------------------ MMA issuer
     const uint32_t id1 = idesc_f16(128, kHC, p.ab_fmt, 0, 1);     // GEMM1: A K-major, B (W1 block) MN-major, N = 64
-    const uint32_t id2 = idesc_f16(128, K, p.ab_fmt, 0, 0);       // GEMM2: A (G) K-major, B (W2 block) K-major, N = dim
     uint32_t ch_cnt = 0;
-    auto gemm2 = [&](uint32_t cc, bool first_of_tile, int t) {    // Y (+)= G(cc) W2-block(cc)^T
-      const int gb = cc & 1, ws = cc % kWStages;
-      wait_or_flag(&bar.w2_full[ws], (cc / kWStages) & 1, abort_flag);
-      wait_or_flag(&bar.g_full[gb], (cc >> 1) & 1, abort_flag);
-      if (first_of_tile && t > 0) wait_or_flag(&bar.y_empty, (t - 1) & 1, abort_flag);
-      tc_fence_after();
-      if (*abort_flag) return;
-      const uint32_t g_lo = desc_lo(smem_u32(sG + gb * G_BYTES), 16), w2_lo = desc_lo(smem_u32(sW + ws * W_BYTES + 2 * W1B), 16);
-#pragma unroll
-      for (int ks = 0; ks < kHC / 16; ++ks)
-        mma_ss_lh(tY, g_lo + ks * 2, desc_hi(1024, kSw128), w2_lo + ks * 2, desc_hi(1024, kSw128), id2, !first_of_tile || ks > 0);
-      tc_commit(&bar.g_empty[gb]);
-      tc_commit(&bar.w2_empty[ws]);
-    };
     for (int t = 0; t < my_tiles && !*abort_flag; ++t) {
       const int buf = t % kAStages;
       wait_or_flag(&bar.a_full[buf], (t / kAStages) & 1, abort_flag);
@@ -291,12 +276,34 @@ transition_fwd_tc_kernel(const __grid_constant__ CUtensorMap mx, const __grid_co
                     w1g_lo + ks * (2048 / 16), desc_hi(1024, kSw128), id1, ks > 0);
         tc_commit(&bar.h_full[hb]);
         tc_commit(&bar.w1_empty[ws]);
-        if (c > 0) gemm2(ch_cnt - 1, c == 1, t);
       }
       if (*abort_flag) break;
-      gemm2(ch_cnt - 1, nch == 1, t);
-      tc_commit(&bar.y_full);
       tc_commit(&bar.a_empty[buf]);
+    }
+  } else if (warp == 14 && lane == 0) {
+    // ------------------------------------------------------------------------------------ second MMA issuer: GEMM2.
+    // One thread issuing both GEMMs spends a chunk's time on its own waits, descriptors and commits (about 3200 cycles
+    // per chunk measured, against 1250 of worker time); two threads run those two instruction streams side by side.
+    const uint32_t id2 = idesc_f16(128, K, p.ab_fmt, 0, 0);       // A (G) K-major, B (W2 block) K-major, N = dim
+    auto gemm2 = [&](uint32_t cc, bool first_of_tile, int t) {    // Y (+)= G(cc) W2-block(cc)^T
+      const int gb = cc & 1, ws = cc % kWStages;
+      wait_or_flag(&bar.w2_full[ws], (cc / kWStages) & 1, abort_flag);
+      wait_or_flag(&bar.g_full[gb], (cc >> 1) & 1, abort_flag);
+      if (first_of_tile && t > 0) wait_or_flag(&bar.y_empty, (t - 1) & 1, abort_flag);
+      tc_fence_after();
+      if (*abort_flag) return;
+      const uint32_t g_lo = desc_lo(smem_u32(sG + gb * G_BYTES), 16), w2_lo = desc_lo(smem_u32(sW + ws * W_BYTES + 2 * W1B), 16);
+#pragma unroll
+      for (int ks = 0; ks < kHC / 16; ++ks)
+        mma_ss_lh(tY, g_lo + ks * 2, desc_hi(1024, kSw128), w2_lo + ks * 2, desc_hi(1024, kSw128), id2, !first_of_tile || ks > 0);
+      tc_commit(&bar.g_empty[gb]);
+      tc_commit(&bar.w2_empty[ws]);
+    };
+    uint32_t ch_cnt = 0;
+    for (int t = 0; t < my_tiles && !*abort_flag; ++t) {
+      for (int c = 0; c < nch && !*abort_flag; ++c, ++ch_cnt) gemm2(ch_cnt, c == 0, t);
+      if (*abort_flag) break;
+      tc_commit(&bar.y_full);
     }
   } else if (warp == 13 && lane == 0) {
     // ------------------------------------------------------------------------------------ TMA producer
