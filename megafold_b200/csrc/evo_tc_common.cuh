@@ -20,6 +20,9 @@ constexpr float kLn2 = 0.6931471805599453f;
 // Waits for a phase; on expiry raises the CTA's abort flag and returns (the caller carries on to its
 // next group barrier, where everybody sees the flag and leaves the loop).
 __device__ __forceinline__ void wait_or_flag(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  // cheap non-blocking probe first: try_wait costs ~270 cycles even when the phase is already complete (measured with
+  // clock stamps in the MMA issuer threads), and that is the common case for the threads that issue MMAs and TMA copies
+  if (mbar_test(bar, parity)) return;
   for (uint32_t i = 0; i < kWaitCap; ++i) {
     if (mbar_try_wait(bar, parity)) return;
     if ((i & 63u) == 63u && *abort_flag) return;

@@ -13,10 +13,10 @@
 //                ([128 rows][32 columns], 64-byte swizzle; three stages).
 //   warp 14      TMA stores of the dh and g tiles of every chunk.
 //   warps 8-11   LayerNorm of the X tile in place (thread per row), one tile ahead.
-//   warp 12      MMAs.  Per chunk c: H(c) = A W1blocks (8 x N=64, the two blocks as the two swizzle atoms of one
-//                MN-major B operand) and DG(c) = dY W2block (8 x N=32) into one of two TMEM buffers; then, once the
-//                workers have written dh(c-1): dyln += dh(c-1) [W1 value block; W1 gate block]^T (4 x N=128; the same
-//                shared-memory blocks read K-major).
+//   warp 12      MMAs of H(c) = A W1blocks (8 x N=64, the two blocks as the two swizzle atoms of one MN-major B operand)
+//                and DG(c) = dY W2block (8 x N=32) into one of two TMEM buffers.
+//   warp 15      MMAs of dyln += dh(c) [W1 value block; W1 gate block]^T (4 x N=128; the same shared-memory blocks read
+//                K-major) once the workers have written dh(c).
 //   warps 0-7    workers, thread (row, half): 16 value, 16 gate, 16 dg columns from TMEM; g, dh in registers with one
 //                MUFU op per element; 16-bit tiles to shared memory: dh as the K-major A operand of the dyln GEMM
 //                (column order inside a chunk: [value 0-15 | gate 0-15 | value 16-31 | gate 16-31]) and both as
@@ -241,24 +241,7 @@ transition_bwd_tc_kernel(const __grid_constant__ CUtensorMap mx, const __grid_co
       // -------------------------------------------------------------------------------- MMA issuer
       const uint32_t id_h = idesc_f16(128, 64, p.ab_fmt, 0, 1);     // A K-major, B = W1 value|gate blocks MN-major, N = 64
       const uint32_t id_g = idesc_f16(128, 32, p.ab_fmt, 0, 1);     // A = dY K-major, B = W2 block MN-major, N = 32
-      const uint32_t id_a = idesc_f16(128, 128, p.ab_fmt, 0, 0);    // A = dh K-major, B = W1 blocks K-major, N = dim
       uint32_t ch_cnt = 0;
-      auto acc_gemm = [&](uint32_t cc, bool first_of_tile, int t) {  // dyln (+)= dh(cc) [W1v; W1g](cc)^T
-        const int hb = cc & 1;
-        wait_or_flag(&bar.dh_full[hb], (cc >> 1) & 1, abort_flag);
-        if (first_of_tile && t > 0) wait_or_flag(&bar.acc_empty, (t - 1) & 1, abort_flag);
-        tc_fence_after();
-        if (*abort_flag) return;
-        const uint32_t dh_lo = desc_lo(smem_u32(sDH + hb * DH_BYTES), 16), w_lo = desc_lo(smem_u32(sW + (cc % kWS) * W_BYTES), 16);
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-          // k-step ks covers dh columns ks*16 .. +15: value (ks even) or gate (ks odd) columns (ks / 2) * 16 .. of the chunk
-          mma_ss_lh(tACC, dh_lo + ((ks * 32) >> 4), desc_hi(1024, kSw128), w_lo + (((ks & 1) * WB + (ks >> 1) * 32) >> 4), desc_hi(512, kSw64),
-                    id_a, !first_of_tile || ks > 0);
-        }
-        tc_commit(&bar.dh_empty[hb]);
-        tc_commit(&bar.w_empty[cc % kWS]);
-      };
       for (int t = 0; t < my_tiles && !*abort_flag; ++t) {
         const int buf = t & 1;
         wait_or_flag(&bar.a_full[buf], (t >> 1) & 1, abort_flag);
@@ -281,12 +264,35 @@ transition_bwd_tc_kernel(const __grid_constant__ CUtensorMap mx, const __grid_co
             mma_ss_lh(tHD + hb * 128 + 64, y_lo + (((ks >> 2) * (kRows * 128) + (ks & 3) * 32) >> 4), desc_hi(1024, kSw128),
                       wg_lo + ((ks * 1024) >> 4), desc_hi(512, kSw64), id_g, ks > 0);
           tc_commit(&bar.hd_full[hb]);
-          if (c > 0) acc_gemm(ch_cnt - 1, c == 1, t);
         }
         if (*abort_flag) break;
         tc_commit(&bar.a_empty[buf]);      // the H / DG MMAs of this tile are all issued: X and dY tiles are free when they complete
         tc_commit(&bar.dy_empty);
-        acc_gemm(ch_cnt - 1, nch == 1, t);
+      }
+    } else if (warp == 15 && lane == 0) {
+      // -------------------------------------------------------------------------------- second MMA issuer: the dyln GEMMs
+      // (a single issuing thread spends more time on its own waits, descriptors and commits than the MMAs take)
+      const uint32_t id_a = idesc_f16(128, 128, p.ab_fmt, 0, 0);    // A = dh K-major, B = W1 blocks K-major, N = dim
+      auto acc_gemm = [&](uint32_t cc, bool first_of_tile, int t) {  // dyln (+)= dh(cc) [W1v; W1g](cc)^T
+        const int hb = cc & 1;
+        wait_or_flag(&bar.dh_full[hb], (cc >> 1) & 1, abort_flag);
+        if (first_of_tile && t > 0) wait_or_flag(&bar.acc_empty, (t - 1) & 1, abort_flag);
+        tc_fence_after();
+        if (*abort_flag) return;
+        const uint32_t dh_lo = desc_lo(smem_u32(sDH + hb * DH_BYTES), 16), w_lo = desc_lo(smem_u32(sW + (cc % kWS) * W_BYTES), 16);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+          // k-step ks covers dh columns ks*16 .. +15: value (ks even) or gate (ks odd) columns (ks / 2) * 16 .. of the chunk
+          mma_ss_lh(tACC, dh_lo + ((ks * 32) >> 4), desc_hi(1024, kSw128), w_lo + (((ks & 1) * WB + (ks >> 1) * 32) >> 4), desc_hi(512, kSw64),
+                    id_a, !first_of_tile || ks > 0);
+        }
+        tc_commit(&bar.dh_empty[hb]);
+        tc_commit(&bar.w_empty[cc % kWS]);
+      };
+      uint32_t ch_cnt = 0;
+      for (int t = 0; t < my_tiles && !*abort_flag; ++t) {
+        for (int c = 0; c < nch && !*abort_flag; ++c, ++ch_cnt) acc_gemm(ch_cnt, c == 0, t);
+        if (*abort_flag) break;
         tc_commit(&bar.acc_full);
       }
     } else if (warp == 14 && lane == 0) {
