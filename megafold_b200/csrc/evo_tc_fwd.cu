@@ -32,8 +32,9 @@ using namespace tcx;
 constexpr int kQT = 128, kKT = 128;
 constexpr int kThreads = 256;
 constexpr int kVS = 2;        // V ring stages per stream
-constexpr int kBC = 6;        // bias chunk ring per stream (4 chunks per key tile)
-constexpr int kBCW = 32;      // columns per bias chunk
+constexpr int kBC = 3;        // bias chunk ring per stream (2 chunks per key tile: every TMA issue costs the
+                              // issuing thread, a lane of a compute warp, some hundreds of cycles)
+constexpr int kBCW = 64;      // columns per bias chunk (128-byte rows)
 constexpr int kBChunkBytes = 128 * kBCW * 2;
 
 template <int DP> struct Cfg {
@@ -201,13 +202,13 @@ evo_fwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
   };
   auto pump_b = [&]() {
     if (!BTMA) return;
-    while (cb_next < g_total * 4) {
+    while (cb_next < g_total * (kKT / kBCW)) {
       if (puse > 0 && !mbar_test(&bar.b_empty[pslot], (puse - 1) & 1)) break;
       mbar_expect_tx(&bar.b_full[pslot], kBChunkBytes);
       tma_load_4d(sB + pslot * kBChunkBytes, &mb, &bar.b_full[pslot], cbias.t * kKT + cb_quarter * kBCW, cbias.qt * kQT,
                   cbias.h, cbias.b * p.bias_b_mul);
       ++cb_next;
-      if (++cb_quarter == 4) { cb_quarter = 0; cursor_next_tile(cbias); }
+      if (++cb_quarter == kKT / kBCW) { cb_quarter = 0; cursor_next_tile(cbias); }
       if (++pslot == kBC) { pslot = 0; ++puse; }
     }
   };
@@ -325,17 +326,20 @@ evo_fwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
     for (int cb = 0; cb < 4; ++cb) {
       float bv[32];
       if (BTMA) {
-        wait_or_flag(&bar.b_full[bslot], bphase, abort_flag);
+        // a chunk holds 64 columns: two passes of this loop read its two halves
+        if ((cb & 1) == 0) wait_or_flag(&bar.b_full[bslot], bphase, abort_flag);
         const uint8_t* chunk = sB + bslot * kBChunkBytes;
 #pragma unroll
         for (int pc = 0; pc < 4; ++pc) {
-          const uint4 x = *reinterpret_cast<const uint4*>(chunk + swz_offset(r, pc, 64));
+          const uint4 x = *reinterpret_cast<const uint4*>(chunk + swz_offset(r, (cb & 1) * 4 + pc, 128));
           float2 a = Pack2<TB>::unpack(x.x), b2 = Pack2<TB>::unpack(x.y), c2 = Pack2<TB>::unpack(x.z), d2 = Pack2<TB>::unpack(x.w);
           bv[8 * pc] = a.x; bv[8 * pc + 1] = a.y; bv[8 * pc + 2] = b2.x; bv[8 * pc + 3] = b2.y;
           bv[8 * pc + 4] = c2.x; bv[8 * pc + 5] = c2.y; bv[8 * pc + 6] = d2.x; bv[8 * pc + 7] = d2.y;
         }
-        mbar_arrive(&bar.b_empty[bslot]);
-        if (++bslot == kBC) { bslot = 0; bphase ^= 1; }
+        if (cb & 1) {
+          mbar_arrive(&bar.b_empty[bslot]);
+          if (++bslot == kBC) { bslot = 0; bphase ^= 1; }
+        }
       } else {
         if (p.bias_fast && (j0 + kKT <= p.L)) load_bias32_fast<TB>(brow + j0 + cb * 32, bv);
         else load_bias32_slow<TB>(brow, p.bs[3], j0 + cb * 32, p.L, bv);
