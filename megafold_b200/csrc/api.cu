@@ -59,7 +59,7 @@ int mf_evo_fwd(const mf_evo_fwd_args* args, void* stream) {
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (!(a.flags & MF_FLAG_FORCE_SIMT) &&
       evo_tc_supported(a.B, a.N, a.L, a.H, a.D, a.dtype, a.q_strides, a.k_strides, a.v_strides, a.q, a.k, a.v)) {
-    r = evo_fwd_tc(a, st);
+    r = (evo_fwd_ws_supported(a) && !debug_old_evo(0)) ? evo_fwd_ws(a, st) : evo_fwd_tc(a, st);
     if (r == MF_OK) set_last_path("tcgen05");
     return r;
   }
@@ -73,9 +73,12 @@ static bool evo_bwd_use_tc(const mf_evo_bwd_args& a) {
          evo_tc_supported(a.B, a.N, a.L, a.H, a.D, a.dtype, a.q_strides, a.k_strides, a.v_strides, a.q, a.k, a.v);
 }
 
+static bool evo_bwd_use_ws(const mf_evo_bwd_args& a) { return evo_bwd_ws_shape_ok(a.L, a.D) && !debug_old_evo(1); }
+
 size_t mf_evo_bwd_workspace_bytes(const mf_evo_bwd_args* args) {
   if (!args) return 0;
-  return evo_bwd_use_tc(*args) ? evo_bwd_tc_workspace(*args) : evo_bwd_simt_workspace(*args);
+  if (!evo_bwd_use_tc(*args)) return evo_bwd_simt_workspace(*args);
+  return evo_bwd_use_ws(*args) ? evo_bwd_ws_workspace(*args) : evo_bwd_tc_workspace(*args);
 }
 
 int mf_evo_bwd(const mf_evo_bwd_args* args, void* stream) {
@@ -93,7 +96,7 @@ int mf_evo_bwd(const mf_evo_bwd_args* args, void* stream) {
   r = check_device(); if (r) return r;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (evo_bwd_use_tc(a)) {
-    r = evo_bwd_tc(a, st);
+    r = evo_bwd_use_ws(a) ? evo_bwd_ws(a, st) : evo_bwd_tc(a, st);
     if (r == MF_OK) set_last_path("tcgen05");
     return r;
   }

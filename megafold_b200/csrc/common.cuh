@@ -129,8 +129,14 @@ bool evo_bwd_tc_available();
 bool evo_bwd_tc_shape_ok(int L, int D);   // the dQ accumulators of all query tiles must fit in TMEM
 int tc_async_status();
 int evo_fwd_tc(const mf_evo_fwd_args& a, cudaStream_t st);
+bool evo_fwd_ws_supported(const mf_evo_fwd_args& a);
+int evo_fwd_ws(const mf_evo_fwd_args& a, cudaStream_t st);
+bool debug_old_evo(int which);
 int evo_bwd_tc(const mf_evo_bwd_args& a, cudaStream_t st);
 size_t evo_bwd_tc_workspace(const mf_evo_bwd_args& a);
+bool evo_bwd_ws_shape_ok(int L, int D);
+int evo_bwd_ws(const mf_evo_bwd_args& a, cudaStream_t st);
+size_t evo_bwd_ws_workspace(const mf_evo_bwd_args& a);
 
 int lnl_fwd_simt(const mf_lnl_fwd_args& a, cudaStream_t st);
 bool lnl_fwd_tc_supported(const mf_lnl_fwd_args& a);

@@ -1,0 +1,975 @@
+// Pair-biased masked attention backward on the tensor cores (tcgen05 + TMEM + TMA), head sizes up to 32.
+//
+// Two kernels share the transposed-score scheme (keys on the TMEM lanes):
+//
+//   S''^T = K_j Q_i^T + sqrt(D) * bias^T        dP^T = V_j dO_i^T          (tcgen05.mma into TMEM; the bias term is
+//   P^T   = 2^(c1 * S''^T + mask_j - lse2_i)    dS^T = P^T (dP^T - delta_i)  itself a product with alpha * I, see
+//                                                                            evo_tc_common.cuh)
+//
+// evo_bwd_ws_kernel (dQ, dK, dV).  A persistent CTA owns a (b, n, h) - or a range of its key tiles - and walks the
+// key tiles j and, inside, the query tiles i in HALF blocks of [128 keys x 64 queries].  Two teams of eight compute
+// warps take alternate half blocks, each with its own score buffers in TMEM, so that the tensor pipe works on one
+// team's products while the other team exponentiates.  A thread (key row, 32 query columns) writes packed 16-bit
+// P^T and dS^T back over the scores it has just read: they are the TMEM A operands of  dV_j += P^T dO_i  and
+// dK_j += dS^T Q_i.  dS^T also goes to a shared-memory tile, read MN-major as the A operand of  dQ_i += dS K_j.
+// dK_j / dV_j accumulate in TMEM over the query tiles and dQ_i over the key tiles (or, for long rows and split
+// items, leave block by block through fp32 adds in global memory).
+//
+// evo_dbias_ws_kernel (dBias = sum of dS over the N rows that share the bias).  A CTA keeps ONE (b, h, i tile,
+// j tile) and walks a range of rows n: scores and dP for row n+1 are produced while the 16 compute warps turn row n
+// into dS and add it to register accumulators; nothing is reduced through memory until the range is done.  Ranges
+// are summed in a fixed order afterwards, so dBias is bit-reproducible.
+//
+// delta_i = rowsum(dO_i * O_i) comes from a small pre-kernel, bias^T from a transposing copy.  All waits are bounded
+// (tc.cuh); on expiry the CTA runs dry without touching global memory and the host sees mf_async_status() != 0.
+#include <type_traits>
+
+#include "evo_tc_common.cuh"
+
+namespace mf {
+namespace {
+using namespace tcx;
+
+constexpr int kT = 128;             // tile edge (keys and queries)
+constexpr int kHalf = 64;           // queries per half block
+constexpr int kComputeWarps = 16;
+constexpr int kThreads = (kComputeWarps + 4) * 32;
+constexpr int kTileB = 128 * 64;    // [128 x 32] 16-bit operand tile, 64-byte rows, 64B swizzle
+constexpr int kAtomB = 128 * 128;   // [128 x 64] 16-bit tile, 128-byte rows, 128B swizzle (bias^T atoms, dS^T atoms)
+constexpr int kDP = 32;             // padded head size
+
+struct BwdWsP {
+  int B, N, L, H, D;
+  int n_t, n_items, lpad;
+  int ksplit;            // work items per (b, n, h): the key tiles are split into this many ranges
+  int dq_stream;         // dQ leaves the SM block by block (more query tiles than TMEM holds)
+  int dbuf;              // dK/dV accumulators double-buffered over the key tiles
+  float* dq_acc;         // fp32 [B,N,L,H,D] accumulator of dQ when ksplit > 1 or dq_stream
+  float c1, scale, inv_L;
+  uint32_t fmt, bfmt;
+  int n_alpha; float alpha[2];
+  int bias_b_mul;
+  const void* mask; int64_t ms[3]; int mask_dtype;
+  const float* lse; const float* delta;
+  void *dq, *dk, *dv;
+  int* status;
+};
+
+struct Bars {
+  uint64_t kv_full[2], kv_empty[2], qd_full[3], qd_empty[3], bt_full[3], bt_empty[3];
+  uint64_t sd_ready[2], written[2], buf_free[2], blk_done[2];
+  uint64_t st_full[2], st_empty[2];          // per-item statistics (lse, delta) in two buffers
+  uint64_t kv_drained, dq_drained[2];
+  int special[2];
+};
+
+// delta[b,n,h,i] = sum_d dO * O; one thread per (b,n,i,h) row, 16-byte loads (D is a multiple of 8)
+template <typename T>
+__global__ void evo_delta_ws_kernel(const T* __restrict__ o, const T* __restrict__ d_o, float* __restrict__ delta,
+                                    int64_t rows, int L, int H, int D) {
+  const int64_t row = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= rows) return;
+  const uint4* po = reinterpret_cast<const uint4*>(o + row * D);
+  const uint4* pg = reinterpret_cast<const uint4*>(d_o + row * D);
+  float s = 0.f;
+  for (int c = 0; c < D / 8; ++c) {
+    const uint4 a = __ldg(po + c), g = __ldg(pg + c);
+    const uint32_t av[4] = {a.x, a.y, a.z, a.w}, gv[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 x = Pack2<T>::unpack(av[e]), y = Pack2<T>::unpack(gv[e]);
+      s = fmaf(x.x, y.x, s); s = fmaf(x.y, y.y, s);
+    }
+  }
+  const int h = (int)(row % H); const int64_t t = row / H; const int i = (int)(t % L); const int64_t bn = t / L;
+  delta[(bn * H + h) * L + i] = s;
+}
+
+// biasT[b][h][j][i] = bias[b][h][i][j] in the 16-bit type TO, rows padded to `lpad` entries (the padding is zeroed by
+// the caller).  The kernels work with keys on the TMEM lanes, so the tile they need has the queries contiguous.
+template <typename TB, typename TO>
+__global__ void transpose_bias_ws_kernel(const TB* __restrict__ bias, TO* __restrict__ biasT, int H, int L, int lpad,
+                                         int64_t sb, int64_t sh, int64_t si, int64_t sj) {
+  __shared__ float tile[32][33];
+  const int bh = blockIdx.z, b = bh / H, h = bh % H;
+  const int i0 = blockIdx.y * 32, j0 = blockIdx.x * 32;
+  for (int k = threadIdx.y; k < 32; k += blockDim.y) {
+    const int i = i0 + k, j = j0 + threadIdx.x;
+    if (i < L && j < L) tile[k][threadIdx.x] = to_f(bias[b * sb + h * sh + (int64_t)i * si + (int64_t)j * sj]);
+  }
+  __syncthreads();
+  for (int k = threadIdx.y; k < 32; k += blockDim.y) {
+    const int j = j0 + k, i = i0 + threadIdx.x;
+    if (i < L && j < L) biasT[((int64_t)bh * L + j) * lpad + i] = from_f<TO>(tile[threadIdx.x][k]);
+  }
+}
+
+// P^T and dS^T of one thread: key row (mask term `mk`), 32 query columns whose statistics sit at l2 / dl.
+// sr: c1-unscaled scores S''^T, dr: dP^T.  Results packed two queries per word.
+template <typename T, bool CAREFUL>
+__device__ __forceinline__ void p_and_ds(const uint32_t (&sr)[32], const uint32_t (&dr)[32], const float* __restrict__ l2,
+                                         const float* __restrict__ dl, float c1, float mk, bool key_ok, bool masked_key,
+                                         float inv_L, uint32_t (&pp)[16], uint32_t (&dd)[16]) {
+  const float2 c1c1 = make_float2(c1, c1), mm = make_float2(mk, mk);
+#pragma unroll
+  for (int c4 = 0; c4 < 8; ++c4) {
+    const float4 l4 = *reinterpret_cast<const float4*>(l2 + c4 * 4);
+    const float4 d4 = *reinterpret_cast<const float4*>(dl + c4 * 4);
+    const float2 x0 = fma2(make_float2(__uint_as_float(sr[c4 * 4]), __uint_as_float(sr[c4 * 4 + 1])), c1c1, sub2(mm, make_float2(l4.x, l4.y)));
+    const float2 x1 = fma2(make_float2(__uint_as_float(sr[c4 * 4 + 2]), __uint_as_float(sr[c4 * 4 + 3])), c1c1, sub2(mm, make_float2(l4.z, l4.w)));
+    float2 p0 = make_float2(ex2f(x0.x), ex2f(x0.y)), p1 = make_float2(ex2f(x1.x), ex2f(x1.y));
+    if (CAREFUL) {       // a fully masked query row is uniform over the keys of the row
+      const float u = key_ok ? inv_L : 0.f;
+      if (l4.x <= -3e38f) p0.x = u;
+      if (l4.y <= -3e38f) p0.y = u;
+      if (l4.z <= -3e38f) p1.x = u;
+      if (l4.w <= -3e38f) p1.y = u;
+    }
+    float2 s0 = mul2(p0, sub2(make_float2(__uint_as_float(dr[c4 * 4]), __uint_as_float(dr[c4 * 4 + 1])), make_float2(d4.x, d4.y)));
+    float2 s1 = mul2(p1, sub2(make_float2(__uint_as_float(dr[c4 * 4 + 2]), __uint_as_float(dr[c4 * 4 + 3])), make_float2(d4.z, d4.w)));
+    if (CAREFUL && masked_key) { s0 = make_float2(0.f, 0.f); s1 = s0; }      // no gradient through a masked logit
+    pp[c4 * 2] = Pack2<T>::pack(p0.x, p0.y); pp[c4 * 2 + 1] = Pack2<T>::pack(p1.x, p1.y);
+    dd[c4 * 2] = Pack2<T>::pack(s0.x, s0.y); dd[c4 * 2 + 1] = Pack2<T>::pack(s1.x, s1.y);
+  }
+}
+
+template <typename T, typename TB, bool DQS>      // DQS: dQ streamed block by block through global memory
+__global__ void __launch_bounds__(kThreads, 1)
+evo_bwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mk,
+                  const __grid_constant__ CUtensorMap mv, const __grid_constant__ CUtensorMap mg,
+                  const __grid_constant__ CUtensorMap mbt, const BwdWsP p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* sDS = smem;                          // [2 blocks][2 atoms]: dS^T tiles for the dQ product
+  uint8_t* sBT = sDS + 4 * kAtomB;              // bias^T atoms, ring of 3
+  uint8_t* sKV = sBT + 3 * kAtomB;              // [2 stages][K, V]
+  uint8_t* sQD = sKV + 4 * kTileB;              // [3 stages][Q, dO]
+  uint8_t* sI = sQD + 6 * kTileB;               // alpha * I, two terms
+  float* lse2 = reinterpret_cast<float*>(sI + 2048);
+  float* dlt = lse2 + 2 * p.lpad;               // lse2, dlt: two buffers each (items alternate)
+
+  __shared__ Bars bar;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_s;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {
+    abort_s = 0;
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bar.kv_full[i], 1); mbar_init(&bar.kv_empty[i], 1);
+      mbar_init(&bar.sd_ready[i], 1); mbar_init(&bar.written[i], kComputeWarps / 2);
+      mbar_init(&bar.buf_free[i], 1); mbar_init(&bar.blk_done[i], 1);
+      mbar_init(&bar.st_full[i], 1); mbar_init(&bar.st_empty[i], kComputeWarps);
+      mbar_init(&bar.dq_drained[i], 4);
+      bar.special[i] = 0;
+    }
+    for (int i = 0; i < 3; ++i) {
+      mbar_init(&bar.qd_full[i], 1); mbar_init(&bar.qd_empty[i], 1); mbar_init(&bar.bt_full[i], 1); mbar_init(&bar.bt_empty[i], 1);
+    }
+    mbar_init(&bar.kv_drained, 8);
+    mbar_fence_init();
+    prefetch_tmap(&mq); prefetch_tmap(&mk); prefetch_tmap(&mv); prefetch_tmap(&mg); prefetch_tmap(&mbt);
+  }
+  write_alpha_identity<TB>(sI, p.alpha[0], tid, kThreads);
+  write_alpha_identity<TB>(sI + 1024, p.alpha[1], tid, kThreads);
+  fence_async_smem();
+  if (warp == 0) { tmem_alloc(&tmem_base_s, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  volatile int* abort_flag = &abort_s;
+  const uint32_t tm0 = tmem_base_s;
+  const int nt = p.n_t;
+  const bool dbuf = p.dbuf != 0;
+  // TMEM: team t's scores S''^T at t*128 + [0,64), dP^T at t*128 + [64,128) (P^T / dS^T are packed over them);
+  // dK | dV accumulators (one or two sets); dQ accumulators (one per query tile, or two used in turn when streaming)
+  const uint32_t tKV = tm0 + 256, tDQ = tm0 + 256 + (dbuf ? 128 : 64);
+  auto tDK_of = [&](uint32_t kc) { return tKV + (dbuf ? (kc & 1) * 64 : 0); };
+  auto tDV_of = [&](uint32_t kc) { return tDK_of(kc) + 32; };
+  auto qd_stage = [&](uint32_t gg) { return sQD + (gg % 3) * 2 * kTileB; };
+  auto kv_stage = [&](uint32_t kc) { return sKV + (kc & 1) * 2 * kTileB; };
+  // work item = (b, n, h, range of key tiles)
+  auto item_range = [&](int item, int& jt0, int& jt1) {
+    const int sp = item % p.ksplit;
+    jt0 = sp * nt / p.ksplit; jt1 = (sp + 1) * nt / p.ksplit;
+  };
+
+  if (warp < kComputeWarps) {
+    // ============================================================================ compute warps
+    // Register re-partition: the CTA is launched with 96 registers per thread (640 threads); the helper warpgroup
+    // drops to 32 and the compute warpgroups rise to 112.  The raise can only draw on what the drop releases inside
+    // this CTA, so 512 * 112 + 128 * 32 must not exceed 640 * 96 - otherwise the raise never returns.
+    static_assert(kComputeWarps * 32 * 112 + 128 * 32 <= kThreads * 96, "setmaxnreg budget");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 112;");
+    const int team = warp >> 3;                       // takes the half blocks with (half == team)
+    const int ch = (warp >> 2) & 1;                   // which 32 of the half block's 64 query columns
+    const int w = warp >> 2;                          // 0..3: role in the write-out of accumulators
+    const int r = (warp & 3) * 32 + lane;             // TMEM lane = key row inside the tile
+    const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t tST = tm0 + team * 128 + ch * 32 + lane_addr, tDP = tST + 64;
+
+    // dK (scaled) and dV rows of key `j` from accumulator set `kc`: warps 0-3 write dK, warps 4-7 dV
+    auto store_kv = [&](uint32_t kc, int j, int b, int n, int h) {
+      tc_fence_after();
+      uint32_t o32[32];
+      tmem_ld32((w == 0 ? tDK_of(kc) : tDV_of(kc)) + lane_addr, o32);
+      tmem_ld_wait();
+      tc_fence_before();
+      if (j < p.L && !*abort_flag) {
+        const float sc = w == 0 ? p.scale : 1.f;
+        T* orow = static_cast<T*>(w == 0 ? p.dk : p.dv) + ((((int64_t)b * p.N + n) * p.L + j) * p.H + h) * p.D;
+#pragma unroll
+        for (int d8 = 0; d8 < 4; ++d8) {
+          if (d8 * 8 < p.D) {
+            uint4 v;
+            v.x = Pack2<T>::pack(__uint_as_float(o32[d8 * 8]) * sc, __uint_as_float(o32[d8 * 8 + 1]) * sc);
+            v.y = Pack2<T>::pack(__uint_as_float(o32[d8 * 8 + 2]) * sc, __uint_as_float(o32[d8 * 8 + 3]) * sc);
+            v.z = Pack2<T>::pack(__uint_as_float(o32[d8 * 8 + 4]) * sc, __uint_as_float(o32[d8 * 8 + 5]) * sc);
+            v.w = Pack2<T>::pack(__uint_as_float(o32[d8 * 8 + 6]) * sc, __uint_as_float(o32[d8 * 8 + 7]) * sc);
+            *reinterpret_cast<uint4*>(orow + d8 * 8) = v;
+          }
+        }
+      }
+    };
+    // rows of a dQ accumulator (TMEM lane = query) added, scaled, to the fp32 dQ rows in global memory
+    auto add_dq = [&](uint32_t tacc, int it2, int b, int n, int h) {
+      tc_fence_after();
+      uint32_t o32[32];
+      tmem_ld32(tacc + lane_addr, o32);
+      tmem_ld_wait();
+      tc_fence_before();
+      const int i = it2 * kT + r;
+      if (i < p.L && !*abort_flag) {
+        float* arow = p.dq_acc + ((((int64_t)b * p.N + n) * p.L + i) * p.H + h) * p.D;
+#pragma unroll
+        for (int d4 = 0; d4 < 8; ++d4)
+          if (d4 * 4 < p.D)
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(arow + d4 * 4),
+                         "f"(__uint_as_float(o32[d4 * 4]) * p.scale), "f"(__uint_as_float(o32[d4 * 4 + 1]) * p.scale),
+                         "f"(__uint_as_float(o32[d4 * 4 + 2]) * p.scale), "f"(__uint_as_float(o32[d4 * 4 + 3]) * p.scale) : "memory");
+      }
+    };
+
+    uint32_t g = 0;                 // full blocks seen by this CTA (both teams count every block)
+    uint32_t kv_cnt = 0;            // (item, j) pairs so far
+    uint32_t tuse = 0;              // half blocks this team has processed
+    int item_no = 0;
+    int pend_j = -1; uint32_t pend_kc = 0, pend_g = 0; int pend_b = 0, pend_n = 0, pend_h = 0;   // deferred dK/dV write-out
+    int dqp_it = -1; uint32_t dqp_g = 0; int dqp_b = 0, dqp_n = 0, dqp_h = 0;                    // deferred streamed dQ
+    for (int item = blockIdx.x; item < p.n_items; item += gridDim.x, ++item_no) {
+      const int bnh = item / p.ksplit;
+      int jt0, jt1; item_range(item, jt0, jt1);
+      const int h = bnh % p.H, bn = bnh / p.H, n = bn % p.N, b = bn / p.N;
+      const int sbuf = item_no & 1;
+      wait_or_flag(&bar.st_full[sbuf], (item_no >> 1) & 1, abort_flag);
+      const bool special = *reinterpret_cast<volatile int*>(&bar.special[sbuf]) != 0;
+      const float* lse2c = lse2 + sbuf * p.lpad;
+      const float* dltc = dlt + sbuf * p.lpad;
+      float mask2_next = -INFINITY;
+      {
+        const int j0r = jt0 * kT + r;
+        if (j0r < p.L) {
+          const int64_t mi = b * p.ms[0] + n * p.ms[1] + (int64_t)j0r * p.ms[2];
+          mask2_next = p.mask_dtype == MF_U8 ? (static_cast<const uint8_t*>(p.mask)[mi] ? 0.f : -FLT_MAX)
+                                             : load_rt(p.mask, mi, p.mask_dtype) * kLog2e;
+        }
+      }
+      for (int jt = jt0; jt < jt1; ++jt, ++kv_cnt) {
+        const int j = jt * kT + r;
+        const bool j_ok = j < p.L;
+        const float mask2 = mask2_next;          // fetched one key tile ahead
+        if (jt + 1 < jt1) {
+          const int jn = (jt + 1) * kT + r;
+          mask2_next = -INFINITY;
+          if (jn < p.L) {
+            const int64_t mi = b * p.ms[0] + n * p.ms[1] + (int64_t)jn * p.ms[2];
+            mask2_next = p.mask_dtype == MF_U8 ? (static_cast<const uint8_t*>(p.mask)[mi] ? 0.f : -FLT_MAX)
+                                               : load_rt(p.mask, mi, p.mask_dtype) * kLog2e;
+          }
+        }
+        const bool masked_key = mask2 <= -FLT_MAX;
+        for (int it = 0; it < nt; ++it, ++g) {
+          const int i0 = it * kT + team * kHalf + ch * 32;
+          // ---- S''^T, dP^T of my half block -> registers
+          wait_or_flag(&bar.sd_ready[team], tuse & 1, abort_flag);
+          tc_fence_after();
+          uint32_t sr[32], dr[32];
+          tmem_ld32(tST, sr);
+          tmem_ld32(tDP, dr);
+          tmem_ld_wait();
+          uint32_t pp[16], dd[16];
+          if (special) p_and_ds<T, true>(sr, dr, lse2c + i0, dltc + i0, p.c1, mask2, j_ok, masked_key, p.inv_L, pp, dd);
+          else p_and_ds<T, false>(sr, dr, lse2c + i0, dltc + i0, p.c1, mask2, j_ok, masked_key, p.inv_L, pp, dd);
+          // ---- packed P^T / dS^T over the scores just read (A operands of the dV / dK products)
+          tmem_st16(tST, pp);
+          tmem_st16(tDP, dd);
+          // ---- dS^T also to the shared-memory tile of this block (A operand of the dQ product), once the dQ
+          // product that read this buffer two blocks ago is complete
+          if (g >= 2) wait_or_flag(&bar.blk_done[g & 1], ((g >> 1) - 1) & 1, abort_flag);
+          {
+            uint8_t* atom = sDS + (g & 1) * 2 * kAtomB + team * kAtomB;
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+              *reinterpret_cast<uint4*>(atom + swz_offset(r, ch * 4 + c, 128)) = make_uint4(dd[c * 4], dd[c * 4 + 1], dd[c * 4 + 2], dd[c * 4 + 3]);
+          }
+          tmem_st_wait();
+          fence_async_smem();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bar.written[team]);
+          ++tuse;
+          // ---- streamed dQ: the product of the previous block sits in accumulator (g - 1) & 1; the four warps with
+          // w == (g - 1) & 3 add it to global memory and hand the accumulator back
+          if constexpr (DQS) {
+            if (dqp_it >= 0 && w == (int)(dqp_g & 3)) {
+              wait_or_flag(&bar.blk_done[dqp_g & 1], (dqp_g >> 1) & 1, abort_flag);
+              add_dq(tDQ + (dqp_g & 1) * 32, dqp_it, dqp_b, dqp_n, dqp_h);
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&bar.dq_drained[dqp_g & 1]);
+            }
+            dqp_it = it; dqp_g = g; dqp_b = b; dqp_n = n; dqp_h = h;
+          }
+          // ---- dK_j, dV_j of the key tile that finished one block ago (warps 0-7)
+          if (pend_j >= 0 && w < 2) {
+            wait_or_flag(&bar.blk_done[pend_g & 1], (pend_g >> 1) & 1, abort_flag);
+            store_kv(pend_kc, pend_j, pend_b, pend_n, pend_h);
+            if (!dbuf) { __syncwarp(); if (lane == 0) mbar_arrive(&bar.kv_drained); }
+          }
+          pend_j = -1;
+          if (it == nt - 1) { pend_j = j; pend_kc = kv_cnt; pend_g = g; pend_b = b; pend_n = n; pend_h = h; }
+        }
+      }
+      // ---- end of the item: the last key tile's dK/dV, the last streamed dQ, or every query tile's dQ
+      const uint32_t gl = g - 1;
+      wait_or_flag(&bar.blk_done[gl & 1], (gl >> 1) & 1, abort_flag);
+      if (pend_j >= 0 && w < 2) {
+        store_kv(pend_kc, pend_j, pend_b, pend_n, pend_h);
+        if (!dbuf) { __syncwarp(); if (lane == 0) mbar_arrive(&bar.kv_drained); }
+      }
+      pend_j = -1;
+      if constexpr (DQS) {
+        if (dqp_it >= 0 && w == (int)(dqp_g & 3)) {
+          add_dq(tDQ + (dqp_g & 1) * 32, dqp_it, dqp_b, dqp_n, dqp_h);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bar.dq_drained[dqp_g & 1]);
+        }
+        dqp_it = -1;
+      } else {
+        for (int it = w; it < nt; it += 4) {
+          if (p.ksplit > 1) {
+            add_dq(tDQ + it * 32, it, b, n, h);
+          } else {
+            tc_fence_after();
+            uint32_t o32[32];
+            tmem_ld32(tDQ + it * 32 + lane_addr, o32);
+            tmem_ld_wait();
+            tc_fence_before();
+            const int i = it * kT + r;
+            if (i < p.L && !*abort_flag) {
+              T* orow = static_cast<T*>(p.dq) + ((((int64_t)b * p.N + n) * p.L + i) * p.H + h) * p.D;
+#pragma unroll
+              for (int d8 = 0; d8 < 4; ++d8) {
+                if (d8 * 8 < p.D) {
+                  uint4 v;
+                  v.x = Pack2<T>::pack(__uint_as_float(o32[d8 * 8]) * p.scale, __uint_as_float(o32[d8 * 8 + 1]) * p.scale);
+                  v.y = Pack2<T>::pack(__uint_as_float(o32[d8 * 8 + 2]) * p.scale, __uint_as_float(o32[d8 * 8 + 3]) * p.scale);
+                  v.z = Pack2<T>::pack(__uint_as_float(o32[d8 * 8 + 4]) * p.scale, __uint_as_float(o32[d8 * 8 + 5]) * p.scale);
+                  v.w = Pack2<T>::pack(__uint_as_float(o32[d8 * 8 + 6]) * p.scale, __uint_as_float(o32[d8 * 8 + 7]) * p.scale);
+                  *reinterpret_cast<uint4*>(orow + d8 * 8) = v;
+                }
+              }
+            }
+          }
+        }
+      }
+      // this item's statistics and on-chip dQ accumulators are no longer needed by this warp
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar.st_empty[sbuf]);
+    }
+  } else {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 32;");
+    if (warp == kComputeWarps && lane == 0) {
+      // ========================================================================== accumulate-MMA issuer
+      const uint32_t id_kv = idesc_f16(128, 32, p.fmt, 0, 1);     // A (TMEM) K-major, B MN-major
+      const uint32_t id_q = idesc_f16(128, 32, p.fmt, 1, 1);      // A MN-major (M = queries), B MN-major
+      constexpr uint32_t hi_t = desc_hi(1024, kSw128), hi_o = desc_hi(512, kSw64);
+      uint32_t g = 0, kv = 0, hb = 0;
+      int item_no = 0;
+      for (int item = blockIdx.x; item < p.n_items && !*abort_flag; item += gridDim.x, ++item_no) {
+        int jt0, jt1; item_range(item, jt0, jt1);
+        for (int jt = jt0; jt < jt1 && !*abort_flag; ++jt, ++kv) {
+          if (!dbuf && kv > 0) wait_or_flag(&bar.kv_drained, (kv - 1) & 1, abort_flag);
+          const uint32_t kvb = smem_u32(kv_stage(kv));
+          for (int it = 0; it < nt; ++it, ++g) {
+            const uint32_t qdb = smem_u32(qd_stage(g));
+            for (int half = 0; half < 2; ++half, ++hb) {
+              wait_or_flag(&bar.written[half], (hb >> 1) & 1, abort_flag);
+              tc_fence_after();
+              if (*abort_flag) break;
+              const uint32_t tPt = tm0 + half * 128, tDSt = tPt + 64;
+              const uint32_t do_lo = desc_lo(qdb + kTileB, 16) + half * 4 * 64, q_lo = desc_lo(qdb, 16) + half * 4 * 64;
+              const bool first = it == 0 && half == 0;
+#pragma unroll
+              for (int kq = 0; kq < 4; ++kq)      // dV_j += P^T dO_i   (16 queries per step)
+                mma_ts_lh(tDV_of(kv), tPt + (kq >> 1) * 32 + (kq & 1) * 8, do_lo + kq * 64, hi_o, id_kv, !first || kq > 0);
+#pragma unroll
+              for (int kq = 0; kq < 4; ++kq)      // dK_j += dS^T Q_i
+                mma_ts_lh(tDK_of(kv), tDSt + (kq >> 1) * 32 + (kq & 1) * 8, q_lo + kq * 64, hi_o, id_kv, !first || kq > 0);
+              tc_commit(&bar.buf_free[half]);
+            }
+            if (*abort_flag) break;
+            // dQ_i += dS K_j   (A = the dS^T tile in shared memory read MN-major: M = queries)
+            if constexpr (DQS) {
+              if (g >= 2) wait_or_flag(&bar.dq_drained[g & 1], ((g >> 1) - 1) & 1, abort_flag);
+            } else if (item_no > 0 && jt == jt0 && it == 0) {
+              // the on-chip dQ accumulators of the previous item must have been read out before they start afresh
+              wait_or_flag(&bar.st_empty[(item_no - 1) & 1], ((item_no - 1) >> 1) & 1, abort_flag);
+            }
+            const uint32_t dst_lo = desc_lo(smem_u32(sDS + (g & 1) * 2 * kAtomB), kAtomB);
+            const uint32_t k_lo = desc_lo(kvb, 16);
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks)
+              mma_ss_lh(tDQ + (DQS ? (g & 1) : it) * 32, dst_lo + ks * (2048 / 16), hi_t, k_lo + ks * 64, hi_o, id_q,
+                        DQS ? ks > 0 : (jt > jt0 || ks > 0));
+            tc_commit(&bar.blk_done[g & 1]);
+            tc_commit(&bar.qd_empty[g % 3]);
+            if (it == nt - 1) tc_commit(&bar.kv_empty[kv & 1]);
+          }
+        }
+      }
+    } else if (warp == kComputeWarps + 2 && lane == 0) {
+      // ========================================================================== score-MMA issuer
+      const uint32_t id_s = idesc_f16(128, kHalf, p.fmt, 0, 0);
+      const uint32_t id_b = idesc_f16(128, 16, p.bfmt, 0, 0);
+      constexpr uint32_t hi64 = desc_hi(512, kSw64), hi128 = desc_hi(1024, kSw128);
+      uint32_t g = 0, kv = 0, hb = 0, bslot = 0, buse = 0;
+      for (int item = blockIdx.x; item < p.n_items && !*abort_flag; item += gridDim.x) {
+        int jt0, jt1; item_range(item, jt0, jt1);
+        for (int jt = jt0; jt < jt1 && !*abort_flag; ++jt, ++kv) {
+          wait_or_flag(&bar.kv_full[kv & 1], (kv >> 1) & 1, abort_flag);
+          const uint32_t kvb = smem_u32(kv_stage(kv));
+          const uint32_t k_lo = desc_lo(kvb, 16), v_lo = desc_lo(kvb + kTileB, 16);
+          for (int it = 0; it < nt; ++it, ++g) {
+            wait_or_flag(&bar.qd_full[g % 3], (g / 3) & 1, abort_flag);
+            const uint32_t qdb = smem_u32(qd_stage(g));
+            for (int half = 0; half < 2; ++half, ++hb) {
+              wait_or_flag(&bar.bt_full[bslot], buse & 1, abort_flag);
+              if (hb >= 2) wait_or_flag(&bar.buf_free[half], ((hb >> 1) - 1) & 1, abort_flag);
+              tc_fence_after();
+              if (*abort_flag) break;
+              const uint32_t tST = tm0 + half * 128, tDP = tST + 64;
+              const uint32_t q_lo = desc_lo(qdb, 16) + half * (kHalf * 64 / 16), g_lo = desc_lo(qdb + kTileB, 16) + half * (kHalf * 64 / 16);
+#pragma unroll
+              for (int ks = 0; ks < 2; ++ks) mma_ss_lh(tST, k_lo + ks * 2, hi64, q_lo + ks * 2, hi64, id_s, ks > 0);
+              const uint32_t a_lo = desc_lo(smem_u32(sBT + bslot * kAtomB), 16);
+              for (int term = 0; term < p.n_alpha; ++term) {
+                const uint32_t i_lo = desc_lo(smem_u32(sI + term * 1024), 16);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) mma_ss_lh(tST + c * 16, a_lo + c * 2, hi128, i_lo, hi64, id_b, true);
+              }
+#pragma unroll
+              for (int ks = 0; ks < 2; ++ks) mma_ss_lh(tDP, v_lo + ks * 2, hi64, g_lo + ks * 2, hi64, id_s, ks > 0);
+              tc_commit(&bar.sd_ready[half]);
+              tc_commit(&bar.bt_empty[bslot]);
+              if (++bslot == 3) { bslot = 0; ++buse; }
+            }
+            if (*abort_flag) break;
+          }
+        }
+      }
+    } else if (warp == kComputeWarps + 1 && lane == 0) {
+      // ========================================================================== TMA producer, in order of need
+      uint32_t g = 0, kv = 0, bslot = 0, buse = 0, nbt = 0;
+      for (int item = blockIdx.x; item < p.n_items && !*abort_flag; item += gridDim.x) {
+        const int bnh = item / p.ksplit;
+        int jt0, jt1; item_range(item, jt0, jt1);
+        const int h = bnh % p.H, bn = bnh / p.H, n = bn % p.N, b = bn / p.N;
+        for (int jt = jt0; jt < jt1 && !*abort_flag; ++jt, ++kv) {
+          if (kv >= 2) wait_or_flag(&bar.kv_empty[kv & 1], ((kv >> 1) - 1) & 1, abort_flag);
+          if (*abort_flag) break;
+          {
+            uint64_t* fb = &bar.kv_full[kv & 1];
+            mbar_expect_tx(fb, 2 * kTileB);
+            tma_load_5d(kv_stage(kv), &mk, fb, 0, h, jt * kT, n, b);
+            tma_load_5d(kv_stage(kv) + kTileB, &mv, fb, 0, h, jt * kT, n, b);
+          }
+          for (int it = 0; it < nt; ++it, ++g) {
+            if (g >= 3) wait_or_flag(&bar.qd_empty[g % 3], ((g / 3) - 1) & 1, abort_flag);
+            if (*abort_flag) break;
+            {
+              uint64_t* fb = &bar.qd_full[g % 3];
+              mbar_expect_tx(fb, 2 * kTileB);
+              tma_load_5d(qd_stage(g), &mq, fb, 0, h, it * kT, n, b);
+              tma_load_5d(qd_stage(g) + kTileB, &mg, fb, 0, h, it * kT, n, b);
+            }
+            for (int half = 0; half < 2; ++half) {
+              if (buse >= 1) wait_or_flag(&bar.bt_empty[bslot], (buse - 1) & 1, abort_flag);
+              if (*abort_flag) break;
+              mbar_expect_tx(&bar.bt_full[bslot], kAtomB);
+              tma_load_4d(sBT + bslot * kAtomB, &mbt, &bar.bt_full[bslot], it * kT + half * kHalf, jt * kT, h, b * p.bias_b_mul);
+              ++nbt;
+              if (++bslot == 3) { bslot = 0; ++buse; }
+            }
+          }
+        }
+      }
+      if (*abort_flag) {
+        // the copies already requested must land before the CTA's shared memory is given back (bounded)
+        for (uint32_t back = 0; back < 2 && back < kv; ++back) { const uint32_t c = kv - 1 - back; mbar_wait(&bar.kv_full[c & 1], (c >> 1) & 1); }
+        for (uint32_t back = 0; back < 3 && back < g; ++back) { const uint32_t c = g - 1 - back; mbar_wait(&bar.qd_full[c % 3], (c / 3) & 1); }
+        for (uint32_t back = 0; back < 3 && back < nbt; ++back) { const uint32_t c = nbt - 1 - back; mbar_wait(&bar.bt_full[c % 3], (c / 3) & 1); }
+      }
+    } else if (warp == kComputeWarps + 3) {
+      // ========================================================================== statistics loader (whole warp):
+      // lse in base 2 and delta of the item's query rows into the buffer of the item's parity; queries beyond L get
+      // lse = +inf so that P = 0.  A fully masked row (lse = -FLT_MAX) sends the item down the careful path.
+      int item_no = 0;
+      for (int item = blockIdx.x; item < p.n_items && !*abort_flag; item += gridDim.x, ++item_no) {
+        const int buf = item_no & 1;
+        if (item_no >= 2) wait_or_flag(&bar.st_empty[buf], ((item_no >> 1) - 1) & 1, abort_flag);
+        const int64_t row0 = (int64_t)(item / p.ksplit) * p.L;       // ((b*N+n)*H + h) * L
+        int sp = 0;
+        for (int i = lane; i < p.lpad; i += 32) {
+          float l2 = INFINITY, dl = 0.f;
+          if (i < p.L) {
+            const float lv = p.lse[row0 + i];
+            if (lv <= -3e38f) sp = 1;
+            l2 = lv * kLog2e; dl = p.delta[row0 + i];
+          }
+          lse2[buf * p.lpad + i] = l2; dlt[buf * p.lpad + i] = dl;
+        }
+        sp = __any_sync(0xffffffffu, sp);
+        if (lane == 0) { bar.special[buf] = sp; }
+        __syncwarp();
+        __threadfence_block();
+        if (lane == 0) mbar_arrive(&bar.st_full[buf]);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (tid == 0 && abort_s) *reinterpret_cast<volatile int*>(p.status) = 1;
+  if (warp == 0) tmem_dealloc(tmem_base_s, 512);
+}
+
+// ------------------------------------------------------------------------------------------------ dBias
+struct DbP {
+  int B, N, L, H, D;
+  int n_t, lpad, nsplit, n_units;
+  float c1;
+  uint32_t fmt, bfmt;
+  int n_alpha; float alpha[2];
+  int bias_b_mul;
+  const void* mask; int64_t ms[3]; int mask_dtype;
+  const float* lse; const float* delta;
+  float* part;            // fp32 [nsplit][B][H][L][L] partial sums
+  int* status;
+};
+
+struct DbBars {
+  uint64_t op_full[3], op_empty[3];          // Q, dO, K, V of one row n
+  uint64_t st_full[3], st_empty[3];          // lse2 / delta of the row's 128 queries
+  uint64_t bt_full, bt_free;                 // the unit's two bias^T atoms
+  uint64_t sd_ready[2], loaded[2];
+};
+
+template <typename T, typename TB>
+__global__ void __launch_bounds__(kThreads, 1)
+evo_dbias_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mk,
+                    const __grid_constant__ CUtensorMap mv, const __grid_constant__ CUtensorMap mg,
+                    const __grid_constant__ CUtensorMap mbt, const DbP p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* sBT = smem;                          // two bias^T atoms (queries 0-63 | 64-127 of the tile)
+  uint8_t* sOP = sBT + 2 * kAtomB;              // [3 stages][Q, dO, K, V]
+  uint8_t* sI = sOP + 12 * kTileB;
+  float* sST = reinterpret_cast<float*>(sI + 2048);     // [3 stages][lse2 x 128 | delta x 128]
+
+  __shared__ DbBars bar;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_s;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {
+    abort_s = 0;
+    for (int i = 0; i < 3; ++i) {
+      mbar_init(&bar.op_full[i], 1); mbar_init(&bar.op_empty[i], 1);
+      mbar_init(&bar.st_full[i], 1); mbar_init(&bar.st_empty[i], kComputeWarps);
+    }
+    mbar_init(&bar.bt_full, 1); mbar_init(&bar.bt_free, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&bar.sd_ready[i], 1); mbar_init(&bar.loaded[i], kComputeWarps); }
+    mbar_fence_init();
+    prefetch_tmap(&mq); prefetch_tmap(&mk); prefetch_tmap(&mv); prefetch_tmap(&mg); prefetch_tmap(&mbt);
+  }
+  write_alpha_identity<TB>(sI, p.alpha[0], tid, kThreads);
+  write_alpha_identity<TB>(sI + 1024, p.alpha[1], tid, kThreads);
+  fence_async_smem();
+  if (warp == 0) { tmem_alloc(&tmem_base_s, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  volatile int* abort_flag = &abort_s;
+  const uint32_t tm0 = tmem_base_s;
+  const int nt = p.n_t;
+  // unit = ((b * H + h) * nt + jt) * nt + it, split `sp` of the rows
+  struct Unit { int b, h, jt, it, n0, n1; };
+  auto unit_of = [&](int u) {
+    Unit x;
+    const int sp = u % p.nsplit; int c = u / p.nsplit;
+    x.it = c % nt; c /= nt; x.jt = c % nt; c /= nt; x.h = c % p.H; x.b = c / p.H;
+    x.n0 = (int)((int64_t)sp * p.N / p.nsplit); x.n1 = (int)((int64_t)(sp + 1) * p.N / p.nsplit);
+    return x;
+  };
+
+  if (warp < kComputeWarps) {
+    static_assert(kComputeWarps * 32 * 112 + 128 * 32 <= kThreads * 96, "setmaxnreg budget");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 112;");
+    const int w = warp >> 2;                          // query quarter (32 columns) handled by this thread
+    const int r = (warp & 3) * 32 + lane;             // TMEM lane = key row inside the tile
+    const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+    uint32_t g = 0;                                   // rows processed by this CTA (buffer g & 1, stage g % 3)
+    const float2 c1c1 = make_float2(p.c1, p.c1);
+    for (int u = blockIdx.x; u < p.n_units; u += gridDim.x) {
+      const Unit x = unit_of(u);
+      const int j = x.jt * kT + r;
+      float2 acc[16];
+#pragma unroll
+      for (int c = 0; c < 16; ++c) acc[c] = make_float2(0.f, 0.f);
+      for (int n = x.n0; n < x.n1; ++n, ++g) {
+        float mask2 = -INFINITY;
+        if (j < p.L) {
+          const int64_t mi = x.b * p.ms[0] + n * p.ms[1] + (int64_t)j * p.ms[2];
+          mask2 = p.mask_dtype == MF_U8 ? (static_cast<const uint8_t*>(p.mask)[mi] ? 0.f : -FLT_MAX)
+                                        : load_rt(p.mask, mi, p.mask_dtype) * kLog2e;
+        }
+        const uint32_t tST = tm0 + (g & 1) * 256 + w * 32 + lane_addr, tDP = tST + 128;
+        wait_or_flag(&bar.sd_ready[g & 1], (g >> 1) & 1, abort_flag);
+        tc_fence_after();
+        uint32_t sr[32], dr[32];
+        tmem_ld32(tST, sr);
+        tmem_ld32(tDP, dr);
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar.loaded[g & 1]);
+        wait_or_flag(&bar.st_full[g % 3], (g / 3) & 1, abort_flag);
+        const float* l2 = sST + (g % 3) * 256 + w * 32;
+        const float* dl = l2 + 128;
+        const float2 mm = make_float2(mask2, mask2);
+#pragma unroll
+        for (int c4 = 0; c4 < 8; ++c4) {
+          const float4 l4 = *reinterpret_cast<const float4*>(l2 + c4 * 4);
+          const float4 d4 = *reinterpret_cast<const float4*>(dl + c4 * 4);
+          const float2 x0 = fma2(make_float2(__uint_as_float(sr[c4 * 4]), __uint_as_float(sr[c4 * 4 + 1])), c1c1, sub2(mm, make_float2(l4.x, l4.y)));
+          const float2 x1 = fma2(make_float2(__uint_as_float(sr[c4 * 4 + 2]), __uint_as_float(sr[c4 * 4 + 3])), c1c1, sub2(mm, make_float2(l4.z, l4.w)));
+          const float2 p0 = make_float2(ex2f(x0.x), ex2f(x0.y)), p1 = make_float2(ex2f(x1.x), ex2f(x1.y));
+          acc[c4 * 2] = fma2(p0, sub2(make_float2(__uint_as_float(dr[c4 * 4]), __uint_as_float(dr[c4 * 4 + 1])), make_float2(d4.x, d4.y)), acc[c4 * 2]);
+          acc[c4 * 2 + 1] = fma2(p1, sub2(make_float2(__uint_as_float(dr[c4 * 4 + 2]), __uint_as_float(dr[c4 * 4 + 3])), make_float2(d4.z, d4.w)), acc[c4 * 2 + 1]);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar.st_empty[g % 3]);
+      }
+      // the unit's partial sum: part[sp][b][h][i][j], lanes = consecutive keys
+      if (j < p.L && !*abort_flag) {
+        const int sp = u % p.nsplit;
+        float* dst = p.part + ((((int64_t)sp * p.B + x.b) * p.H + x.h) * p.L) * (int64_t)p.L + j;
+        const int i0 = x.it * kT + w * 32;
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+          if (i0 + 2 * c < p.L) dst[(int64_t)(i0 + 2 * c) * p.L] = acc[c].x;
+          if (i0 + 2 * c + 1 < p.L) dst[(int64_t)(i0 + 2 * c + 1) * p.L] = acc[c].y;
+        }
+      }
+    }
+  } else {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 32;");
+    if (warp == kComputeWarps && lane == 0) {
+      // ========================================================================== MMA issuer
+      const uint32_t id_s = idesc_f16(128, 128, p.fmt, 0, 0);
+      const uint32_t id_b = idesc_f16(128, 16, p.bfmt, 0, 0);
+      constexpr uint32_t hi64 = desc_hi(512, kSw64), hi128 = desc_hi(1024, kSw128);
+      uint32_t g = 0, un = 0;
+      for (int u = blockIdx.x; u < p.n_units && !*abort_flag; u += gridDim.x, ++un) {
+        const Unit x = unit_of(u);
+        wait_or_flag(&bar.bt_full, un & 1, abort_flag);
+        for (int n = x.n0; n < x.n1 && !*abort_flag; ++n, ++g) {
+          wait_or_flag(&bar.op_full[g % 3], (g / 3) & 1, abort_flag);
+          if (g >= 2) wait_or_flag(&bar.loaded[g & 1], ((g >> 1) - 1) & 1, abort_flag);
+          tc_fence_after();
+          if (*abort_flag) break;
+          const uint32_t ob = smem_u32(sOP + (g % 3) * 4 * kTileB);
+          const uint32_t q_lo = desc_lo(ob, 16), g_lo = desc_lo(ob + kTileB, 16), k_lo = desc_lo(ob + 2 * kTileB, 16), v_lo = desc_lo(ob + 3 * kTileB, 16);
+          const uint32_t tST = tm0 + (g & 1) * 256, tDP = tST + 128;
+#pragma unroll
+          for (int ks = 0; ks < 2; ++ks) mma_ss_lh(tST, k_lo + ks * 2, hi64, q_lo + ks * 2, hi64, id_s, ks > 0);
+          for (int term = 0; term < p.n_alpha; ++term) {
+            const uint32_t i_lo = desc_lo(smem_u32(sI + term * 1024), 16);
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+              mma_ss_lh(tST + c * 16, desc_lo(smem_u32(sBT + (c >> 2) * kAtomB), 16) + (c & 3) * 2, hi128, i_lo, hi64, id_b, true);
+          }
+#pragma unroll
+          for (int ks = 0; ks < 2; ++ks) mma_ss_lh(tDP, v_lo + ks * 2, hi64, g_lo + ks * 2, hi64, id_s, ks > 0);
+          tc_commit(&bar.sd_ready[g & 1]);
+          tc_commit(&bar.op_empty[g % 3]);
+        }
+        tc_commit(&bar.bt_free);       // every product that reads this unit's bias atoms is complete
+      }
+    } else if (warp == kComputeWarps + 1 && lane == 0) {
+      // ========================================================================== TMA producer
+      uint32_t g = 0, un = 0;
+      for (int u = blockIdx.x; u < p.n_units && !*abort_flag; u += gridDim.x, ++un) {
+        const Unit x = unit_of(u);
+        if (un >= 1) wait_or_flag(&bar.bt_free, (un - 1) & 1, abort_flag);
+        if (*abort_flag) break;
+        mbar_expect_tx(&bar.bt_full, 2 * kAtomB);
+        tma_load_4d(sBT, &mbt, &bar.bt_full, x.it * kT, x.jt * kT, x.h, x.b * p.bias_b_mul);
+        tma_load_4d(sBT + kAtomB, &mbt, &bar.bt_full, x.it * kT + kHalf, x.jt * kT, x.h, x.b * p.bias_b_mul);
+        for (int n = x.n0; n < x.n1; ++n, ++g) {
+          if (g >= 3) wait_or_flag(&bar.op_empty[g % 3], ((g / 3) - 1) & 1, abort_flag);
+          if (*abort_flag) break;
+          uint64_t* fb = &bar.op_full[g % 3];
+          uint8_t* st = sOP + (g % 3) * 4 * kTileB;
+          mbar_expect_tx(fb, 4 * kTileB);
+          tma_load_5d(st, &mq, fb, 0, x.h, x.it * kT, n, x.b);
+          tma_load_5d(st + kTileB, &mg, fb, 0, x.h, x.it * kT, n, x.b);
+          tma_load_5d(st + 2 * kTileB, &mk, fb, 0, x.h, x.jt * kT, n, x.b);
+          tma_load_5d(st + 3 * kTileB, &mv, fb, 0, x.h, x.jt * kT, n, x.b);
+        }
+      }
+      if (*abort_flag) {
+        for (uint32_t back = 0; back < 3 && back < g; ++back) { const uint32_t c = g - 1 - back; mbar_wait(&bar.op_full[c % 3], (c / 3) & 1); }
+        if (un > 0) mbar_wait(&bar.bt_full, (un - 1) & 1);
+      }
+    } else if (warp == kComputeWarps + 3) {
+      // ========================================================================== statistics loader (whole warp):
+      // lse in base 2 and delta of the 128 queries of the unit's tile, row by row.  Queries beyond L and fully
+      // masked rows (lse = -FLT_MAX: no gradient reaches the bias through them) get lse = +inf, hence P = 0.
+      uint32_t g = 0;
+      for (int u = blockIdx.x; u < p.n_units && !*abort_flag; u += gridDim.x) {
+        const Unit x = unit_of(u);
+        for (int n = x.n0; n < x.n1 && !*abort_flag; ++n, ++g) {
+          if (g >= 3) wait_or_flag(&bar.st_empty[g % 3], ((g / 3) - 1) & 1, abort_flag);
+          const int64_t row0 = (((int64_t)x.b * p.N + n) * p.H + x.h) * p.L;
+          float* dst = sST + (g % 3) * 256;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int i = x.it * kT + k * 32 + lane;
+            float l2 = INFINITY, dl = 0.f;
+            if (i < p.L) {
+              const float lv = p.lse[row0 + i];
+              if (lv > -3e38f) l2 = lv * kLog2e;
+              dl = p.delta[row0 + i];
+            }
+            dst[k * 32 + lane] = l2; dst[128 + k * 32 + lane] = dl;
+          }
+          __syncwarp();
+          __threadfence_block();
+          if (lane == 0) mbar_arrive(&bar.st_full[g % 3]);
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (tid == 0 && abort_s) *reinterpret_cast<volatile int*>(p.status) = 1;
+  if (warp == 0) tmem_dealloc(tmem_base_s, 512);
+}
+
+// d_bias[b][h][i][j] = sum over the row ranges, in order, cast to the output type
+template <typename TO>
+__global__ void dbias_finish_kernel(const float* __restrict__ part, TO* __restrict__ out, int64_t n, int nsplit) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float s = part[i];
+  for (int k = 1; k < nsplit; ++k) s += part[(int64_t)k * n + i];
+  out[i] = from_f<TO>(s);
+}
+
+template <typename T>
+__global__ void cast_rows_ws_kernel(const float* __restrict__ src, T* __restrict__ dst, int64_t n) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) dst[i] = from_f<T>(src[i]);
+}
+
+// With few (b, n, h) triples (single-representation attention: N = 1) the key tiles of each are spread over several
+// CTAs so that the whole GPU works; the partial dQ rows then meet in an fp32 accumulator.
+int bwd_ksplit(int64_t bnh, int nt, int sms) {
+  if (bnh >= sms || nt < 2) return 1;
+  int64_t k = sms / bnh;                 // as many ranges as keep every CTA at one work item
+  if (k > nt) k = nt;
+  return k < 1 ? 1 : (int)k;
+}
+
+struct BwdPlan {
+  int nt, lpad, ksplit, dq_stream, dbuf, nsplit;
+  bool dq_fp32, part_direct;
+  size_t off_delta, off_part, off_dq, off_biasT, total;
+};
+
+BwdPlan plan_bwd(const mf_evo_bwd_args& a) {
+  BwdPlan pl{};
+  const int sms = sm_count();
+  pl.nt = (a.L + kT - 1) / kT;
+  pl.lpad = pl.nt * kT;
+  pl.ksplit = bwd_ksplit((int64_t)a.B * a.N * a.H, pl.nt, sms);
+  // dQ accumulators of all query tiles next to one set (up to six tiles) or two sets (up to four) of dK/dV accumulators;
+  // longer rows stream dQ
+  pl.dq_stream = pl.nt > 6;
+  pl.dbuf = pl.dq_stream || pl.nt <= 4;
+  pl.dq_fp32 = pl.ksplit > 1 || pl.dq_stream;
+  const int64_t combos = (int64_t)a.B * a.H * pl.nt * pl.nt;
+  int64_t ns = sms / combos;
+  if (ns < 1) ns = 1;
+  if (ns > a.N) ns = a.N;
+  pl.nsplit = (int)ns;
+  pl.part_direct = pl.nsplit == 1 && a.dbias_dtype == MF_F32;      // a single range writes d_bias itself
+  size_t off = 0;
+  pl.off_delta = off; off += align_up(sizeof(float) * (size_t)a.B * a.N * a.H * a.L, 256);
+  pl.off_part = off; if (!pl.part_direct) off += align_up(sizeof(float) * (size_t)pl.nsplit * a.B * a.H * a.L * a.L, 256);
+  pl.off_dq = off; if (pl.dq_fp32) off += align_up(sizeof(float) * (size_t)a.B * a.N * a.L * a.H * a.D, 256);
+  pl.off_biasT = off; off += align_up(2 * (size_t)a.B * a.H * a.L * pl.lpad, 256);
+  pl.total = off;
+  return pl;
+}
+
+template <typename T, typename TB>
+int launch_bwd_ws(const mf_evo_bwd_args& a, cudaStream_t st) {
+  const BwdPlan pl = plan_bwd(a);
+  CUtensorMap mq, mk, mv, mg, mbt;
+  int r;
+  const int64_t cs[5] = {(int64_t)a.N * a.L * a.H * a.D, (int64_t)a.L * a.H * a.D, (int64_t)a.H * a.D, a.D, 1};
+  if ((r = make_qkv_map(&mq, a.q, a.dtype, a.B, a.N, a.L, a.H, a.D, a.q_strides, kDP, kT))) return r;
+  if ((r = make_qkv_map(&mk, a.k, a.dtype, a.B, a.N, a.L, a.H, a.D, a.k_strides, kDP, kT))) return r;
+  if ((r = make_qkv_map(&mv, a.v, a.dtype, a.B, a.N, a.L, a.H, a.D, a.v_strides, kDP, kT))) return r;
+  if ((r = make_qkv_map(&mg, a.d_o, a.dtype, a.B, a.N, a.L, a.H, a.D, cs, kDP, kT))) return r;
+  int* status = status_word();
+  MF_REQUIRE(status, MF_ERR_CUDA, "could not allocate the device status word");
+  MF_REQUIRE(tc_async_status() == 0, MF_ERR_CUDA, "an earlier tensor-core kernel gave up on a bounded wait; results are invalid");
+  char* ws = static_cast<char*>(a.workspace);
+  float* delta = reinterpret_cast<float*>(ws + pl.off_delta);
+  float* part = pl.part_direct ? static_cast<float*>(a.d_bias) : reinterpret_cast<float*>(ws + pl.off_part);
+  float* dq_acc = reinterpret_cast<float*>(ws + pl.off_dq);
+  // the transposed bias copy is kept in a 16-bit type: the bias dtype when that is one, else the q/k/v dtype
+  using TT = typename std::conditional<sizeof(TB) == 2, TB, T>::type;
+  const int bt_dtype = sizeof(TB) == 2 ? a.bias_dtype : a.dtype;
+  TT* biasT = reinterpret_cast<TT*>(ws + pl.off_biasT);
+  const int lpad = pl.lpad;
+  {
+    MF_CUDA(cudaMemsetAsync(biasT, 0, 2 * (size_t)a.B * a.H * a.L * lpad, st));
+    dim3 grid((a.L + 31) / 32, (a.L + 31) / 32, a.B * a.H), block(32, 8);
+    transpose_bias_ws_kernel<TB, TT><<<grid, block, 0, st>>>(static_cast<const TB*>(a.bias), biasT, a.H, a.L, lpad, a.bias_strides[0],
+                                                             a.bias_strides[1], a.bias_strides[2], a.bias_strides[3]);
+    MF_LAUNCHED("transpose_bias_ws_kernel");
+    const int64_t dims[4] = {lpad, a.L, a.H, a.B};
+    const int64_t str[4] = {1, lpad, (int64_t)a.L * lpad, (int64_t)a.H * a.L * lpad};
+    const int box[4] = {kHalf, 128, 1, 1};
+    if ((r = make_tiled_map(&mbt, biasT, bt_dtype, 4, dims, str, box, 128))) return r;
+  }
+  const int64_t rows = (int64_t)a.B * a.N * a.L * a.H;
+  evo_delta_ws_kernel<T><<<(unsigned)((rows + 255) / 256), 256, 0, st>>>(static_cast<const T*>(a.o), static_cast<const T*>(a.d_o),
+                                                                      delta, rows, a.L, a.H, a.D);
+  MF_LAUNCHED("evo_delta_ws_kernel");
+  const int64_t n_dq = (int64_t)a.B * a.N * a.L * a.H * a.D;
+  if (pl.dq_fp32) MF_CUDA(cudaMemsetAsync(dq_acc, 0, sizeof(float) * (size_t)n_dq, st));
+
+  float alpha[2];
+  const int n_alpha = split_alpha(a.D, bt_dtype, alpha);
+  // ---- dQ, dK, dV
+  {
+    BwdWsP p{};
+    p.B = a.B; p.N = a.N; p.L = a.L; p.H = a.H; p.D = a.D;
+    p.n_t = pl.nt; p.lpad = lpad; p.ksplit = pl.ksplit; p.dq_stream = pl.dq_stream; p.dbuf = pl.dbuf;
+    p.n_items = a.B * a.N * a.H * pl.ksplit;
+    p.dq_acc = dq_acc;
+    p.scale = 1.0f / sqrtf((float)a.D); p.c1 = kLog2e * p.scale; p.inv_L = 1.0f / a.L;
+    p.fmt = a.dtype == MF_BF16 ? 1u : 0u; p.bfmt = bt_dtype == MF_BF16 ? 1u : 0u;
+    p.n_alpha = n_alpha; p.alpha[0] = alpha[0]; p.alpha[1] = alpha[1];
+    p.bias_b_mul = 1;
+    p.mask = a.mask; for (int i = 0; i < 3; ++i) p.ms[i] = a.mask_strides[i];
+    p.mask_dtype = a.mask_dtype;
+    p.lse = a.lse; p.delta = delta;
+    p.dq = a.dq; p.dk = a.dk; p.dv = a.dv;
+    p.status = status;
+    const size_t smem = 1024 + 4 * (size_t)kAtomB + 3 * kAtomB + 10 * kTileB + 2048 + 4 * sizeof(float) * lpad;
+    int grid = sm_count();
+    if (grid > p.n_items) grid = p.n_items;
+    if (pl.dq_stream) {
+      auto kern = evo_bwd_ws_kernel<T, TT, true>;
+      MF_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      kern<<<grid, kThreads, smem, st>>>(mq, mk, mv, mg, mbt, p);
+    } else {
+      auto kern = evo_bwd_ws_kernel<T, TT, false>;
+      MF_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      kern<<<grid, kThreads, smem, st>>>(mq, mk, mv, mg, mbt, p);
+    }
+    MF_LAUNCHED("evo_bwd_ws_kernel");
+  }
+  if (pl.dq_fp32) {
+    cast_rows_ws_kernel<T><<<(unsigned)((n_dq + 255) / 256), 256, 0, st>>>(dq_acc, static_cast<T*>(a.dq), n_dq);
+    MF_LAUNCHED("cast_rows_ws_kernel");
+  }
+  // ---- dBias
+  {
+    DbP p{};
+    p.B = a.B; p.N = a.N; p.L = a.L; p.H = a.H; p.D = a.D;
+    p.n_t = pl.nt; p.lpad = lpad; p.nsplit = pl.nsplit;
+    p.n_units = a.B * a.H * pl.nt * pl.nt * pl.nsplit;
+    p.c1 = kLog2e / sqrtf((float)a.D);
+    p.fmt = a.dtype == MF_BF16 ? 1u : 0u; p.bfmt = bt_dtype == MF_BF16 ? 1u : 0u;
+    p.n_alpha = n_alpha; p.alpha[0] = alpha[0]; p.alpha[1] = alpha[1];
+    p.bias_b_mul = 1;
+    p.mask = a.mask; for (int i = 0; i < 3; ++i) p.ms[i] = a.mask_strides[i];
+    p.mask_dtype = a.mask_dtype;
+    p.lse = a.lse; p.delta = delta;
+    p.part = part;
+    p.status = status;
+    const size_t smem = 1024 + 2 * (size_t)kAtomB + 12 * kTileB + 2048 + 3 * 256 * sizeof(float);
+    int grid = sm_count();
+    if (grid > p.n_units) grid = p.n_units;
+    auto kern = evo_dbias_ws_kernel<T, TT>;
+    MF_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kern<<<grid, kThreads, smem, st>>>(mq, mk, mv, mg, mbt, p);
+    MF_LAUNCHED("evo_dbias_ws_kernel");
+    if (!pl.part_direct) {
+      const int64_t n_out = (int64_t)a.B * a.H * a.L * a.L;
+      if (a.dbias_dtype == MF_F32)
+        dbias_finish_kernel<float><<<(unsigned)((n_out + 255) / 256), 256, 0, st>>>(part, static_cast<float*>(a.d_bias), n_out, pl.nsplit);
+      else
+        dbias_finish_kernel<T><<<(unsigned)((n_out + 255) / 256), 256, 0, st>>>(part, static_cast<T*>(a.d_bias), n_out, pl.nsplit);
+      MF_LAUNCHED("dbias_finish_kernel");
+    }
+  }
+  return MF_OK;
+}
+
+}  // namespace
+
+bool evo_bwd_ws_shape_ok(int L, int D) {
+  // head sizes above 32 would need more shared memory than an SM has with this tiling; rows longer than 1024 tokens
+  // more than it has for the per-row statistics
+  return D <= 32 && L <= 1024;
+}
+
+size_t evo_bwd_ws_workspace(const mf_evo_bwd_args& a) { return plan_bwd(a).total; }
+
+#define MF_DISPATCH_BIAS(dt, TB, ...)                                         \
+  switch (dt) {                                                               \
+    case MF_F32: { using TB = float; __VA_ARGS__; } break;                    \
+    case MF_BF16: { using TB = __nv_bfloat16; __VA_ARGS__; } break;           \
+    case MF_F16: { using TB = __half; __VA_ARGS__; } break;                   \
+    default: return fail(MF_ERR_BAD_ARG, "unknown bias dtype %d", (int)(dt)); \
+  }
+
+int evo_bwd_ws(const mf_evo_bwd_args& a, cudaStream_t st) {
+  int r = MF_OK;
+  if (a.dtype == MF_BF16) {
+    MF_DISPATCH_BIAS(a.bias_dtype, TB, { r = launch_bwd_ws<__nv_bfloat16, TB>(a, st); });
+  } else {
+    MF_DISPATCH_BIAS(a.bias_dtype, TB, { r = launch_bwd_ws<__half, TB>(a, st); });
+  }
+  return r;
+}
+
+}  // namespace mf

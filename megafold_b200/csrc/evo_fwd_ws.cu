@@ -1,0 +1,427 @@
+// Pair-biased masked attention forward, warp-specialised (tcgen05 + TMEM + TMA), head sizes up to 32.
+//
+// A persistent CTA (one per SM, 384 threads) runs TWO independent streams.  A stream walks a contiguous range of
+// work items (b, n, h, 128-query tile) and, per item, the key tiles of 128.  Roles:
+//
+//   warps 0-3 / 4-7   softmax warpgroup of stream 0 / 1: one query row (= one TMEM lane) per thread
+//   warp 8 / 9        tcgen05.mma issuer of stream 0 / 1 (one thread)
+//   warp 10 / 11      TMA producer of stream 0 / 1 (one thread)
+//
+// Per key tile the issuer builds   S = Q K^T + sqrt(D) * bias   entirely on the tensor core: two MMAs for Q K^T and
+// eight [128 x 16] x [16 x 16] MMAs that add the bias tile (A operand, straight from the TMA-loaded tile) times
+// alpha * I (B operand) - see evo_tc_common.cuh.  The softmax thread reads its 128 logits, scales them into the base-2
+// domain with the key mask added (one packed FMA per two logits), takes the maximum with three-input max, and writes
+// packed 16-bit P = 2^(x - m) back to TMEM.  P V accumulates into O in TMEM over the key tiles, and a second product
+// P * ones accumulates the row sum next to it, so the softmax threads neither add nor rescale: O and the sum are
+// only multiplied by 2^(m_old - m_new) when the running maximum has grown by more than 8 (rare after the first
+// tile; P then stays below 2^8, far inside the 16-bit range).  Only O and the log-sum-exp reach global memory.
+//
+// Every wait is bounded; on expiry the CTA raises a flag, all roles run dry without touching global memory, TMEM is
+// freed and the host sees mf_async_status() != 0.
+#include "evo_tc_common.cuh"
+
+namespace mf {
+namespace {
+using namespace tcx;
+
+constexpr int kT = 128;                      // tile edge (queries and keys)
+constexpr int kThreads = 384;
+constexpr int kTileB = 128 * 64;             // [128 x 32] 16-bit tile, 64-byte rows, 64B swizzle
+constexpr int kAtomB = 128 * 128;            // bias atom: [128 rows x 64 columns] 16-bit, 128-byte rows, 128B swizzle
+constexpr int kStreamBytes = 6 * kTileB + 3 * kAtomB;     // Q x2, K x2, V x2, three bias atoms
+constexpr float kRescaleStep = 8.f;          // O is rescaled only when the running maximum grows by more than this (base 2)
+
+struct FwdWsP {
+  int B, N, L, H, D;
+  int n_qt, n_kt, n_items, lpad, items_per_stream, bias_b_mul;
+  float c1;               // D^-1/2 * log2(e)
+  uint32_t fmt, bfmt;     // tcgen05 operand formats of q/k/v and of the bias (1 = bf16, 0 = f16)
+  int n_alpha; float alpha[2];
+  const void* mask; int64_t ms[3]; int mask_dtype;
+  void* o; float* lse; int* status;
+};
+
+struct StreamBars {
+  uint64_t q_full[2], q_empty[2], k_full[2], k_empty[2], v_full[2], v_empty[2], b_full[3], b_empty[3];
+  uint64_t s_ready, s_free, p_ready, pv_done;
+};
+
+// position of a stream's work item
+struct ItemPos { int qt, h, n, b, bn; };
+__device__ __forceinline__ ItemPos item_pos(int it, const FwdWsP& p) {
+  ItemPos x;
+  x.qt = it % p.n_qt;
+  const int r = it / p.n_qt;
+  x.h = r % p.H; x.bn = r / p.H; x.n = x.bn % p.N; x.b = x.bn / p.N;
+  return x;
+}
+
+template <typename T, typename TB>
+__global__ void __launch_bounds__(kThreads, 1)
+evo_fwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mk,
+                  const __grid_constant__ CUtensorMap mv, const __grid_constant__ CUtensorMap mb, const FwdWsP p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* sOnes = smem + 2 * kStreamBytes;           // [128 x 32] ones, V-tile layout (every element equal: no swizzle to mind)
+  uint8_t* sI = sOnes + kTileB;                       // alpha * I tiles, 1 KB each
+  float* mask2_all = reinterpret_cast<float*>(sI + 2048);
+
+  __shared__ StreamBars bars[2];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_s;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {
+    abort_s = 0;
+    for (int q = 0; q < 2; ++q) {
+      StreamBars& b = bars[q];
+      for (int i = 0; i < 2; ++i) {
+        mbar_init(&b.q_full[i], 1); mbar_init(&b.q_empty[i], 1); mbar_init(&b.k_full[i], 1); mbar_init(&b.k_empty[i], 1);
+        mbar_init(&b.v_full[i], 1); mbar_init(&b.v_empty[i], 1);
+      }
+      for (int i = 0; i < 3; ++i) { mbar_init(&b.b_full[i], 1); mbar_init(&b.b_empty[i], 1); }
+      mbar_init(&b.s_ready, 1); mbar_init(&b.pv_done, 1);
+      mbar_init(&b.s_free, 4); mbar_init(&b.p_ready, 4);          // one arrival per softmax warp
+    }
+    mbar_fence_init();
+    prefetch_tmap(&mq); prefetch_tmap(&mk); prefetch_tmap(&mv); prefetch_tmap(&mb);
+  }
+  // constant MMA operands: ones (row sums) and alpha * I (bias)
+  for (int e = tid; e < kTileB / 4; e += kThreads) reinterpret_cast<uint32_t*>(sOnes)[e] = Pack2<T>::pack(1.f, 1.f);
+  write_alpha_identity<TB>(sI, p.alpha[0], tid, kThreads);
+  write_alpha_identity<TB>(sI + 1024, p.alpha[1], tid, kThreads);
+  fence_async_smem();
+  if (warp == 0) { tmem_alloc(&tmem_base_s, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  volatile int* abort_flag = &abort_s;
+
+  const int s = warp < 8 ? (warp >> 2) : (warp & 1);          // stream of this warp
+  StreamBars& bar = bars[s];
+  uint8_t* sb = smem + s * kStreamBytes;
+  uint8_t* sQ = sb;
+  uint8_t* sK = sb + 2 * kTileB;
+  uint8_t* sV = sb + 4 * kTileB;
+  uint8_t* sB = sb + 6 * kTileB;
+  const uint32_t tbase = tmem_base_s + s * 256;               // S [0,128) | P [128,192) | O [192,224) | row sum [224,256)
+
+  const int stream = blockIdx.x * 2 + s;
+  const int item_begin = stream * p.items_per_stream;
+  int item_end = item_begin + p.items_per_stream;
+  if (item_end > p.n_items) item_end = p.n_items;
+  const int n_my = item_end > item_begin ? item_end - item_begin : 0;
+  const int n_kt = p.n_kt;
+
+  if (warp < 8) {
+    // =========================================================================== softmax warpgroup
+    // Register re-partition: the CTA is launched with 168 registers per thread; the helper warpgroup drops to 88 and the
+    // softmax warpgroups rise to 208.  The raise can only draw on what the drop releases inside this CTA.
+    static_assert(256 * 208 + 128 * 88 <= kThreads * 168, "setmaxnreg budget");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
+    const int wg_tid = tid & 127;
+    const int r = (warp & 3) * 32 + lane;
+    const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t tS = tbase + lane_addr, tP = tS + 128, tO = tS + 192, tL = tS + 224;
+    float* mask2 = mask2_all + s * p.lpad;
+    const float2 c1c1 = make_float2(p.c1, p.c1);
+    int prev_bn = -1;
+    uint32_t g = 0;
+    for (int il = 0; il < n_my; ++il) {
+      const ItemPos ip = item_pos(item_begin + il, p);
+      const int i = ip.qt * kT + r;
+      if (ip.bn != prev_bn) {
+        // additive key terms of row (b, n) in the base-2 domain; columns beyond L are -inf
+        named_sync(1 + s, 128);
+        for (int j = wg_tid; j < p.lpad; j += 128) {
+          float v = -INFINITY;
+          if (j < p.L) {
+            const int64_t mi = ip.b * p.ms[0] + ip.n * p.ms[1] + j * p.ms[2];
+            v = p.mask_dtype == MF_U8 ? (static_cast<const uint8_t*>(p.mask)[mi] ? 0.f : -FLT_MAX)
+                                      : load_rt(p.mask, mi, p.mask_dtype) * kLog2e;
+          }
+          mask2[j] = v;
+        }
+        named_sync(1 + s, 128);
+        prev_bn = ip.bn;
+      }
+      float m_used = 0.f;
+      for (int t = 0; t < n_kt; ++t, ++g) {
+        // ---------------------------------------------------------------- S(g) -> registers
+        wait_or_flag(&bar.s_ready, g & 1, abort_flag);
+        tc_fence_after();
+        uint32_t sr[kT];
+        {
+          uint32_t (*s4)[32] = reinterpret_cast<uint32_t (*)[32]>(sr);
+          tmem_ld32(tS, s4[0]); tmem_ld32(tS + 32, s4[1]); tmem_ld32(tS + 64, s4[2]); tmem_ld32(tS + 96, s4[3]);
+          tmem_ld_wait();
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar.s_free);          // the issuer may overwrite S with the next tile's scores
+        // ---------------------------------------------------------------- pass 1: base-2 logits and their maximum
+        const float* mk = mask2 + t * kT;
+        float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int c4 = 0; c4 < kT / 4; ++c4) {
+          const float4 m4 = *reinterpret_cast<const float4*>(mk + c4 * 4);
+          const float2 a = fma2(make_float2(__uint_as_float(sr[c4 * 4]), __uint_as_float(sr[c4 * 4 + 1])), c1c1, make_float2(m4.x, m4.y));
+          const float2 b2 = fma2(make_float2(__uint_as_float(sr[c4 * 4 + 2]), __uint_as_float(sr[c4 * 4 + 3])), c1c1, make_float2(m4.z, m4.w));
+          sr[c4 * 4] = __float_as_uint(a.x); sr[c4 * 4 + 1] = __float_as_uint(a.y);
+          sr[c4 * 4 + 2] = __float_as_uint(b2.x); sr[c4 * 4 + 3] = __float_as_uint(b2.y);
+          mx[c4 & 1 ? 2 : 0] = max3f(mx[c4 & 1 ? 2 : 0], a.x, a.y);
+          mx[c4 & 1 ? 3 : 1] = max3f(mx[c4 & 1 ? 3 : 1], b2.x, b2.y);
+        }
+        const float m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+        if (t == 0) {
+          m_used = m_blk;
+        } else {
+          const bool grow = m_blk > m_used + kRescaleStep;
+          if (__any_sync(0xffffffffu, grow)) {
+            // rare: bring O and the row sum of this warp's rows to the new maximum
+            wait_or_flag(&bar.pv_done, (g - 1) & 1, abort_flag);
+            tc_fence_after();
+            const float f = grow ? ex2f(m_used - m_blk) : 1.f;
+            if (grow) m_used = m_blk;
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf) {
+              uint32_t o16[16];
+              tmem_ld16(tO + hf * 16, o16);
+              tmem_ld_wait();
+#pragma unroll
+              for (int d = 0; d < 16; ++d) o16[d] = __float_as_uint(__uint_as_float(o16[d]) * f);
+              tmem_st16(tO + hf * 16, o16);
+            }
+            // of the 32 row-sum columns (all equal) only the first is ever read
+            const uint32_t l0 = tmem_ld1(tL);
+            tmem_ld_wait();
+            tmem_st1(tL, __float_as_uint(__uint_as_float(l0) * f));
+            tmem_st_wait();
+          }
+        }
+        // ---------------------------------------------------------------- pass 2: P = 2^(x - m) as packed 16-bit
+        if (g > 0) wait_or_flag(&bar.pv_done, (g - 1) & 1, abort_flag);      // the previous product has read P
+        const float2 mm = make_float2(m_used, m_used);
+#pragma unroll
+        for (int qr = 0; qr < 4; ++qr) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int jj = 0; jj < 16; ++jj) {
+            const float2 x = sub2(make_float2(__uint_as_float(sr[qr * 32 + 2 * jj]), __uint_as_float(sr[qr * 32 + 2 * jj + 1])), mm);
+            pk[jj] = Pack2<T>::pack(ex2f(x.x), ex2f(x.y));
+          }
+          tmem_st16(tP + qr * 16, pk);
+        }
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar.p_ready);
+      }
+      // ------------------------------------------------------------------ item done: O / l and the log-sum-exp
+      wait_or_flag(&bar.pv_done, (g - 1) & 1, abort_flag);
+      tc_fence_after();
+      uint32_t o32[32];
+      tmem_ld32(tO, o32);
+      const float l = __uint_as_float(tmem_ld1(tL));
+      tmem_ld_wait();
+      tc_fence_before();
+      if (i < p.L && !*abort_flag) {
+        const float inv = 1.f / l;
+        T* orow = static_cast<T*>(p.o) + ((((int64_t)ip.b * p.N + ip.n) * p.L + i) * p.H + ip.h) * p.D;
+#pragma unroll
+        for (int d8 = 0; d8 < 4; ++d8) {
+          if (d8 * 8 < p.D) {
+            uint4 v;
+            v.x = Pack2<T>::pack(__uint_as_float(o32[d8 * 8]) * inv, __uint_as_float(o32[d8 * 8 + 1]) * inv);
+            v.y = Pack2<T>::pack(__uint_as_float(o32[d8 * 8 + 2]) * inv, __uint_as_float(o32[d8 * 8 + 3]) * inv);
+            v.z = Pack2<T>::pack(__uint_as_float(o32[d8 * 8 + 4]) * inv, __uint_as_float(o32[d8 * 8 + 5]) * inv);
+            v.w = Pack2<T>::pack(__uint_as_float(o32[d8 * 8 + 6]) * inv, __uint_as_float(o32[d8 * 8 + 7]) * inv);
+            *reinterpret_cast<uint4*>(orow + d8 * 8) = v;
+          }
+        }
+        // a row whose keys are all masked keeps m = -FLT_MAX: its log-sum-exp is stored as -FLT_MAX, the value the
+        // backward kernels recognise
+        p.lse[(((int64_t)ip.b * p.N + ip.n) * p.H + ip.h) * p.L + i] = m_used <= -1e38f ? -FLT_MAX : (m_used + lg2f(l)) * kLn2;
+      }
+    }
+  } else {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");
+    if (warp < 10 && lane == 0) {
+      // ========================================================================= tcgen05.mma issuer of stream s
+      const uint32_t id_s = idesc_f16(128, 128, p.fmt, 0, 0);
+      const uint32_t id_b = idesc_f16(128, 16, p.bfmt, 0, 0);
+      const uint32_t id_o = idesc_f16(128, 32, p.fmt, 0, 1);           // B (V, ones) MN-major
+      constexpr uint32_t hi64 = desc_hi(512, kSw64), hi128 = desc_hi(1024, kSw128);
+      const uint32_t ones_lo = desc_lo(smem_u32(sOnes), 16);
+      const uint32_t tS = tbase, tP = tbase + 128, tO = tbase + 192, tL = tbase + 224;
+      uint32_t bslot = 0, buse = 0;               // bias atoms consumed: ring slot and use count of the next one
+      auto issue_s = [&](uint32_t g, int il, int t) {      // S(g) = Q K^T + alpha * bias
+        if (t == 0) wait_or_flag(&bar.q_full[il & 1], (il >> 1) & 1, abort_flag);
+        wait_or_flag(&bar.k_full[g & 1], (g >> 1) & 1, abort_flag);
+        const uint32_t slot0 = bslot, use0 = buse;
+        uint32_t slot1 = slot0 + 1, use1 = use0;
+        if (slot1 == 3) { slot1 = 0; ++use1; }
+        wait_or_flag(&bar.b_full[slot0], use0 & 1, abort_flag);
+        wait_or_flag(&bar.b_full[slot1], use1 & 1, abort_flag);
+        bslot = slot1 + 1; buse = use1;
+        if (bslot == 3) { bslot = 0; ++buse; }
+        if (g > 0) wait_or_flag(&bar.s_free, (g - 1) & 1, abort_flag);
+        tc_fence_after();
+        if (*abort_flag) return;
+        const uint32_t q_lo = desc_lo(smem_u32(sQ + (il & 1) * kTileB), 16), k_lo = desc_lo(smem_u32(sK + (g & 1) * kTileB), 16);
+#pragma unroll
+        for (int ks = 0; ks < 2; ++ks) mma_ss_lh(tS, q_lo + ks * 2, hi64, k_lo + ks * 2, hi64, id_s, ks > 0);
+        const uint32_t a_lo[2] = {desc_lo(smem_u32(sB + slot0 * kAtomB), 16), desc_lo(smem_u32(sB + slot1 * kAtomB), 16)};
+        for (int term = 0; term < p.n_alpha; ++term) {
+          const uint32_t i_lo = desc_lo(smem_u32(sI + term * 1024), 16);
+#pragma unroll
+          for (int c = 0; c < 8; ++c)       // 16 key columns each
+            mma_ss_lh(tS + c * 16, a_lo[c >> 2] + (c & 3) * 2, hi128, i_lo, hi64, id_b, true);
+        }
+        tc_commit(&bar.s_ready);
+        tc_commit(&bar.k_empty[g & 1]);
+        tc_commit(&bar.b_empty[slot0]);
+        tc_commit(&bar.b_empty[slot1]);
+        if (t == n_kt - 1) tc_commit(&bar.q_empty[il & 1]);
+      };
+      auto issue_pv = [&](uint32_t g, int t) {             // O (+)= P V,  row sum (+)= P ones
+        wait_or_flag(&bar.p_ready, g & 1, abort_flag);
+        wait_or_flag(&bar.v_full[g & 1], (g >> 1) & 1, abort_flag);
+        tc_fence_after();
+        if (*abort_flag) return;
+        const uint32_t v_lo = desc_lo(smem_u32(sV + (g & 1) * kTileB), 16);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) mma_ts_lh(tO, tP + ks * 8, v_lo + ks * 64, hi64, id_o, t > 0 || ks > 0);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) mma_ts_lh(tL, tP + ks * 8, ones_lo + ks * 64, hi64, id_o, t > 0 || ks > 0);
+        tc_commit(&bar.pv_done);
+        tc_commit(&bar.v_empty[g & 1]);
+      };
+      const uint32_t g_total = (uint32_t)n_my * n_kt;
+      if (g_total > 0) issue_s(0, 0, 0);
+      int il = 0, t = 0;
+      for (uint32_t g = 0; g < g_total; ++g) {
+        int il1 = il, t1 = t + 1;
+        if (t1 == n_kt) { t1 = 0; ++il1; }
+        if (g + 1 < g_total) issue_s(g + 1, il1, t1);
+        issue_pv(g, t);
+        il = il1; t = t1;
+      }
+    } else if (warp >= 10 && lane == 0) {
+      // ========================================================================= TMA producer of stream s
+      uint32_t g = 0, bslot = 0, buse = 0;
+      uint32_t nq = 0, nk = 0, nv = 0, nb = 0;      // loads issued, for the drain on abort
+      auto load_q = [&](int il) {        // the Q tile of item il (requested one key tile before the item starts)
+        const ItemPos iq = item_pos(item_begin + il, p);
+        if (il >= 2) wait_or_flag(&bar.q_empty[il & 1], ((il >> 1) - 1) & 1, abort_flag);
+        if (*abort_flag) return;
+        mbar_expect_tx(&bar.q_full[il & 1], kTileB);
+        tma_load_5d(sQ + (il & 1) * kTileB, &mq, &bar.q_full[il & 1], 0, iq.h, iq.qt * kT, iq.n, iq.b);
+        ++nq;
+      };
+      if (n_my > 0) load_q(0);
+      for (int il = 0; il < n_my && !*abort_flag; ++il) {
+        const ItemPos ip = item_pos(item_begin + il, p);
+        for (int t = 0; t < n_kt; ++t, ++g) {
+          if (t == n_kt - 1 && il + 1 < n_my) load_q(il + 1);
+          if (g >= 2) wait_or_flag(&bar.k_empty[g & 1], ((g >> 1) - 1) & 1, abort_flag);
+          if (*abort_flag) break;
+          mbar_expect_tx(&bar.k_full[g & 1], kTileB);
+          tma_load_5d(sK + (g & 1) * kTileB, &mk, &bar.k_full[g & 1], 0, ip.h, t * kT, ip.n, ip.b);
+          ++nk;
+          for (int hf = 0; hf < 2; ++hf) {
+            if (buse >= 1) wait_or_flag(&bar.b_empty[bslot], (buse - 1) & 1, abort_flag);
+            if (*abort_flag) break;
+            mbar_expect_tx(&bar.b_full[bslot], kAtomB);
+            tma_load_4d(sB + bslot * kAtomB, &mb, &bar.b_full[bslot], t * kT + hf * 64, ip.qt * kT, ip.h, ip.b * p.bias_b_mul);
+            ++nb;
+            if (++bslot == 3) { bslot = 0; ++buse; }
+          }
+          if (g >= 2) wait_or_flag(&bar.v_empty[g & 1], ((g >> 1) - 1) & 1, abort_flag);
+          if (*abort_flag) break;
+          mbar_expect_tx(&bar.v_full[g & 1], kTileB);
+          tma_load_5d(sV + (g & 1) * kTileB, &mv, &bar.v_full[g & 1], 0, ip.h, t * kT, ip.n, ip.b);
+          ++nv;
+        }
+      }
+      if (*abort_flag) {
+        // the copies already requested must land before the CTA's shared memory is given back (bounded)
+        auto drain = [&](uint64_t* ring, uint32_t n, uint32_t depth) {
+          for (uint32_t back = 0; back < depth && back < n; ++back) {
+            const uint32_t c = n - 1 - back;
+            mbar_wait(&ring[c % depth], (c / depth) & 1);
+          }
+        };
+        drain(bar.q_full, nq, 2); drain(bar.k_full, nk, 2); drain(bar.v_full, nv, 2); drain(bar.b_full, nb, 3);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (tid == 0 && abort_s) *reinterpret_cast<volatile int*>(p.status) = 1;
+  if (warp == 0) tmem_dealloc(tmem_base_s, 512);
+}
+
+template <typename T, typename TB>
+int launch_fwd_ws(const mf_evo_fwd_args& a, cudaStream_t st) {
+  CUtensorMap mq, mk, mv, mb;
+  int r;
+  if ((r = make_qkv_map(&mq, a.q, a.dtype, a.B, a.N, a.L, a.H, a.D, a.q_strides, 32, kT))) return r;
+  if ((r = make_qkv_map(&mk, a.k, a.dtype, a.B, a.N, a.L, a.H, a.D, a.k_strides, 32, kT))) return r;
+  if ((r = make_qkv_map(&mv, a.v, a.dtype, a.B, a.N, a.L, a.H, a.D, a.v_strides, 32, kT))) return r;
+  FwdWsP p{};
+  p.B = a.B; p.N = a.N; p.L = a.L; p.H = a.H; p.D = a.D;
+  p.n_qt = (a.L + kT - 1) / kT; p.n_kt = p.n_qt;
+  p.n_items = a.B * a.N * a.H * p.n_qt;
+  p.lpad = p.n_kt * kT;
+  p.c1 = kLog2e / sqrtf((float)a.D);
+  p.fmt = a.dtype == MF_BF16 ? 1u : 0u;
+  p.bfmt = a.bias_dtype == MF_BF16 ? 1u : 0u;
+  p.n_alpha = split_alpha(a.D, a.bias_dtype, p.alpha);
+  p.mask = a.mask; for (int i = 0; i < 3; ++i) p.ms[i] = a.mask_strides[i];
+  p.mask_dtype = a.mask_dtype;
+  p.o = a.o; p.lse = a.lse;
+  p.status = status_word();
+  MF_REQUIRE(p.status, MF_ERR_CUDA, "could not allocate the device status word");
+  MF_REQUIRE(tc_async_status() == 0, MF_ERR_CUDA, "an earlier tensor-core kernel gave up on a bounded wait; results are invalid");
+  p.bias_b_mul = a.bias_strides[0] == 0 ? 0 : 1;
+  {
+    const int64_t dims[4] = {a.L, a.L, a.H, p.bias_b_mul ? a.B : 1};
+    const int64_t str[4] = {1, a.bias_strides[2], a.bias_strides[1], a.bias_strides[0]};
+    const int box[4] = {64, 128, 1, 1};
+    if ((r = make_tiled_map(&mb, a.bias, a.bias_dtype, 4, dims, str, box, 128))) return r;
+  }
+  int grid = sm_count();
+  const int pairs = (p.n_items + 1) / 2;
+  if (grid > pairs) grid = pairs;
+  p.items_per_stream = (p.n_items + 2 * grid - 1) / (2 * grid);
+  const size_t smem = 1024 + 2 * (size_t)kStreamBytes + kTileB + 2048 + 2 * sizeof(float) * p.lpad;
+  auto kern = evo_fwd_ws_kernel<T, TB>;
+  MF_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  kern<<<grid, kThreads, smem, st>>>(mq, mk, mv, mb, p);
+  MF_LAUNCHED("evo_fwd_ws_kernel");
+  return MF_OK;
+}
+
+}  // namespace
+
+// The warp-specialised kernel covers head sizes up to 32, rows up to 2048 tokens and a 16-bit pair bias whose rows
+// TMA can address (unit stride on keys, 16-byte multiples elsewhere); other calls use the general kernel.
+bool evo_fwd_ws_supported(const mf_evo_fwd_args& a) {
+  if (a.D > 32 || a.L > 2048) return false;
+  if (a.bias_dtype != MF_BF16 && a.bias_dtype != MF_F16) return false;
+  const int64_t* s = a.bias_strides;
+  if (s[3] != 1 || (reinterpret_cast<uintptr_t>(a.bias) & 15) != 0) return false;
+  if ((s[2] * 2) % 16 != 0 || s[2] <= 0) return false;
+  if (a.H > 1 && ((s[1] * 2) % 16 != 0 || s[1] <= 0)) return false;
+  if (a.B > 1 && s[0] != 0 && ((s[0] * 2) % 16 != 0 || s[0] < 0)) return false;
+  return true;
+}
+
+int evo_fwd_ws(const mf_evo_fwd_args& a, cudaStream_t st) {
+  if (a.dtype == MF_BF16)
+    return a.bias_dtype == MF_BF16 ? launch_fwd_ws<__nv_bfloat16, __nv_bfloat16>(a, st) : launch_fwd_ws<__nv_bfloat16, __half>(a, st);
+  return a.bias_dtype == MF_BF16 ? launch_fwd_ws<__half, __nv_bfloat16>(a, st) : launch_fwd_ws<__half, __half>(a, st);
+}
+
+}  // namespace mf

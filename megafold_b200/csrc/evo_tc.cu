@@ -1,5 +1,7 @@
 // Host-side support shared by the tensor-core attention kernels: status word, device queries and the
 // test that decides whether a call can take the tensor-core path.
+#include <stdlib.h>
+
 #include "evo_tc_common.cuh"
 
 namespace mf {
@@ -45,5 +47,11 @@ bool evo_tc_supported(int B, int N, int L, int H, int D, int dtype, const int64_
 }
 
 bool evo_bwd_tc_available() { return true; }
+
+bool debug_old_evo(int which) {
+  static const bool f = [] { const char* e = getenv("MF_DEBUG_OLD_EVO_FWD"); return e && e[0] == '1'; }();
+  static const bool b = [] { const char* e = getenv("MF_DEBUG_OLD_EVO_BWD"); return e && e[0] == '1'; }();
+  return which == 0 ? f : b;
+}
 
 }  // namespace mf

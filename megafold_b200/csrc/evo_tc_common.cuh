@@ -23,6 +23,7 @@ __device__ __forceinline__ void wait_or_flag(uint64_t* bar, uint32_t parity, vol
   // cheap non-blocking probe first: try_wait costs ~270 cycles even when the phase is already complete (measured with
   // clock stamps in the MMA issuer threads), and that is the common case for the threads that issue MMAs and TMA copies
   if (mbar_test(bar, parity)) return;
+  if (*abort_flag) return;            // the CTA is already draining: nobody blocks any more
   for (uint32_t i = 0; i < kWaitCap; ++i) {
     if (mbar_try_wait(bar, parity)) return;
     if ((i & 63u) == 63u && *abort_flag) return;
@@ -57,6 +58,61 @@ __device__ __forceinline__ float lg2f(float x) {
   return y;
 }
 
+// ---- packed fp32 pairs (one issue slot for two lanes of work) and the three-input maximum ------------
+__device__ __forceinline__ uint64_t pack_f2(float a, float b) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ float2 unpack_f2(uint64_t r) {
+  float2 d;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(r));
+  return d;
+}
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(pack_f2(a.x, a.y)), "l"(pack_f2(b.x, b.y)), "l"(pack_f2(c.x, c.y)));
+  return unpack_f2(d);
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(pack_f2(a.x, a.y)), "l"(pack_f2(b.x, b.y)));
+  return unpack_f2(d);
+}
+__device__ __forceinline__ float2 sub2(float2 a, float2 b) {
+  uint64_t d;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(pack_f2(a.x, a.y)), "l"(pack_f2(b.x, b.y)));
+  return unpack_f2(d);
+}
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+  uint64_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(pack_f2(a.x, a.y)), "l"(pack_f2(b.x, b.y)));
+  return unpack_f2(d);
+}
+__device__ __forceinline__ float max3f(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
+// One 32-bit column of this thread's TMEM lane
+__device__ __forceinline__ uint32_t tmem_ld1(uint32_t taddr) {
+  uint32_t r;
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r) : "r"(taddr) : "memory");
+  return r;
+}
+__device__ __forceinline__ void tmem_st1(uint32_t taddr, uint32_t v) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(taddr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+      "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+
 template <typename T> struct Pack2;
 template <> struct Pack2<__nv_bfloat16> {
   static __device__ __forceinline__ uint32_t pack(float a, float b) {
@@ -88,7 +144,32 @@ __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* m, uin
       : "memory");
 }
 
+// ---- the pair bias through the tensor core ----------------------------------------------------------
+// logits * sqrt(D) = Q K^T + sqrt(D) * bias.  The second term is a matrix product too: bias tile (A operand, 16 columns
+// at a time) times alpha * I_16 (B operand) lands in 16 columns of the score accumulator, so no thread ever touches a
+// bias value.  alpha = sqrt(D) is split into one or two terms of the bias dtype (hi + lo), each with its own B tile.
+// Layout of one B tile: K-major [16 rows x 32 columns], 64-byte rows, 64B swizzle (1 KB, 1024-byte aligned); only the
+// first 16 columns (one MMA K step) are used.
+template <typename TB>
+__device__ __forceinline__ void write_alpha_identity(uint8_t* tile, float alpha, int tid, int nthreads) {
+  for (int e = tid; e < 16 * 32; e += nthreads) {
+    const int n = e >> 5, k = e & 31;
+    *reinterpret_cast<TB*>(tile + swz_offset(n, k >> 3, 64) + (k & 7) * 2) = from_f<TB>(k == n ? alpha : 0.f);
+  }
+}
+
 // ---- host side ------------------------------------------------------------------------------------
+// sqrt(D) as a sum of values representable in the 16-bit type `dt`; returns the number of terms (1 when the first
+// one is within 2.5e-4 relative, which is below the rounding of the bias values themselves)
+inline int split_alpha(int D, int dt, float (&alpha)[2]) {
+  const float a = sqrtf((float)D);
+  const float hi = dt == MF_BF16 ? __bfloat162float(__float2bfloat16_rn(a)) : __half2float(__float2half_rn(a));
+  const float rest = a - hi;
+  const float lo = dt == MF_BF16 ? __bfloat162float(__float2bfloat16_rn(rest)) : __half2float(__float2half_rn(rest));
+  alpha[0] = hi; alpha[1] = lo;
+  return fabsf(rest) > 2.5e-4f * a ? 2 : 1;
+}
+
 typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
