@@ -12,7 +12,7 @@ import threading
 import torch
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "libmegafold_b200.so")
+LIB_PATH = os.path.join(_PKG, "libmegafold_b200_trace.so" if os.environ.get("MF_TRACE") == "1" else "libmegafold_b200.so")
 
 MF_F32, MF_BF16, MF_F16, MF_U8 = 0, 1, 2, 3
 MF_FLAG_FORCE_SIMT = 1

@@ -16,8 +16,11 @@ from concurrent.futures import ThreadPoolExecutor
 PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 ROOT = os.path.dirname(PKG)
-LIB = os.path.join(PKG, "libmegafold_b200.so")
-OBJ_DIR = os.path.join(PKG, "build")
+# MF_TRACE=1 in the environment builds the phase-trace variant (-DMF_TRACE, see csrc/evo_tc_common.cuh) next to the
+# regular library; megafold_b200._lib loads it when MF_TRACE=1 is set there too.
+TRACE = os.environ.get("MF_TRACE") == "1"
+LIB = os.path.join(PKG, "libmegafold_b200_trace.so" if TRACE else "libmegafold_b200.so")
+OBJ_DIR = os.path.join(PKG, "build_trace" if TRACE else "build")
 
 SOURCES = ["api.cu", "evo_simt.cu", "evo_tc.cu", "evo_tc_fwd.cu", "evo_fwd_ws.cu", "evo_tc_bwd.cu", "evo_bwd_ws.cu", "lnl_simt.cu", "lnl_tc.cu", "transition_tc.cu", "gemm_tc.cu", "transition_bwd_tc.cu"]
 NVCC_FLAGS = [
@@ -56,7 +59,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     for src in SOURCES:
         obj = os.path.join(OBJ_DIR, src.replace(".cu", ".o"))
         if force or _stale(obj, _deps(src)):
-            cmd = [nvcc, *NVCC_FLAGS, "-c", os.path.join(CSRC, src), "-o", obj]
+            cmd = [nvcc, *NVCC_FLAGS, *(["-DMF_TRACE"] if TRACE else []), "-c", os.path.join(CSRC, src), "-o", obj]
             if verbose:
                 cmd.insert(1, "-Xptxas=-v")
             jobs.append(cmd)

@@ -37,6 +37,10 @@ constexpr int kThreads = (kComputeWarps + 4) * 32;
 constexpr int kTileB = 128 * 64;    // [128 x 32] 16-bit operand tile, 64-byte rows, 64B swizzle
 constexpr int kAtomB = 128 * 128;   // [128 x 64] 16-bit tile, 128-byte rows, 128B swizzle (bias^T atoms, dS^T atoms)
 constexpr int kDP = 32;             // padded head size
+// registers per thread: at launch (640 threads) / compute warps / helper warps after setmaxnreg.  The raise of the
+// compute warps can only draw on what the helper warps release inside the CTA - otherwise it never returns.
+constexpr int kLaunchRegs = 96, kComputeRegs = 104, kHelperRegs = 64;
+static_assert(kComputeWarps * 32 * kComputeRegs + 128 * kHelperRegs <= kThreads * kLaunchRegs, "setmaxnreg budget");
 
 struct BwdWsP {
   int B, N, L, H, D;
@@ -50,39 +54,57 @@ struct BwdWsP {
   int n_alpha; float alpha[2];
   int bias_b_mul;
   const void* mask; int64_t ms[3]; int mask_dtype;
-  const float* lse; const float* delta;
+  const float* stats; const int* flags;     // per-query statistics and per-(b,n,h) careful-path flags (evo_stats_ws_kernel)
   void *dq, *dk, *dv;
   int* status;
 };
 
 struct Bars {
   uint64_t kv_full[2], kv_empty[2], qd_full[3], qd_empty[3], bt_full[3], bt_empty[3];
-  uint64_t sd_ready[2], written[2], buf_free[2], blk_done[2];
+  uint64_t sd_ready[2], written[2], buf_free[2];
+  uint64_t ds_written[2], dq_done[2];        // per block parity: dS^T tile complete in shared memory / its dQ product complete
+  uint64_t kv_done;                          // the dK / dV accumulation of a key tile is complete
   uint64_t st_full[2], st_empty[2];          // per-item statistics (lse, delta) in two buffers
   uint64_t kv_drained, dq_drained[2];
-  int special[2];
 };
 
-// delta[b,n,h,i] = sum_d dO * O; one thread per (b,n,i,h) row, 16-byte loads (D is a multiple of 8)
+// 1-D bulk copy global -> shared, completion counted in bytes on `bar` (addresses and size multiples of 16 bytes)
+__device__ __forceinline__ void bulk_load_1d(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
+// Per-query statistics for the backward kernels, in the layout they fetch with bulk copies:
+//   st[bnh][0][i] = lse * log2(e)   (+inf for padding rows i >= L and for fully masked rows, so that P = 0 there)
+//   st[bnh][1][i] = delta = sum_d dO * O   (0 for padding rows)
+// with rows padded to `lpad`; flags[bnh] is raised when the (b, n, h) row has a fully masked query (lse = -FLT_MAX).
+// One thread per (b, n, i, h), 16-byte loads (D is a multiple of 8).
 template <typename T>
-__global__ void evo_delta_ws_kernel(const T* __restrict__ o, const T* __restrict__ d_o, float* __restrict__ delta,
-                                    int64_t rows, int L, int H, int D) {
-  const int64_t row = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (row >= rows) return;
-  const uint4* po = reinterpret_cast<const uint4*>(o + row * D);
-  const uint4* pg = reinterpret_cast<const uint4*>(d_o + row * D);
-  float s = 0.f;
-  for (int c = 0; c < D / 8; ++c) {
-    const uint4 a = __ldg(po + c), g = __ldg(pg + c);
-    const uint32_t av[4] = {a.x, a.y, a.z, a.w}, gv[4] = {g.x, g.y, g.z, g.w};
+__global__ void evo_stats_ws_kernel(const T* __restrict__ o, const T* __restrict__ d_o, const float* __restrict__ lse,
+                                    float* __restrict__ st, int* __restrict__ flags, int64_t rows_pad, int L, int lpad, int H, int D) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= rows_pad) return;
+  const int h = (int)(idx % H); const int64_t t = idx / H; const int i = (int)(t % lpad); const int64_t bn = t / lpad;
+  const int64_t bnh = bn * H + h;
+  float l2 = INFINITY, dl = 0.f;
+  if (i < L) {
+    const int64_t row = (bn * L + i) * H + h;
+    const uint4* po = reinterpret_cast<const uint4*>(o + row * D);
+    const uint4* pg = reinterpret_cast<const uint4*>(d_o + row * D);
+    for (int c = 0; c < D / 8; ++c) {
+      const uint4 a = __ldg(po + c), g = __ldg(pg + c);
+      const uint32_t av[4] = {a.x, a.y, a.z, a.w}, gv[4] = {g.x, g.y, g.z, g.w};
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const float2 x = Pack2<T>::unpack(av[e]), y = Pack2<T>::unpack(gv[e]);
-      s = fmaf(x.x, y.x, s); s = fmaf(x.y, y.y, s);
+      for (int e = 0; e < 4; ++e) {
+        const float2 x = Pack2<T>::unpack(av[e]), y = Pack2<T>::unpack(gv[e]);
+        dl = fmaf(x.x, y.x, dl); dl = fmaf(x.y, y.y, dl);
+      }
     }
+    const float lv = lse[bnh * L + i];
+    if (lv <= -3e38f) flags[bnh] = 1; else l2 = lv * kLog2e;
   }
-  const int h = (int)(row % H); const int64_t t = row / H; const int i = (int)(t % L); const int64_t bn = t / L;
-  delta[(bn * H + h) * L + i] = s;
+  st[bnh * 2 * lpad + i] = l2;
+  st[bnh * 2 * lpad + lpad + i] = dl;
 }
 
 // biasT[b][h][j][i] = bias[b][h][i][j] in the 16-bit type TO, rows padded to `lpad` entries (the padding is zeroed by
@@ -104,26 +126,27 @@ __global__ void transpose_bias_ws_kernel(const TB* __restrict__ bias, TO* __rest
   }
 }
 
-// P^T and dS^T of one thread: key row (mask term `mk`), 32 query columns whose statistics sit at l2 / dl.
+// P^T and dS^T of one thread: key row (mask term `mk`), 16 query columns whose statistics sit at l2 / dl.
 // sr: c1-unscaled scores S''^T, dr: dP^T.  Results packed two queries per word.
 template <typename T, bool CAREFUL>
-__device__ __forceinline__ void p_and_ds(const uint32_t (&sr)[32], const uint32_t (&dr)[32], const float* __restrict__ l2,
+__device__ __forceinline__ void p_and_ds(const uint32_t (&sr)[16], const uint32_t (&dr)[16], const float* __restrict__ l2,
                                          const float* __restrict__ dl, float c1, float mk, bool key_ok, bool masked_key,
-                                         float inv_L, uint32_t (&pp)[16], uint32_t (&dd)[16]) {
+                                         float inv_L, uint32_t* __restrict__ pp, uint32_t* __restrict__ dd) {
   const float2 c1c1 = make_float2(c1, c1), mm = make_float2(mk, mk);
 #pragma unroll
-  for (int c4 = 0; c4 < 8; ++c4) {
+  for (int c4 = 0; c4 < 4; ++c4) {
     const float4 l4 = *reinterpret_cast<const float4*>(l2 + c4 * 4);
     const float4 d4 = *reinterpret_cast<const float4*>(dl + c4 * 4);
     const float2 x0 = fma2(make_float2(__uint_as_float(sr[c4 * 4]), __uint_as_float(sr[c4 * 4 + 1])), c1c1, sub2(mm, make_float2(l4.x, l4.y)));
     const float2 x1 = fma2(make_float2(__uint_as_float(sr[c4 * 4 + 2]), __uint_as_float(sr[c4 * 4 + 3])), c1c1, sub2(mm, make_float2(l4.z, l4.w)));
     float2 p0 = make_float2(ex2f(x0.x), ex2f(x0.y)), p1 = make_float2(ex2f(x1.x), ex2f(x1.y));
-    if (CAREFUL) {       // a fully masked query row is uniform over the keys of the row
+    if (CAREFUL) {       // a fully masked query row (statistic +inf) is uniform over the keys of the row; padding rows
+                         // share the mark, harmlessly: their dO, dP and delta are zero
       const float u = key_ok ? inv_L : 0.f;
-      if (l4.x <= -3e38f) p0.x = u;
-      if (l4.y <= -3e38f) p0.y = u;
-      if (l4.z <= -3e38f) p1.x = u;
-      if (l4.w <= -3e38f) p1.y = u;
+      if (l4.x >= 3e38f) p0.x = u;
+      if (l4.y >= 3e38f) p0.y = u;
+      if (l4.z >= 3e38f) p1.x = u;
+      if (l4.w >= 3e38f) p1.y = u;
     }
     float2 s0 = mul2(p0, sub2(make_float2(__uint_as_float(dr[c4 * 4]), __uint_as_float(dr[c4 * 4 + 1])), make_float2(d4.x, d4.y)));
     float2 s1 = mul2(p1, sub2(make_float2(__uint_as_float(dr[c4 * 4 + 2]), __uint_as_float(dr[c4 * 4 + 3])), make_float2(d4.z, d4.w)));
@@ -137,7 +160,7 @@ template <typename T, typename TB, bool DQS>      // DQS: dQ streamed block by b
 __global__ void __launch_bounds__(kThreads, 1)
 evo_bwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mk,
                   const __grid_constant__ CUtensorMap mv, const __grid_constant__ CUtensorMap mg,
-                  const __grid_constant__ CUtensorMap mbt, const BwdWsP p) {
+                  const __grid_constant__ CUtensorMap mbt, const BwdWsP p MF_TRACE_PARAM) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* sDS = smem;                          // [2 blocks][2 atoms]: dS^T tiles for the dQ product
@@ -145,8 +168,7 @@ evo_bwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
   uint8_t* sKV = sBT + 3 * kAtomB;              // [2 stages][K, V]
   uint8_t* sQD = sKV + 4 * kTileB;              // [3 stages][Q, dO]
   uint8_t* sI = sQD + 6 * kTileB;               // alpha * I, two terms
-  float* lse2 = reinterpret_cast<float*>(sI + 2048);
-  float* dlt = lse2 + 2 * p.lpad;               // lse2, dlt: two buffers each (items alternate)
+  float* sST = reinterpret_cast<float*>(sI + 2048);     // [2 items][lse2 x lpad | delta x lpad]
 
   __shared__ Bars bar;
   __shared__ uint32_t tmem_base_s;
@@ -158,14 +180,15 @@ evo_bwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bar.kv_full[i], 1); mbar_init(&bar.kv_empty[i], 1);
       mbar_init(&bar.sd_ready[i], 1); mbar_init(&bar.written[i], kComputeWarps / 2);
-      mbar_init(&bar.buf_free[i], 1); mbar_init(&bar.blk_done[i], 1);
+      mbar_init(&bar.buf_free[i], 1);
+      mbar_init(&bar.ds_written[i], kComputeWarps); mbar_init(&bar.dq_done[i], 1);
       mbar_init(&bar.st_full[i], 1); mbar_init(&bar.st_empty[i], kComputeWarps);
       mbar_init(&bar.dq_drained[i], 4);
-      bar.special[i] = 0;
     }
     for (int i = 0; i < 3; ++i) {
       mbar_init(&bar.qd_full[i], 1); mbar_init(&bar.qd_empty[i], 1); mbar_init(&bar.bt_full[i], 1); mbar_init(&bar.bt_empty[i], 1);
     }
+    mbar_init(&bar.kv_done, 1);
     mbar_init(&bar.kv_drained, 8);
     mbar_fence_init();
     prefetch_tmap(&mq); prefetch_tmap(&mk); prefetch_tmap(&mv); prefetch_tmap(&mg); prefetch_tmap(&mbt);
@@ -184,10 +207,7 @@ evo_bwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
   // TMEM: team t's scores S''^T at t*128 + [0,64), dP^T at t*128 + [64,128) (P^T / dS^T are packed over them);
   // dK | dV accumulators (one or two sets); dQ accumulators (one per query tile, or two used in turn when streaming)
   const uint32_t tKV = tm0 + 256, tDQ = tm0 + 256 + (dbuf ? 128 : 64);
-  auto tDK_of = [&](uint32_t kc) { return tKV + (dbuf ? (kc & 1) * 64 : 0); };
-  auto tDV_of = [&](uint32_t kc) { return tDK_of(kc) + 32; };
-  auto qd_stage = [&](uint32_t gg) { return sQD + (gg % 3) * 2 * kTileB; };
-  auto kv_stage = [&](uint32_t kc) { return sKV + (kc & 1) * 2 * kTileB; };
+  const uint32_t kv_set = dbuf ? 64 : 0;         // column distance between the two dK|dV accumulator sets
   // work item = (b, n, h, range of key tiles)
   auto item_range = [&](int item, int& jt0, int& jt1) {
     const int sp = item % p.ksplit;
@@ -196,23 +216,20 @@ evo_bwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
 
   if (warp < kComputeWarps) {
     // ============================================================================ compute warps
-    // Register re-partition: the CTA is launched with 96 registers per thread (640 threads); the helper warpgroup
-    // drops to 32 and the compute warpgroups rise to 112.  The raise can only draw on what the drop releases inside
-    // this CTA, so 512 * 112 + 128 * 32 must not exceed 640 * 96 - otherwise the raise never returns.
-    static_assert(kComputeWarps * 32 * 112 + 128 * 32 <= kThreads * 96, "setmaxnreg budget");
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 112;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kComputeRegs));
     const int team = warp >> 3;                       // takes the half blocks with (half == team)
     const int ch = (warp >> 2) & 1;                   // which 32 of the half block's 64 query columns
     const int w = warp >> 2;                          // 0..3: role in the write-out of accumulators
     const int r = (warp & 3) * 32 + lane;             // TMEM lane = key row inside the tile
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t tST = tm0 + team * 128 + ch * 32 + lane_addr, tDP = tST + 64;
+    MF_TRACE_DECL(tr, team, blockIdx.x == 0 && (warp == 0 || warp == 8) && lane == 0);
 
     // dK (scaled) and dV rows of key `j` from accumulator set `kc`: warps 0-3 write dK, warps 4-7 dV
     auto store_kv = [&](uint32_t kc, int j, int b, int n, int h) {
       tc_fence_after();
       uint32_t o32[32];
-      tmem_ld32((w == 0 ? tDK_of(kc) : tDV_of(kc)) + lane_addr, o32);
+      tmem_ld32(tKV + (kc & 1) * kv_set + (w == 0 ? 0 : 32) + lane_addr, o32);
       tmem_ld_wait();
       tc_fence_before();
       if (j < p.L && !*abort_flag) {
@@ -252,19 +269,20 @@ evo_bwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
 
     uint32_t g = 0;                 // full blocks seen by this CTA (both teams count every block)
     uint32_t kv_cnt = 0;            // (item, j) pairs so far
-    uint32_t tuse = 0;              // half blocks this team has processed
     int item_no = 0;
-    int pend_j = -1; uint32_t pend_kc = 0, pend_g = 0; int pend_b = 0, pend_n = 0, pend_h = 0;   // deferred dK/dV write-out
-    int dqp_it = -1; uint32_t dqp_g = 0; int dqp_b = 0, dqp_n = 0, dqp_h = 0;                    // deferred streamed dQ
+    int pend_j = -1; uint32_t pend_kc = 0; int pend_b = 0, pend_n = 0, pend_h = 0;   // deferred dK/dV write-out
+    int dqp_it = -1; uint32_t dqp_g = 0; int dqp_b = 0, dqp_n = 0, dqp_h = 0;        // deferred streamed dQ
+    int special_next = blockIdx.x < p.n_items ? p.flags[blockIdx.x / p.ksplit] : 0;
     for (int item = blockIdx.x; item < p.n_items; item += gridDim.x, ++item_no) {
       const int bnh = item / p.ksplit;
       int jt0, jt1; item_range(item, jt0, jt1);
       const int h = bnh % p.H, bn = bnh / p.H, n = bn % p.N, b = bn / p.N;
       const int sbuf = item_no & 1;
+      const bool special = special_next != 0;      // a fully masked row: the item takes the careful path
+      if (item + (int)gridDim.x < p.n_items) special_next = p.flags[(item + (int)gridDim.x) / p.ksplit];
       wait_or_flag(&bar.st_full[sbuf], (item_no >> 1) & 1, abort_flag);
-      const bool special = *reinterpret_cast<volatile int*>(&bar.special[sbuf]) != 0;
-      const float* lse2c = lse2 + sbuf * p.lpad;
-      const float* dltc = dlt + sbuf * p.lpad;
+      const float* lse2c = sST + sbuf * 2 * p.lpad;
+      const float* dltc = lse2c + p.lpad;
       float mask2_next = -INFINITY;
       {
         const int j0r = jt0 * kT + r;
@@ -291,21 +309,29 @@ evo_bwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
         for (int it = 0; it < nt; ++it, ++g) {
           const int i0 = it * kT + team * kHalf + ch * 32;
           // ---- S''^T, dP^T of my half block -> registers
-          wait_or_flag(&bar.sd_ready[team], tuse & 1, abort_flag);
+          tr(1);
+          wait_or_flag(&bar.sd_ready[team], g & 1, abort_flag);
           tc_fence_after();
-          uint32_t sr[32], dr[32];
-          tmem_ld32(tST, sr);
-          tmem_ld32(tDP, dr);
-          tmem_ld_wait();
+          tr(2);
           uint32_t pp[16], dd[16];
-          if (special) p_and_ds<T, true>(sr, dr, lse2c + i0, dltc + i0, p.c1, mask2, j_ok, masked_key, p.inv_L, pp, dd);
-          else p_and_ds<T, false>(sr, dr, lse2c + i0, dltc + i0, p.c1, mask2, j_ok, masked_key, p.inv_L, pp, dd);
+#pragma unroll
+          for (int hf = 0; hf < 2; ++hf) {        // 16 query columns at a time keeps the live registers down
+            uint32_t sr[16], dr[16];
+            tmem_ld16(tST + hf * 16, sr);
+            tmem_ld16(tDP + hf * 16, dr);
+            tmem_ld_wait();
+            if (hf == 0) tr(3);
+            if (special) p_and_ds<T, true>(sr, dr, lse2c + i0 + hf * 16, dltc + i0 + hf * 16, p.c1, mask2, j_ok, masked_key, p.inv_L, pp + hf * 8, dd + hf * 8);
+            else p_and_ds<T, false>(sr, dr, lse2c + i0 + hf * 16, dltc + i0 + hf * 16, p.c1, mask2, j_ok, masked_key, p.inv_L, pp + hf * 8, dd + hf * 8);
+          }
+          tr(4);
           // ---- packed P^T / dS^T over the scores just read (A operands of the dV / dK products)
           tmem_st16(tST, pp);
           tmem_st16(tDP, dd);
           // ---- dS^T also to the shared-memory tile of this block (A operand of the dQ product), once the dQ
           // product that read this buffer two blocks ago is complete
-          if (g >= 2) wait_or_flag(&bar.blk_done[g & 1], ((g >> 1) - 1) & 1, abort_flag);
+          if (g >= 2) wait_or_flag(&bar.dq_done[g & 1], ((g >> 1) - 1) & 1, abort_flag);
+          tr(5);
           {
             uint8_t* atom = sDS + (g & 1) * 2 * kAtomB + team * kAtomB;
 #pragma unroll
@@ -316,13 +342,13 @@ evo_bwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
           fence_async_smem();
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(&bar.written[team]);
-          ++tuse;
+          if (lane == 0) { mbar_arrive(&bar.written[team]); mbar_arrive(&bar.ds_written[g & 1]); }
+          tr(6);
           // ---- streamed dQ: the product of the previous block sits in accumulator (g - 1) & 1; the four warps with
           // w == (g - 1) & 3 add it to global memory and hand the accumulator back
           if constexpr (DQS) {
             if (dqp_it >= 0 && w == (int)(dqp_g & 3)) {
-              wait_or_flag(&bar.blk_done[dqp_g & 1], (dqp_g >> 1) & 1, abort_flag);
+              wait_or_flag(&bar.dq_done[dqp_g & 1], (dqp_g >> 1) & 1, abort_flag);
               add_dq(tDQ + (dqp_g & 1) * 32, dqp_it, dqp_b, dqp_n, dqp_h);
               __syncwarp();
               if (lane == 0) mbar_arrive(&bar.dq_drained[dqp_g & 1]);
@@ -331,22 +357,24 @@ evo_bwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
           }
           // ---- dK_j, dV_j of the key tile that finished one block ago (warps 0-7)
           if (pend_j >= 0 && w < 2) {
-            wait_or_flag(&bar.blk_done[pend_g & 1], (pend_g >> 1) & 1, abort_flag);
+            wait_or_flag(&bar.kv_done, pend_kc & 1, abort_flag);
             store_kv(pend_kc, pend_j, pend_b, pend_n, pend_h);
             if (!dbuf) { __syncwarp(); if (lane == 0) mbar_arrive(&bar.kv_drained); }
           }
           pend_j = -1;
-          if (it == nt - 1) { pend_j = j; pend_kc = kv_cnt; pend_g = g; pend_b = b; pend_n = n; pend_h = h; }
+          if (it == nt - 1) { pend_j = j; pend_kc = kv_cnt; pend_b = b; pend_n = n; pend_h = h; }
         }
       }
       // ---- end of the item: the last key tile's dK/dV, the last streamed dQ, or every query tile's dQ
-      const uint32_t gl = g - 1;
-      wait_or_flag(&bar.blk_done[gl & 1], (gl >> 1) & 1, abort_flag);
+      tr(7);
       if (pend_j >= 0 && w < 2) {
+        wait_or_flag(&bar.kv_done, pend_kc & 1, abort_flag);
         store_kv(pend_kc, pend_j, pend_b, pend_n, pend_h);
         if (!dbuf) { __syncwarp(); if (lane == 0) mbar_arrive(&bar.kv_drained); }
       }
       pend_j = -1;
+      const uint32_t gl = g - 1;
+      wait_or_flag(&bar.dq_done[gl & 1], (gl >> 1) & 1, abort_flag);
       if constexpr (DQS) {
         if (dqp_it >= 0 && w == (int)(dqp_g & 3)) {
           add_dq(tDQ + (dqp_g & 1) * 32, dqp_it, dqp_b, dqp_n, dqp_h);
@@ -386,164 +414,187 @@ evo_bwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bar.st_empty[sbuf]);
+      tr(8);
     }
   } else {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 32;");
-    if (warp == kComputeWarps && lane == 0) {
-      // ========================================================================== accumulate-MMA issuer
-      const uint32_t id_kv = idesc_f16(128, 32, p.fmt, 0, 1);     // A (TMEM) K-major, B MN-major
-      const uint32_t id_q = idesc_f16(128, 32, p.fmt, 1, 1);      // A MN-major (M = queries), B MN-major
-      constexpr uint32_t hi_t = desc_hi(1024, kSw128), hi_o = desc_hi(512, kSw64);
-      uint32_t g = 0, kv = 0, hb = 0;
-      int item_no = 0;
-      for (int item = blockIdx.x; item < p.n_items && !*abort_flag; item += gridDim.x, ++item_no) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kHelperRegs));
+    // The helper roles are run by whole warps (one elected lane issues: see mma_ss_el); every exit decision is a warp vote.
+    auto dead = [&] { return __any_sync(0xffffffffu, *abort_flag) != 0; };
+    constexpr uint32_t hi64 = desc_hi(512, kSw64), hi128 = desc_hi(1024, kSw128);
+    constexpr uint32_t kTile16 = kTileB / 16, kAtom16 = kAtomB / 16;      // descriptor address units
+    const uint32_t kv_base = desc_lo(smem_u32(sKV), 16), qd_base = desc_lo(smem_u32(sQD), 16);
+    if (warp == kComputeWarps) {
+      // ========================================================================== dV / dK issuer: per half block
+      //   dV_j += P^T dO_i,  dK_j += dS^T Q_i   (A = packed P^T / dS^T in TMEM, B = the dO / Q rows of the half, MN-major)
+      const uint32_t id_kv = idesc_f16(128, 32, p.fmt, 0, 1);
+      MF_TRACE_DECL(tr, 2, blockIdx.x == 0 && lane == 0);
+      uint32_t g = 0, kv = 0, qslot = 0;
+      for (int item = blockIdx.x; item < p.n_items && !dead(); item += gridDim.x) {
         int jt0, jt1; item_range(item, jt0, jt1);
-        for (int jt = jt0; jt < jt1 && !*abort_flag; ++jt, ++kv) {
+        for (int jt = jt0; jt < jt1 && !dead(); ++jt, ++kv) {
           if (!dbuf && kv > 0) wait_or_flag(&bar.kv_drained, (kv - 1) & 1, abort_flag);
-          const uint32_t kvb = smem_u32(kv_stage(kv));
-          for (int it = 0; it < nt; ++it, ++g) {
-            const uint32_t qdb = smem_u32(qd_stage(g));
-            for (int half = 0; half < 2; ++half, ++hb) {
-              wait_or_flag(&bar.written[half], (hb >> 1) & 1, abort_flag);
+          const uint32_t tdk = tKV + (kv & 1) * kv_set, tdv = tdk + 32;
+          for (int it = 0; it < nt && !dead(); ++it, ++g) {
+            const uint32_t q_lo = qd_base + qslot * 2 * kTile16, do_lo = q_lo + kTile16;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+              tr(20);
+              wait_or_flag(&bar.written[half], g & 1, abort_flag);
               tc_fence_after();
-              if (*abort_flag) break;
+              tr(21);
               const uint32_t tPt = tm0 + half * 128, tDSt = tPt + 64;
-              const uint32_t do_lo = desc_lo(qdb + kTileB, 16) + half * 4 * 64, q_lo = desc_lo(qdb, 16) + half * 4 * 64;
+              const uint32_t b_do = do_lo + half * 256, b_q = q_lo + half * 256;
               const bool first = it == 0 && half == 0;
-#pragma unroll
-              for (int kq = 0; kq < 4; ++kq)      // dV_j += P^T dO_i   (16 queries per step)
-                mma_ts_lh(tDV_of(kv), tPt + (kq >> 1) * 32 + (kq & 1) * 8, do_lo + kq * 64, hi_o, id_kv, !first || kq > 0);
-#pragma unroll
-              for (int kq = 0; kq < 4; ++kq)      // dK_j += dS^T Q_i
-                mma_ts_lh(tDK_of(kv), tDSt + (kq >> 1) * 32 + (kq & 1) * 8, q_lo + kq * 64, hi_o, id_kv, !first || kq > 0);
-              tc_commit(&bar.buf_free[half]);
+              mma_ts_el(tdv, tPt, b_do, hi64, id_kv, !first);
+              mma_ts_el(tdv, tPt + 8, b_do + 64, hi64, id_kv, true);
+              mma_ts_el(tdv, tPt + 32, b_do + 128, hi64, id_kv, true);
+              mma_ts_el(tdv, tPt + 40, b_do + 192, hi64, id_kv, true);
+              mma_ts_el(tdk, tDSt, b_q, hi64, id_kv, !first);
+              mma_ts_el(tdk, tDSt + 8, b_q + 64, hi64, id_kv, true);
+              mma_ts_el(tdk, tDSt + 32, b_q + 128, hi64, id_kv, true);
+              mma_ts_el(tdk, tDSt + 40, b_q + 192, hi64, id_kv, true);
+              tc_commit_el(&bar.buf_free[half]);
+              tr(22);
             }
-            if (*abort_flag) break;
-            // dQ_i += dS K_j   (A = the dS^T tile in shared memory read MN-major: M = queries)
-            if constexpr (DQS) {
-              if (g >= 2) wait_or_flag(&bar.dq_drained[g & 1], ((g >> 1) - 1) & 1, abort_flag);
-            } else if (item_no > 0 && jt == jt0 && it == 0) {
-              // the on-chip dQ accumulators of the previous item must have been read out before they start afresh
-              wait_or_flag(&bar.st_empty[(item_no - 1) & 1], ((item_no - 1) >> 1) & 1, abort_flag);
-            }
-            const uint32_t dst_lo = desc_lo(smem_u32(sDS + (g & 1) * 2 * kAtomB), kAtomB);
-            const uint32_t k_lo = desc_lo(kvb, 16);
-#pragma unroll
-            for (int ks = 0; ks < 8; ++ks)
-              mma_ss_lh(tDQ + (DQS ? (g & 1) : it) * 32, dst_lo + ks * (2048 / 16), hi_t, k_lo + ks * 64, hi_o, id_q,
-                        DQS ? ks > 0 : (jt > jt0 || ks > 0));
-            tc_commit(&bar.blk_done[g & 1]);
-            tc_commit(&bar.qd_empty[g % 3]);
-            if (it == nt - 1) tc_commit(&bar.kv_empty[kv & 1]);
+            tc_commit_el(&bar.qd_empty[qslot]);
+            if (it == nt - 1) tc_commit_el(&bar.kv_done);
+            if (++qslot == 3) qslot = 0;
           }
         }
       }
-    } else if (warp == kComputeWarps + 2 && lane == 0) {
-      // ========================================================================== score-MMA issuer
+    } else if (warp == kComputeWarps + 3) {
+      // ========================================================================== dQ issuer: per block
+      //   dQ_i += dS K_j   (A = the dS^T tile in shared memory read MN-major: M = queries; B = K_j, MN-major)
+      const uint32_t id_q = idesc_f16(128, 32, p.fmt, 1, 1);
+      const uint32_t ds_base = desc_lo(smem_u32(sDS), kAtomB);
+      uint32_t g = 0, kv = 0;
+      int item_no = 0;
+      for (int item = blockIdx.x; item < p.n_items && !dead(); item += gridDim.x, ++item_no) {
+        int jt0, jt1; item_range(item, jt0, jt1);
+        // the on-chip dQ accumulators of the previous item must have been read out before they start afresh
+        if (!DQS && item_no > 0) wait_or_flag(&bar.st_empty[(item_no - 1) & 1], ((item_no - 1) >> 1) & 1, abort_flag);
+        for (int jt = jt0; jt < jt1 && !dead(); ++jt, ++kv) {
+          const uint32_t k_lo = kv_base + (kv & 1) * 2 * kTile16;
+          for (int it = 0; it < nt && !dead(); ++it, ++g) {
+            wait_or_flag(&bar.ds_written[g & 1], (g >> 1) & 1, abort_flag);
+            if constexpr (DQS) { if (g >= 2) wait_or_flag(&bar.dq_drained[g & 1], ((g >> 1) - 1) & 1, abort_flag); }
+            tc_fence_after();
+            const uint32_t a_lo = ds_base + (g & 1) * 2 * kAtom16;
+            const uint32_t tacc = tDQ + (DQS ? (g & 1) : it) * 32;
+            mma_ss_el(tacc, a_lo, hi128, k_lo, hi64, id_q, DQS ? false : jt > jt0);
+#pragma unroll
+            for (int ks = 1; ks < 8; ++ks) mma_ss_el(tacc, a_lo + ks * (2048 / 16), hi128, k_lo + ks * 64, hi64, id_q, true);
+            tc_commit_el(&bar.dq_done[g & 1]);
+            if (it == nt - 1) tc_commit_el(&bar.kv_empty[kv & 1]);
+          }
+        }
+      }
+    } else if (warp == kComputeWarps + 2) {
+      // ========================================================================== score issuer: per half block
+      //   S''^T = K_j Q_i^T + alpha * bias^T,  dP^T = V_j dO_i^T
       const uint32_t id_s = idesc_f16(128, kHalf, p.fmt, 0, 0);
       const uint32_t id_b = idesc_f16(128, 16, p.bfmt, 0, 0);
-      constexpr uint32_t hi64 = desc_hi(512, kSw64), hi128 = desc_hi(1024, kSw128);
-      uint32_t g = 0, kv = 0, hb = 0, bslot = 0, buse = 0;
-      for (int item = blockIdx.x; item < p.n_items && !*abort_flag; item += gridDim.x) {
+      const uint32_t bt_base = desc_lo(smem_u32(sBT), 16);
+      const uint32_t i_lo0 = desc_lo(smem_u32(sI), 16), i_lo1 = i_lo0 + 1024 / 16;
+      const bool two_terms = p.n_alpha > 1;
+      MF_TRACE_DECL(tr, 3, blockIdx.x == 0 && lane == 0);
+      uint32_t g = 0, kv = 0, bslot = 0, buse = 0, qslot = 0, quse = 0;
+      for (int item = blockIdx.x; item < p.n_items && !dead(); item += gridDim.x) {
         int jt0, jt1; item_range(item, jt0, jt1);
-        for (int jt = jt0; jt < jt1 && !*abort_flag; ++jt, ++kv) {
+        for (int jt = jt0; jt < jt1 && !dead(); ++jt, ++kv) {
           wait_or_flag(&bar.kv_full[kv & 1], (kv >> 1) & 1, abort_flag);
-          const uint32_t kvb = smem_u32(kv_stage(kv));
-          const uint32_t k_lo = desc_lo(kvb, 16), v_lo = desc_lo(kvb + kTileB, 16);
-          for (int it = 0; it < nt; ++it, ++g) {
-            wait_or_flag(&bar.qd_full[g % 3], (g / 3) & 1, abort_flag);
-            const uint32_t qdb = smem_u32(qd_stage(g));
-            for (int half = 0; half < 2; ++half, ++hb) {
+          const uint32_t k_lo = kv_base + (kv & 1) * 2 * kTile16, v_lo = k_lo + kTile16;
+          for (int it = 0; it < nt && !dead(); ++it, ++g) {
+            wait_or_flag(&bar.qd_full[qslot], quse & 1, abort_flag);
+            const uint32_t q_blk = qd_base + qslot * 2 * kTile16;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+              tr(30);
               wait_or_flag(&bar.bt_full[bslot], buse & 1, abort_flag);
-              if (hb >= 2) wait_or_flag(&bar.buf_free[half], ((hb >> 1) - 1) & 1, abort_flag);
+              if (g >= 1) wait_or_flag(&bar.buf_free[half], (g - 1) & 1, abort_flag);
               tc_fence_after();
-              if (*abort_flag) break;
-              const uint32_t tST = tm0 + half * 128, tDP = tST + 64;
-              const uint32_t q_lo = desc_lo(qdb, 16) + half * (kHalf * 64 / 16), g_lo = desc_lo(qdb + kTileB, 16) + half * (kHalf * 64 / 16);
+              tr(31);
+              const uint32_t tS = tm0 + half * 128, tD = tS + 64;
+              const uint32_t q_lo = q_blk + half * 256, g_lo = q_lo + kTile16;
+              mma_ss_el(tS, k_lo, hi64, q_lo, hi64, id_s, false);
+              mma_ss_el(tS, k_lo + 2, hi64, q_lo + 2, hi64, id_s, true);
+              const uint32_t a_lo = bt_base + bslot * kAtom16;
 #pragma unroll
-              for (int ks = 0; ks < 2; ++ks) mma_ss_lh(tST, k_lo + ks * 2, hi64, q_lo + ks * 2, hi64, id_s, ks > 0);
-              const uint32_t a_lo = desc_lo(smem_u32(sBT + bslot * kAtomB), 16);
-              for (int term = 0; term < p.n_alpha; ++term) {
-                const uint32_t i_lo = desc_lo(smem_u32(sI + term * 1024), 16);
+              for (int c = 0; c < 4; ++c) mma_ss_el(tS + c * 16, a_lo + c * 2, hi128, i_lo0, hi64, id_b, true);
+              if (two_terms) {
 #pragma unroll
-                for (int c = 0; c < 4; ++c) mma_ss_lh(tST + c * 16, a_lo + c * 2, hi128, i_lo, hi64, id_b, true);
+                for (int c = 0; c < 4; ++c) mma_ss_el(tS + c * 16, a_lo + c * 2, hi128, i_lo1, hi64, id_b, true);
               }
-#pragma unroll
-              for (int ks = 0; ks < 2; ++ks) mma_ss_lh(tDP, v_lo + ks * 2, hi64, g_lo + ks * 2, hi64, id_s, ks > 0);
-              tc_commit(&bar.sd_ready[half]);
-              tc_commit(&bar.bt_empty[bslot]);
+              mma_ss_el(tD, v_lo, hi64, g_lo, hi64, id_s, false);
+              mma_ss_el(tD, v_lo + 2, hi64, g_lo + 2, hi64, id_s, true);
+              tc_commit_el(&bar.sd_ready[half]);
+              tc_commit_el(&bar.bt_empty[bslot]);
               if (++bslot == 3) { bslot = 0; ++buse; }
+              tr(32);
             }
-            if (*abort_flag) break;
+            if (++qslot == 3) { qslot = 0; ++quse; }
           }
         }
       }
-    } else if (warp == kComputeWarps + 1 && lane == 0) {
+    } else if (warp == kComputeWarps + 1) {
       // ========================================================================== TMA producer, in order of need
-      uint32_t g = 0, kv = 0, bslot = 0, buse = 0, nbt = 0;
-      for (int item = blockIdx.x; item < p.n_items && !*abort_flag; item += gridDim.x) {
+      uint32_t g = 0, kv = 0, bslot = 0, buse = 0, nbt = 0, qslot = 0, quse = 0;
+      int item_no = 0;
+      for (int item = blockIdx.x; item < p.n_items && !dead(); item += gridDim.x, ++item_no) {
         const int bnh = item / p.ksplit;
         int jt0, jt1; item_range(item, jt0, jt1);
         const int h = bnh % p.H, bn = bnh / p.H, n = bn % p.N, b = bn / p.N;
-        for (int jt = jt0; jt < jt1 && !*abort_flag; ++jt, ++kv) {
+        {
+          // the item's statistics: lse2 | delta, 2 * lpad floats
+          const int sb = item_no & 1;
+          if (item_no >= 2) wait_or_flag(&bar.st_empty[sb], ((item_no >> 1) - 1) & 1, abort_flag);
+          if (dead()) break;
+          const uint32_t bytes = 2u * p.lpad * sizeof(float);
+          if (elect_one()) {
+            mbar_expect_tx(&bar.st_full[sb], bytes);
+            bulk_load_1d(sST + sb * 2 * p.lpad, p.stats + (int64_t)bnh * 2 * p.lpad, bytes, &bar.st_full[sb]);
+          }
+        }
+        for (int jt = jt0; jt < jt1 && !dead(); ++jt, ++kv) {
           if (kv >= 2) wait_or_flag(&bar.kv_empty[kv & 1], ((kv >> 1) - 1) & 1, abort_flag);
-          if (*abort_flag) break;
-          {
+          if (dead()) break;
+          if (elect_one()) {
             uint64_t* fb = &bar.kv_full[kv & 1];
+            uint8_t* st = sKV + (kv & 1) * 2 * kTileB;
             mbar_expect_tx(fb, 2 * kTileB);
-            tma_load_5d(kv_stage(kv), &mk, fb, 0, h, jt * kT, n, b);
-            tma_load_5d(kv_stage(kv) + kTileB, &mv, fb, 0, h, jt * kT, n, b);
+            tma_load_5d(st, &mk, fb, 0, h, jt * kT, n, b);
+            tma_load_5d(st + kTileB, &mv, fb, 0, h, jt * kT, n, b);
           }
           for (int it = 0; it < nt; ++it, ++g) {
-            if (g >= 3) wait_or_flag(&bar.qd_empty[g % 3], ((g / 3) - 1) & 1, abort_flag);
-            if (*abort_flag) break;
-            {
-              uint64_t* fb = &bar.qd_full[g % 3];
+            if (quse >= 1) wait_or_flag(&bar.qd_empty[qslot], (quse - 1) & 1, abort_flag);
+            if (dead()) break;
+            if (elect_one()) {
+              uint64_t* fb = &bar.qd_full[qslot];
+              uint8_t* st = sQD + qslot * 2 * kTileB;
               mbar_expect_tx(fb, 2 * kTileB);
-              tma_load_5d(qd_stage(g), &mq, fb, 0, h, it * kT, n, b);
-              tma_load_5d(qd_stage(g) + kTileB, &mg, fb, 0, h, it * kT, n, b);
+              tma_load_5d(st, &mq, fb, 0, h, it * kT, n, b);
+              tma_load_5d(st + kTileB, &mg, fb, 0, h, it * kT, n, b);
             }
+            if (++qslot == 3) { qslot = 0; ++quse; }
             for (int half = 0; half < 2; ++half) {
               if (buse >= 1) wait_or_flag(&bar.bt_empty[bslot], (buse - 1) & 1, abort_flag);
-              if (*abort_flag) break;
-              mbar_expect_tx(&bar.bt_full[bslot], kAtomB);
-              tma_load_4d(sBT + bslot * kAtomB, &mbt, &bar.bt_full[bslot], it * kT + half * kHalf, jt * kT, h, b * p.bias_b_mul);
+              if (dead()) break;
+              if (elect_one()) {
+                mbar_expect_tx(&bar.bt_full[bslot], kAtomB);
+                tma_load_4d(sBT + bslot * kAtomB, &mbt, &bar.bt_full[bslot], it * kT + half * kHalf, jt * kT, h, b * p.bias_b_mul);
+              }
               ++nbt;
               if (++bslot == 3) { bslot = 0; ++buse; }
             }
           }
         }
       }
-      if (*abort_flag) {
+      if (dead() && lane == 0) {
         // the copies already requested must land before the CTA's shared memory is given back (bounded)
         for (uint32_t back = 0; back < 2 && back < kv; ++back) { const uint32_t c = kv - 1 - back; mbar_wait(&bar.kv_full[c & 1], (c >> 1) & 1); }
         for (uint32_t back = 0; back < 3 && back < g; ++back) { const uint32_t c = g - 1 - back; mbar_wait(&bar.qd_full[c % 3], (c / 3) & 1); }
         for (uint32_t back = 0; back < 3 && back < nbt; ++back) { const uint32_t c = nbt - 1 - back; mbar_wait(&bar.bt_full[c % 3], (c / 3) & 1); }
-      }
-    } else if (warp == kComputeWarps + 3) {
-      // ========================================================================== statistics loader (whole warp):
-      // lse in base 2 and delta of the item's query rows into the buffer of the item's parity; queries beyond L get
-      // lse = +inf so that P = 0.  A fully masked row (lse = -FLT_MAX) sends the item down the careful path.
-      int item_no = 0;
-      for (int item = blockIdx.x; item < p.n_items && !*abort_flag; item += gridDim.x, ++item_no) {
-        const int buf = item_no & 1;
-        if (item_no >= 2) wait_or_flag(&bar.st_empty[buf], ((item_no >> 1) - 1) & 1, abort_flag);
-        const int64_t row0 = (int64_t)(item / p.ksplit) * p.L;       // ((b*N+n)*H + h) * L
-        int sp = 0;
-        for (int i = lane; i < p.lpad; i += 32) {
-          float l2 = INFINITY, dl = 0.f;
-          if (i < p.L) {
-            const float lv = p.lse[row0 + i];
-            if (lv <= -3e38f) sp = 1;
-            l2 = lv * kLog2e; dl = p.delta[row0 + i];
-          }
-          lse2[buf * p.lpad + i] = l2; dlt[buf * p.lpad + i] = dl;
-        }
-        sp = __any_sync(0xffffffffu, sp);
-        if (lane == 0) { bar.special[buf] = sp; }
-        __syncwarp();
-        __threadfence_block();
-        if (lane == 0) mbar_arrive(&bar.st_full[buf]);
+        for (int back = 0; back < 2 && back < item_no; ++back) { const int c = item_no - 1 - back; mbar_wait(&bar.st_full[c & 1], (c >> 1) & 1); }
       }
     }
   }
@@ -562,14 +613,14 @@ struct DbP {
   int n_alpha; float alpha[2];
   int bias_b_mul;
   const void* mask; int64_t ms[3]; int mask_dtype;
-  const float* lse; const float* delta;
+  const float* stats;     // per-query statistics (evo_stats_ws_kernel)
   float* part;            // fp32 [nsplit][B][H][L][L] partial sums
   int* status;
 };
 
 struct DbBars {
-  uint64_t op_full[3], op_empty[3];          // Q, dO, K, V of one row n
-  uint64_t st_full[3], st_empty[3];          // lse2 / delta of the row's 128 queries
+  uint64_t op_full[3], op_empty[3];          // Q, dO, K, V and the statistics of one row n
+  uint64_t st_empty[3];                      // the compute warps are done with the stage's statistics
   uint64_t bt_full, bt_free;                 // the unit's two bias^T atoms
   uint64_t sd_ready[2], loaded[2];
 };
@@ -578,7 +629,7 @@ template <typename T, typename TB>
 __global__ void __launch_bounds__(kThreads, 1)
 evo_dbias_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mk,
                     const __grid_constant__ CUtensorMap mv, const __grid_constant__ CUtensorMap mg,
-                    const __grid_constant__ CUtensorMap mbt, const DbP p) {
+                    const __grid_constant__ CUtensorMap mbt, const DbP p MF_TRACE_PARAM) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* sBT = smem;                          // two bias^T atoms (queries 0-63 | 64-127 of the tile)
@@ -594,11 +645,11 @@ evo_dbias_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constan
   if (tid == 0) {
     abort_s = 0;
     for (int i = 0; i < 3; ++i) {
-      mbar_init(&bar.op_full[i], 1); mbar_init(&bar.op_empty[i], 1);
-      mbar_init(&bar.st_full[i], 1); mbar_init(&bar.st_empty[i], kComputeWarps);
+      mbar_init(&bar.op_full[i], 1); mbar_init(&bar.op_empty[i], 2);      // two issuers commit
+      mbar_init(&bar.st_empty[i], kComputeWarps);
     }
     mbar_init(&bar.bt_full, 1); mbar_init(&bar.bt_free, 1);
-    for (int i = 0; i < 2; ++i) { mbar_init(&bar.sd_ready[i], 1); mbar_init(&bar.loaded[i], kComputeWarps); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&bar.sd_ready[i], 2); mbar_init(&bar.loaded[i], kComputeWarps); }
     mbar_fence_init();
     prefetch_tmap(&mq); prefetch_tmap(&mk); prefetch_tmap(&mv); prefetch_tmap(&mg); prefetch_tmap(&mbt);
   }
@@ -623,52 +674,69 @@ evo_dbias_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constan
   };
 
   if (warp < kComputeWarps) {
-    static_assert(kComputeWarps * 32 * 112 + 128 * 32 <= kThreads * 96, "setmaxnreg budget");
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 112;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kComputeRegs));
     const int w = warp >> 2;                          // query quarter (32 columns) handled by this thread
     const int r = (warp & 3) * 32 + lane;             // TMEM lane = key row inside the tile
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
-    uint32_t g = 0;                                   // rows processed by this CTA (buffer g & 1, stage g % 3)
+    uint32_t g = 0, stage = 0, suse = 0;              // rows processed by this CTA (TMEM buffer g & 1, stage g % 3)
     const float2 c1c1 = make_float2(p.c1, p.c1);
+    MF_TRACE_DECL(tr, 0, blockIdx.x == 0 && tid == 0);
     for (int u = blockIdx.x; u < p.n_units; u += gridDim.x) {
       const Unit x = unit_of(u);
       const int j = x.jt * kT + r;
       float2 acc[16];
 #pragma unroll
       for (int c = 0; c < 16; ++c) acc[c] = make_float2(0.f, 0.f);
-      for (int n = x.n0; n < x.n1; ++n, ++g) {
-        float mask2 = -INFINITY;
+      const int64_t mrow = x.b * p.ms[0] + (int64_t)j * p.ms[2];
+      auto load_mask = [&](int n) {
+        float m2 = -INFINITY;
         if (j < p.L) {
-          const int64_t mi = x.b * p.ms[0] + n * p.ms[1] + (int64_t)j * p.ms[2];
-          mask2 = p.mask_dtype == MF_U8 ? (static_cast<const uint8_t*>(p.mask)[mi] ? 0.f : -FLT_MAX)
-                                        : load_rt(p.mask, mi, p.mask_dtype) * kLog2e;
+          const int64_t mi = mrow + n * p.ms[1];
+          m2 = p.mask_dtype == MF_U8 ? (static_cast<const uint8_t*>(p.mask)[mi] ? 0.f : -FLT_MAX)
+                                     : load_rt(p.mask, mi, p.mask_dtype) * kLog2e;
         }
+        return m2;
+      };
+      float mask_next = load_mask(x.n0);
+      for (int n = x.n0; n < x.n1; ++n, ++g) {
+        const float mask2 = mask_next;                 // fetched one row ahead
+        if (n + 1 < x.n1) mask_next = load_mask(n + 1);
         const uint32_t tST = tm0 + (g & 1) * 256 + w * 32 + lane_addr, tDP = tST + 128;
-        wait_or_flag(&bar.sd_ready[g & 1], (g >> 1) & 1, abort_flag);
+        tr(1);
+        wait_or_flag(&bar.sd_ready[g & 1], (g >> 1) & 1, abort_flag);     // implies the stage's statistics have landed
         tc_fence_after();
-        uint32_t sr[32], dr[32];
-        tmem_ld32(tST, sr);
-        tmem_ld32(tDP, dr);
-        tmem_ld_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bar.loaded[g & 1]);
-        wait_or_flag(&bar.st_full[g % 3], (g / 3) & 1, abort_flag);
-        const float* l2 = sST + (g % 3) * 256 + w * 32;
+        tr(2);
+        wait_or_flag(&bar.op_full[stage], suse & 1, abort_flag);      // complete long ago: the bulk-copied statistics become visible to this thread
+        const float* l2 = sST + stage * 256 + w * 32;
         const float* dl = l2 + 128;
         const float2 mm = make_float2(mask2, mask2);
 #pragma unroll
-        for (int c4 = 0; c4 < 8; ++c4) {
-          const float4 l4 = *reinterpret_cast<const float4*>(l2 + c4 * 4);
-          const float4 d4 = *reinterpret_cast<const float4*>(dl + c4 * 4);
-          const float2 x0 = fma2(make_float2(__uint_as_float(sr[c4 * 4]), __uint_as_float(sr[c4 * 4 + 1])), c1c1, sub2(mm, make_float2(l4.x, l4.y)));
-          const float2 x1 = fma2(make_float2(__uint_as_float(sr[c4 * 4 + 2]), __uint_as_float(sr[c4 * 4 + 3])), c1c1, sub2(mm, make_float2(l4.z, l4.w)));
-          const float2 p0 = make_float2(ex2f(x0.x), ex2f(x0.y)), p1 = make_float2(ex2f(x1.x), ex2f(x1.y));
-          acc[c4 * 2] = fma2(p0, sub2(make_float2(__uint_as_float(dr[c4 * 4]), __uint_as_float(dr[c4 * 4 + 1])), make_float2(d4.x, d4.y)), acc[c4 * 2]);
-          acc[c4 * 2 + 1] = fma2(p1, sub2(make_float2(__uint_as_float(dr[c4 * 4 + 2]), __uint_as_float(dr[c4 * 4 + 3])), make_float2(d4.z, d4.w)), acc[c4 * 2 + 1]);
+        for (int hf = 0; hf < 2; ++hf) {          // 16 query columns at a time keeps the live registers down
+          uint32_t sr[16], dr[16];
+          tmem_ld16(tST + hf * 16, sr);
+          tmem_ld16(tDP + hf * 16, dr);
+          tmem_ld_wait();
+          if (hf == 1) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bar.loaded[g & 1]);
+            tr(3);
+          }
+#pragma unroll
+          for (int c4 = 0; c4 < 4; ++c4) {
+            const float4 l4 = *reinterpret_cast<const float4*>(l2 + hf * 16 + c4 * 4);
+            const float4 d4 = *reinterpret_cast<const float4*>(dl + hf * 16 + c4 * 4);
+            const float2 x0 = fma2(make_float2(__uint_as_float(sr[c4 * 4]), __uint_as_float(sr[c4 * 4 + 1])), c1c1, sub2(mm, make_float2(l4.x, l4.y)));
+            const float2 x1 = fma2(make_float2(__uint_as_float(sr[c4 * 4 + 2]), __uint_as_float(sr[c4 * 4 + 3])), c1c1, sub2(mm, make_float2(l4.z, l4.w)));
+            const float2 p0 = make_float2(ex2f(x0.x), ex2f(x0.y)), p1 = make_float2(ex2f(x1.x), ex2f(x1.y));
+            acc[hf * 8 + c4 * 2] = fma2(p0, sub2(make_float2(__uint_as_float(dr[c4 * 4]), __uint_as_float(dr[c4 * 4 + 1])), make_float2(d4.x, d4.y)), acc[hf * 8 + c4 * 2]);
+            acc[hf * 8 + c4 * 2 + 1] = fma2(p1, sub2(make_float2(__uint_as_float(dr[c4 * 4 + 2]), __uint_as_float(dr[c4 * 4 + 3])), make_float2(d4.z, d4.w)), acc[hf * 8 + c4 * 2 + 1]);
+          }
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(&bar.st_empty[g % 3]);
+        if (lane == 0) mbar_arrive(&bar.st_empty[stage]);
+        if (++stage == 3) { stage = 0; ++suse; }
+        tr(4);
       }
       // the unit's partial sum: part[sp][b][h][i][j], lanes = consecutive keys
       if (j < p.L && !*abort_flag) {
@@ -683,91 +751,102 @@ evo_dbias_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constan
       }
     }
   } else {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 32;");
-    if (warp == kComputeWarps && lane == 0) {
-      // ========================================================================== MMA issuer
-      const uint32_t id_s = idesc_f16(128, 128, p.fmt, 0, 0);
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kHelperRegs));
+    // The helper roles are run by whole warps (one elected lane issues: see mma_ss_el); every exit decision is a warp vote.
+    auto dead = [&] { return __any_sync(0xffffffffu, *abort_flag) != 0; };
+    constexpr uint32_t hi64 = desc_hi(512, kSw64), hi128 = desc_hi(1024, kSw128);
+    constexpr uint32_t kTile16 = kTileB / 16, kAtom16 = kAtomB / 16;
+    const uint32_t op_base = desc_lo(smem_u32(sOP), 16);
+    const uint32_t id_s = idesc_f16(128, 128, p.fmt, 0, 0);
+    if (warp == kComputeWarps) {
+      // ========================================================================== score issuer: S''^T = K Q^T + alpha * bias^T
       const uint32_t id_b = idesc_f16(128, 16, p.bfmt, 0, 0);
-      constexpr uint32_t hi64 = desc_hi(512, kSw64), hi128 = desc_hi(1024, kSw128);
-      uint32_t g = 0, un = 0;
-      for (int u = blockIdx.x; u < p.n_units && !*abort_flag; u += gridDim.x, ++un) {
+      const uint32_t bt_lo = desc_lo(smem_u32(sBT), 16);
+      const uint32_t i_lo0 = desc_lo(smem_u32(sI), 16), i_lo1 = i_lo0 + 1024 / 16;
+      const bool two_terms = p.n_alpha > 1;
+      MF_TRACE_DECL(tr, 2, blockIdx.x == 0 && lane == 0);
+      uint32_t g = 0, un = 0, stage = 0, suse = 0;
+      for (int u = blockIdx.x; u < p.n_units && !dead(); u += gridDim.x, ++un) {
         const Unit x = unit_of(u);
         wait_or_flag(&bar.bt_full, un & 1, abort_flag);
-        for (int n = x.n0; n < x.n1 && !*abort_flag; ++n, ++g) {
-          wait_or_flag(&bar.op_full[g % 3], (g / 3) & 1, abort_flag);
+        for (int n = x.n0; n < x.n1 && !dead(); ++n, ++g) {
+          tr(20);
+          wait_or_flag(&bar.op_full[stage], suse & 1, abort_flag);
           if (g >= 2) wait_or_flag(&bar.loaded[g & 1], ((g >> 1) - 1) & 1, abort_flag);
           tc_fence_after();
-          if (*abort_flag) break;
-          const uint32_t ob = smem_u32(sOP + (g % 3) * 4 * kTileB);
-          const uint32_t q_lo = desc_lo(ob, 16), g_lo = desc_lo(ob + kTileB, 16), k_lo = desc_lo(ob + 2 * kTileB, 16), v_lo = desc_lo(ob + 3 * kTileB, 16);
-          const uint32_t tST = tm0 + (g & 1) * 256, tDP = tST + 128;
+          tr(21);
+          const uint32_t q_lo = op_base + stage * 4 * kTile16, k_lo = q_lo + 2 * kTile16;
+          const uint32_t tST = tm0 + (g & 1) * 256;
+          mma_ss_el(tST, k_lo, hi64, q_lo, hi64, id_s, false);
+          mma_ss_el(tST, k_lo + 2, hi64, q_lo + 2, hi64, id_s, true);
 #pragma unroll
-          for (int ks = 0; ks < 2; ++ks) mma_ss_lh(tST, k_lo + ks * 2, hi64, q_lo + ks * 2, hi64, id_s, ks > 0);
-          for (int term = 0; term < p.n_alpha; ++term) {
-            const uint32_t i_lo = desc_lo(smem_u32(sI + term * 1024), 16);
+          for (int c = 0; c < 8; ++c) mma_ss_el(tST + c * 16, bt_lo + (c >> 2) * kAtom16 + (c & 3) * 2, hi128, i_lo0, hi64, id_b, true);
+          if (two_terms) {
 #pragma unroll
-            for (int c = 0; c < 8; ++c)
-              mma_ss_lh(tST + c * 16, desc_lo(smem_u32(sBT + (c >> 2) * kAtomB), 16) + (c & 3) * 2, hi128, i_lo, hi64, id_b, true);
+            for (int c = 0; c < 8; ++c) mma_ss_el(tST + c * 16, bt_lo + (c >> 2) * kAtom16 + (c & 3) * 2, hi128, i_lo1, hi64, id_b, true);
           }
-#pragma unroll
-          for (int ks = 0; ks < 2; ++ks) mma_ss_lh(tDP, v_lo + ks * 2, hi64, g_lo + ks * 2, hi64, id_s, ks > 0);
-          tc_commit(&bar.sd_ready[g & 1]);
-          tc_commit(&bar.op_empty[g % 3]);
+          tc_commit_el(&bar.sd_ready[g & 1]);
+          tc_commit_el(&bar.op_empty[stage]);
+          if (++stage == 3) { stage = 0; ++suse; }
+          tr(22);
         }
-        tc_commit(&bar.bt_free);       // every product that reads this unit's bias atoms is complete
+        tc_commit_el(&bar.bt_free);       // every product that reads this unit's bias atoms is complete
       }
-    } else if (warp == kComputeWarps + 1 && lane == 0) {
+    } else if (warp == kComputeWarps + 2) {
+      // ========================================================================== dP issuer: dP^T = V dO^T
+      uint32_t g = 0, stage = 0, suse = 0;
+      for (int u = blockIdx.x; u < p.n_units && !dead(); u += gridDim.x) {
+        const Unit x = unit_of(u);
+        for (int n = x.n0; n < x.n1 && !dead(); ++n, ++g) {
+          wait_or_flag(&bar.op_full[stage], suse & 1, abort_flag);
+          if (g >= 2) wait_or_flag(&bar.loaded[g & 1], ((g >> 1) - 1) & 1, abort_flag);
+          tc_fence_after();
+          const uint32_t g_lo = op_base + stage * 4 * kTile16 + kTile16, v_lo = g_lo + 2 * kTile16;
+          const uint32_t tDP = tm0 + (g & 1) * 256 + 128;
+          mma_ss_el(tDP, v_lo, hi64, g_lo, hi64, id_s, false);
+          mma_ss_el(tDP, v_lo + 2, hi64, g_lo + 2, hi64, id_s, true);
+          tc_commit_el(&bar.sd_ready[g & 1]);
+          tc_commit_el(&bar.op_empty[stage]);
+          if (++stage == 3) { stage = 0; ++suse; }
+        }
+      }
+    } else if (warp == kComputeWarps + 1) {
       // ========================================================================== TMA producer
-      uint32_t g = 0, un = 0;
-      for (int u = blockIdx.x; u < p.n_units && !*abort_flag; u += gridDim.x, ++un) {
+      uint32_t g = 0, un = 0, stage = 0, suse = 0;
+      for (int u = blockIdx.x; u < p.n_units && !dead(); u += gridDim.x, ++un) {
         const Unit x = unit_of(u);
         if (un >= 1) wait_or_flag(&bar.bt_free, (un - 1) & 1, abort_flag);
-        if (*abort_flag) break;
-        mbar_expect_tx(&bar.bt_full, 2 * kAtomB);
-        tma_load_4d(sBT, &mbt, &bar.bt_full, x.it * kT, x.jt * kT, x.h, x.b * p.bias_b_mul);
-        tma_load_4d(sBT + kAtomB, &mbt, &bar.bt_full, x.it * kT + kHalf, x.jt * kT, x.h, x.b * p.bias_b_mul);
+        if (dead()) break;
+        if (elect_one()) {
+          mbar_expect_tx(&bar.bt_full, 2 * kAtomB);
+          tma_load_4d(sBT, &mbt, &bar.bt_full, x.it * kT, x.jt * kT, x.h, x.b * p.bias_b_mul);
+          tma_load_4d(sBT + kAtomB, &mbt, &bar.bt_full, x.it * kT + kHalf, x.jt * kT, x.h, x.b * p.bias_b_mul);
+        }
         for (int n = x.n0; n < x.n1; ++n, ++g) {
-          if (g >= 3) wait_or_flag(&bar.op_empty[g % 3], ((g / 3) - 1) & 1, abort_flag);
-          if (*abort_flag) break;
-          uint64_t* fb = &bar.op_full[g % 3];
-          uint8_t* st = sOP + (g % 3) * 4 * kTileB;
-          mbar_expect_tx(fb, 4 * kTileB);
-          tma_load_5d(st, &mq, fb, 0, x.h, x.it * kT, n, x.b);
-          tma_load_5d(st + kTileB, &mg, fb, 0, x.h, x.it * kT, n, x.b);
-          tma_load_5d(st + 2 * kTileB, &mk, fb, 0, x.h, x.jt * kT, n, x.b);
-          tma_load_5d(st + 3 * kTileB, &mv, fb, 0, x.h, x.jt * kT, n, x.b);
+          if (suse >= 1) {
+            wait_or_flag(&bar.op_empty[stage], (suse - 1) & 1, abort_flag);
+            wait_or_flag(&bar.st_empty[stage], (suse - 1) & 1, abort_flag);
+          }
+          if (dead()) break;
+          if (elect_one()) {
+            uint64_t* fb = &bar.op_full[stage];
+            uint8_t* st = sOP + stage * 4 * kTileB;
+            mbar_expect_tx(fb, 4 * kTileB + 1024);
+            tma_load_5d(st, &mq, fb, 0, x.h, x.it * kT, n, x.b);
+            tma_load_5d(st + kTileB, &mg, fb, 0, x.h, x.it * kT, n, x.b);
+            tma_load_5d(st + 2 * kTileB, &mk, fb, 0, x.h, x.jt * kT, n, x.b);
+            tma_load_5d(st + 3 * kTileB, &mv, fb, 0, x.h, x.jt * kT, n, x.b);
+            // lse2 | delta of the tile's 128 queries
+            const float* src = p.stats + ((((int64_t)x.b * p.N + n) * p.H + x.h) * 2) * p.lpad + x.it * kT;
+            bulk_load_1d(sST + stage * 256, src, 512, fb);
+            bulk_load_1d(sST + stage * 256 + 128, src + p.lpad, 512, fb);
+          }
+          if (++stage == 3) { stage = 0; ++suse; }
         }
       }
-      if (*abort_flag) {
+      if (dead() && lane == 0) {
         for (uint32_t back = 0; back < 3 && back < g; ++back) { const uint32_t c = g - 1 - back; mbar_wait(&bar.op_full[c % 3], (c / 3) & 1); }
         if (un > 0) mbar_wait(&bar.bt_full, (un - 1) & 1);
-      }
-    } else if (warp == kComputeWarps + 3) {
-      // ========================================================================== statistics loader (whole warp):
-      // lse in base 2 and delta of the 128 queries of the unit's tile, row by row.  Queries beyond L and fully
-      // masked rows (lse = -FLT_MAX: no gradient reaches the bias through them) get lse = +inf, hence P = 0.
-      uint32_t g = 0;
-      for (int u = blockIdx.x; u < p.n_units && !*abort_flag; u += gridDim.x) {
-        const Unit x = unit_of(u);
-        for (int n = x.n0; n < x.n1 && !*abort_flag; ++n, ++g) {
-          if (g >= 3) wait_or_flag(&bar.st_empty[g % 3], ((g / 3) - 1) & 1, abort_flag);
-          const int64_t row0 = (((int64_t)x.b * p.N + n) * p.H + x.h) * p.L;
-          float* dst = sST + (g % 3) * 256;
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const int i = x.it * kT + k * 32 + lane;
-            float l2 = INFINITY, dl = 0.f;
-            if (i < p.L) {
-              const float lv = p.lse[row0 + i];
-              if (lv > -3e38f) l2 = lv * kLog2e;
-              dl = p.delta[row0 + i];
-            }
-            dst[k * 32 + lane] = l2; dst[128 + k * 32 + lane] = dl;
-          }
-          __syncwarp();
-          __threadfence_block();
-          if (lane == 0) mbar_arrive(&bar.st_full[g % 3]);
-        }
       }
     }
   }
@@ -805,7 +884,7 @@ int bwd_ksplit(int64_t bnh, int nt, int sms) {
 struct BwdPlan {
   int nt, lpad, ksplit, dq_stream, dbuf, nsplit;
   bool dq_fp32, part_direct;
-  size_t off_delta, off_part, off_dq, off_biasT, total;
+  size_t off_stats, off_flags, off_part, off_dq, off_biasT, total;
 };
 
 BwdPlan plan_bwd(const mf_evo_bwd_args& a) {
@@ -826,7 +905,8 @@ BwdPlan plan_bwd(const mf_evo_bwd_args& a) {
   pl.nsplit = (int)ns;
   pl.part_direct = pl.nsplit == 1 && a.dbias_dtype == MF_F32;      // a single range writes d_bias itself
   size_t off = 0;
-  pl.off_delta = off; off += align_up(sizeof(float) * (size_t)a.B * a.N * a.H * a.L, 256);
+  pl.off_stats = off; off += align_up(sizeof(float) * (size_t)a.B * a.N * a.H * 2 * pl.lpad, 256);
+  pl.off_flags = off; off += align_up(sizeof(int) * (size_t)a.B * a.N * a.H, 256);
   pl.off_part = off; if (!pl.part_direct) off += align_up(sizeof(float) * (size_t)pl.nsplit * a.B * a.H * a.L * a.L, 256);
   pl.off_dq = off; if (pl.dq_fp32) off += align_up(sizeof(float) * (size_t)a.B * a.N * a.L * a.H * a.D, 256);
   pl.off_biasT = off; off += align_up(2 * (size_t)a.B * a.H * a.L * pl.lpad, 256);
@@ -848,7 +928,8 @@ int launch_bwd_ws(const mf_evo_bwd_args& a, cudaStream_t st) {
   MF_REQUIRE(status, MF_ERR_CUDA, "could not allocate the device status word");
   MF_REQUIRE(tc_async_status() == 0, MF_ERR_CUDA, "an earlier tensor-core kernel gave up on a bounded wait; results are invalid");
   char* ws = static_cast<char*>(a.workspace);
-  float* delta = reinterpret_cast<float*>(ws + pl.off_delta);
+  float* stats = reinterpret_cast<float*>(ws + pl.off_stats);
+  int* flags = reinterpret_cast<int*>(ws + pl.off_flags);
   float* part = pl.part_direct ? static_cast<float*>(a.d_bias) : reinterpret_cast<float*>(ws + pl.off_part);
   float* dq_acc = reinterpret_cast<float*>(ws + pl.off_dq);
   // the transposed bias copy is kept in a 16-bit type: the bias dtype when that is one, else the q/k/v dtype
@@ -867,10 +948,11 @@ int launch_bwd_ws(const mf_evo_bwd_args& a, cudaStream_t st) {
     const int box[4] = {kHalf, 128, 1, 1};
     if ((r = make_tiled_map(&mbt, biasT, bt_dtype, 4, dims, str, box, 128))) return r;
   }
-  const int64_t rows = (int64_t)a.B * a.N * a.L * a.H;
-  evo_delta_ws_kernel<T><<<(unsigned)((rows + 255) / 256), 256, 0, st>>>(static_cast<const T*>(a.o), static_cast<const T*>(a.d_o),
-                                                                      delta, rows, a.L, a.H, a.D);
-  MF_LAUNCHED("evo_delta_ws_kernel");
+  MF_CUDA(cudaMemsetAsync(flags, 0, sizeof(int) * (size_t)a.B * a.N * a.H, st));
+  const int64_t rows_pad = (int64_t)a.B * a.N * lpad * a.H;
+  evo_stats_ws_kernel<T><<<(unsigned)((rows_pad + 255) / 256), 256, 0, st>>>(static_cast<const T*>(a.o), static_cast<const T*>(a.d_o), a.lse,
+                                                                          stats, flags, rows_pad, a.L, lpad, a.H, a.D);
+  MF_LAUNCHED("evo_stats_ws_kernel");
   const int64_t n_dq = (int64_t)a.B * a.N * a.L * a.H * a.D;
   if (pl.dq_fp32) MF_CUDA(cudaMemsetAsync(dq_acc, 0, sizeof(float) * (size_t)n_dq, st));
 
@@ -889,7 +971,7 @@ int launch_bwd_ws(const mf_evo_bwd_args& a, cudaStream_t st) {
     p.bias_b_mul = 1;
     p.mask = a.mask; for (int i = 0; i < 3; ++i) p.ms[i] = a.mask_strides[i];
     p.mask_dtype = a.mask_dtype;
-    p.lse = a.lse; p.delta = delta;
+    p.stats = stats; p.flags = flags;
     p.dq = a.dq; p.dk = a.dk; p.dv = a.dv;
     p.status = status;
     const size_t smem = 1024 + 4 * (size_t)kAtomB + 3 * kAtomB + 10 * kTileB + 2048 + 4 * sizeof(float) * lpad;
@@ -898,11 +980,11 @@ int launch_bwd_ws(const mf_evo_bwd_args& a, cudaStream_t st) {
     if (pl.dq_stream) {
       auto kern = evo_bwd_ws_kernel<T, TT, true>;
       MF_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      kern<<<grid, kThreads, smem, st>>>(mq, mk, mv, mg, mbt, p);
+      kern<<<grid, kThreads, smem, st>>>(mq, mk, mv, mg, mbt, p MF_TRACE_ARG);
     } else {
       auto kern = evo_bwd_ws_kernel<T, TT, false>;
       MF_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      kern<<<grid, kThreads, smem, st>>>(mq, mk, mv, mg, mbt, p);
+      kern<<<grid, kThreads, smem, st>>>(mq, mk, mv, mg, mbt, p MF_TRACE_ARG);
     }
     MF_LAUNCHED("evo_bwd_ws_kernel");
   }
@@ -922,7 +1004,7 @@ int launch_bwd_ws(const mf_evo_bwd_args& a, cudaStream_t st) {
     p.bias_b_mul = 1;
     p.mask = a.mask; for (int i = 0; i < 3; ++i) p.ms[i] = a.mask_strides[i];
     p.mask_dtype = a.mask_dtype;
-    p.lse = a.lse; p.delta = delta;
+    p.stats = stats;
     p.part = part;
     p.status = status;
     const size_t smem = 1024 + 2 * (size_t)kAtomB + 12 * kTileB + 2048 + 3 * 256 * sizeof(float);
@@ -930,7 +1012,7 @@ int launch_bwd_ws(const mf_evo_bwd_args& a, cudaStream_t st) {
     if (grid > p.n_units) grid = p.n_units;
     auto kern = evo_dbias_ws_kernel<T, TT>;
     MF_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<grid, kThreads, smem, st>>>(mq, mk, mv, mg, mbt, p);
+    kern<<<grid, kThreads, smem, st>>>(mq, mk, mv, mg, mbt, p MF_TRACE_ARG);
     MF_LAUNCHED("evo_dbias_ws_kernel");
     if (!pl.part_direct) {
       const int64_t n_out = (int64_t)a.B * a.H * a.L * a.L;

@@ -1,20 +1,22 @@
 // Pair-biased masked attention forward, warp-specialised (tcgen05 + TMEM + TMA), head sizes up to 32.
 //
-// A persistent CTA (one per SM, 384 threads) runs TWO independent streams.  A stream walks a contiguous range of
+// A persistent CTA (one per SM, 512 threads) runs TWO independent streams.  A stream walks a contiguous range of
 // work items (b, n, h, 128-query tile) and, per item, the key tiles of 128.  Roles:
 //
 //   warps 0-3 / 4-7   softmax warpgroup of stream 0 / 1: one query row (= one TMEM lane) per thread
-//   warp 8 / 9        tcgen05.mma issuer of stream 0 / 1 (one thread)
-//   warp 10 / 11      TMA producer of stream 0 / 1 (one thread)
+//   warp 8 / 9        issuer of the score MMAs of stream 0 / 1 (one thread)
+//   warp 10 / 11      issuer of the P V MMAs of stream 0 / 1 (one thread)
+//   warp 12 / 13      TMA producer of stream 0 / 1 (one thread); warps 14, 15 idle
+// (a single thread issues an MMA every ~60 cycles at best, so the two kinds of products get a thread each)
 //
 // Per key tile the issuer builds   S = Q K^T + sqrt(D) * bias   entirely on the tensor core: two MMAs for Q K^T and
 // eight [128 x 16] x [16 x 16] MMAs that add the bias tile (A operand, straight from the TMA-loaded tile) times
 // alpha * I (B operand) - see evo_tc_common.cuh.  The softmax thread reads its 128 logits, scales them into the base-2
 // domain with the key mask added (one packed FMA per two logits), takes the maximum with three-input max, and writes
-// packed 16-bit P = 2^(x - m) back to TMEM.  P V accumulates into O in TMEM over the key tiles, and a second product
-// P * ones accumulates the row sum next to it, so the softmax threads neither add nor rescale: O and the sum are
-// only multiplied by 2^(m_old - m_new) when the running maximum has grown by more than 8 (rare after the first
-// tile; P then stays below 2^8, far inside the 16-bit range).  Only O and the log-sum-exp reach global memory.
+// packed 16-bit P = 2^(x - m) back to TMEM while adding up the row sum (packed adds that hide under the
+// exponentials).  P V accumulates into O in TMEM over the key tiles; O and the sum are only multiplied by
+// 2^(m_old - m_new) when the running maximum has grown by more than 8 (rare after the first tile; P then stays
+// below 2^8, far inside the 16-bit range).  Only O and the log-sum-exp reach global memory.
 //
 // Every wait is bounded; on expiry the CTA raises a flag, all roles run dry without touching global memory, TMEM is
 // freed and the host sees mf_async_status() != 0.
@@ -25,7 +27,7 @@ namespace {
 using namespace tcx;
 
 constexpr int kT = 128;                      // tile edge (queries and keys)
-constexpr int kThreads = 384;
+constexpr int kThreads = 512;             // registers are allocated to warps in groups of four
 constexpr int kTileB = 128 * 64;             // [128 x 32] 16-bit tile, 64-byte rows, 64B swizzle
 constexpr int kAtomB = 128 * 128;            // bias atom: [128 rows x 64 columns] 16-bit, 128-byte rows, 128B swizzle
 constexpr int kStreamBytes = 6 * kTileB + 3 * kAtomB;     // Q x2, K x2, V x2, three bias atoms
@@ -56,14 +58,17 @@ __device__ __forceinline__ ItemPos item_pos(int it, const FwdWsP& p) {
   return x;
 }
 
+constexpr int kLaunchRegs = 128, kSoftmaxRegs = 208, kHelperRegs = 48;      // registers per thread: at launch / after setmaxnreg
+static_assert(kLaunchRegs * kThreads <= 65536, "register file");
+static_assert(256 * kSoftmaxRegs + (kThreads - 256) * kHelperRegs <= kThreads * kLaunchRegs, "setmaxnreg budget");
+
 template <typename T, typename TB>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __maxnreg__(kLaunchRegs)
 evo_fwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mk,
-                  const __grid_constant__ CUtensorMap mv, const __grid_constant__ CUtensorMap mb, const FwdWsP p) {
+                  const __grid_constant__ CUtensorMap mv, const __grid_constant__ CUtensorMap mb, const FwdWsP p MF_TRACE_PARAM) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  uint8_t* sOnes = smem + 2 * kStreamBytes;           // [128 x 32] ones, V-tile layout (every element equal: no swizzle to mind)
-  uint8_t* sI = sOnes + kTileB;                       // alpha * I tiles, 1 KB each
+  uint8_t* sI = smem + 2 * kStreamBytes;              // alpha * I tiles, 1 KB each
   float* mask2_all = reinterpret_cast<float*>(sI + 2048);
 
   __shared__ StreamBars bars[2];
@@ -86,8 +91,7 @@ evo_fwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
     mbar_fence_init();
     prefetch_tmap(&mq); prefetch_tmap(&mk); prefetch_tmap(&mv); prefetch_tmap(&mb);
   }
-  // constant MMA operands: ones (row sums) and alpha * I (bias)
-  for (int e = tid; e < kTileB / 4; e += kThreads) reinterpret_cast<uint32_t*>(sOnes)[e] = Pack2<T>::pack(1.f, 1.f);
+  // constant MMA operand: alpha * I (bias)
   write_alpha_identity<TB>(sI, p.alpha[0], tid, kThreads);
   write_alpha_identity<TB>(sI + 1024, p.alpha[1], tid, kThreads);
   fence_async_smem();
@@ -97,14 +101,14 @@ evo_fwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
   tc_fence_after();
   volatile int* abort_flag = &abort_s;
 
-  const int s = warp < 8 ? (warp >> 2) : (warp & 1);          // stream of this warp
+  const int s = warp < 8 ? (warp >> 2) : (warp & 1);          // stream of this warp (helper warps alternate)
   StreamBars& bar = bars[s];
   uint8_t* sb = smem + s * kStreamBytes;
   uint8_t* sQ = sb;
   uint8_t* sK = sb + 2 * kTileB;
   uint8_t* sV = sb + 4 * kTileB;
   uint8_t* sB = sb + 6 * kTileB;
-  const uint32_t tbase = tmem_base_s + s * 256;               // S [0,128) | P [128,192) | O [192,224) | row sum [224,256)
+  const uint32_t tbase = tmem_base_s + s * 256;               // S [0,128) | P [128,192) | O [192,224)
 
   const int stream = blockIdx.x * 2 + s;
   const int item_begin = stream * p.items_per_stream;
@@ -115,18 +119,19 @@ evo_fwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
 
   if (warp < 8) {
     // =========================================================================== softmax warpgroup
-    // Register re-partition: the CTA is launched with 168 registers per thread; the helper warpgroup drops to 88 and the
-    // softmax warpgroups rise to 208.  The raise can only draw on what the drop releases inside this CTA.
-    static_assert(256 * 208 + 128 * 88 <= kThreads * 168, "setmaxnreg budget");
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
+    // Register re-partition: the CTA is launched with kLaunchRegs registers per thread; the helper warps drop to
+    // kHelperRegs and the softmax warpgroups rise to kSoftmaxRegs.  The raise can only draw on what the drop releases
+    // inside this CTA (otherwise it never returns): the launcher checks the launch figure.
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kSoftmaxRegs));
     const int wg_tid = tid & 127;
     const int r = (warp & 3) * 32 + lane;
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
-    const uint32_t tS = tbase + lane_addr, tP = tS + 128, tO = tS + 192, tL = tS + 224;
+    const uint32_t tS = tbase + lane_addr, tP = tS + 128, tO = tS + 192;
     float* mask2 = mask2_all + s * p.lpad;
     const float2 c1c1 = make_float2(p.c1, p.c1);
     int prev_bn = -1;
     uint32_t g = 0;
+    MF_TRACE_DECL(tr, 0, blockIdx.x == 0 && tid == 0);
     for (int il = 0; il < n_my; ++il) {
       const ItemPos ip = item_pos(item_begin + il, p);
       const int i = ip.qt * kT + r;
@@ -146,10 +151,13 @@ evo_fwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
         prev_bn = ip.bn;
       }
       float m_used = 0.f;
+      float2 lsum = make_float2(0.f, 0.f);        // row sum of P relative to m_used (two partial sums)
       for (int t = 0; t < n_kt; ++t, ++g) {
         // ---------------------------------------------------------------- S(g) -> registers
+        tr(1);
         wait_or_flag(&bar.s_ready, g & 1, abort_flag);
         tc_fence_after();
+        tr(2);
         uint32_t sr[kT];
         {
           uint32_t (*s4)[32] = reinterpret_cast<uint32_t (*)[32]>(sr);
@@ -159,6 +167,7 @@ evo_fwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bar.s_free);          // the issuer may overwrite S with the next tile's scores
+        tr(3);
         // ---------------------------------------------------------------- pass 1: base-2 logits and their maximum
         const float* mk = mask2 + t * kT;
         float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -173,6 +182,7 @@ evo_fwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
           mx[c4 & 1 ? 3 : 1] = max3f(mx[c4 & 1 ? 3 : 1], b2.x, b2.y);
         }
         const float m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+        tr(4);
         if (t == 0) {
           m_used = m_blk;
         } else {
@@ -192,15 +202,13 @@ evo_fwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
               for (int d = 0; d < 16; ++d) o16[d] = __float_as_uint(__uint_as_float(o16[d]) * f);
               tmem_st16(tO + hf * 16, o16);
             }
-            // of the 32 row-sum columns (all equal) only the first is ever read
-            const uint32_t l0 = tmem_ld1(tL);
-            tmem_ld_wait();
-            tmem_st1(tL, __float_as_uint(__uint_as_float(l0) * f));
             tmem_st_wait();
+            lsum.x *= f; lsum.y *= f;
           }
         }
         // ---------------------------------------------------------------- pass 2: P = 2^(x - m) as packed 16-bit
         if (g > 0) wait_or_flag(&bar.pv_done, (g - 1) & 1, abort_flag);      // the previous product has read P
+        tr(5);
         const float2 mm = make_float2(m_used, m_used);
 #pragma unroll
         for (int qr = 0; qr < 4; ++qr) {
@@ -208,7 +216,9 @@ evo_fwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
 #pragma unroll
           for (int jj = 0; jj < 16; ++jj) {
             const float2 x = sub2(make_float2(__uint_as_float(sr[qr * 32 + 2 * jj]), __uint_as_float(sr[qr * 32 + 2 * jj + 1])), mm);
-            pk[jj] = Pack2<T>::pack(ex2f(x.x), ex2f(x.y));
+            const float2 e = make_float2(ex2f(x.x), ex2f(x.y));
+            lsum = add2(lsum, e);
+            pk[jj] = Pack2<T>::pack(e.x, e.y);
           }
           tmem_st16(tP + qr * 16, pk);
         }
@@ -216,15 +226,18 @@ evo_fwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bar.p_ready);
+        tr(6);
       }
       // ------------------------------------------------------------------ item done: O / l and the log-sum-exp
       wait_or_flag(&bar.pv_done, (g - 1) & 1, abort_flag);
       tc_fence_after();
+      tr(7);
       uint32_t o32[32];
       tmem_ld32(tO, o32);
-      const float l = __uint_as_float(tmem_ld1(tL));
+      const float l = lsum.x + lsum.y;
       tmem_ld_wait();
       tc_fence_before();
+      tr(8);
       if (i < p.L && !*abort_flag) {
         const float inv = 1.f / l;
         T* orow = static_cast<T*>(p.o) + ((((int64_t)ip.b * p.N + ip.n) * p.L + i) * p.H + ip.h) * p.D;
@@ -243,19 +256,27 @@ evo_fwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
         // backward kernels recognise
         p.lse[(((int64_t)ip.b * p.N + ip.n) * p.H + ip.h) * p.L + i] = m_used <= -1e38f ? -FLT_MAX : (m_used + lg2f(l)) * kLn2;
       }
+      tr(9);
     }
   } else {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");
-    if (warp < 10 && lane == 0) {
-      // ========================================================================= tcgen05.mma issuer of stream s
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kHelperRegs));
+    // The helper roles are run by whole warps (one elected lane issues: see mma_ss_el); every exit decision is a warp vote.
+    auto dead = [&] { return __any_sync(0xffffffffu, *abort_flag) != 0; };
+    if (warp < 10) {
+      // ========================================================================= score-MMA issuer of stream s
       const uint32_t id_s = idesc_f16(128, 128, p.fmt, 0, 0);
       const uint32_t id_b = idesc_f16(128, 16, p.bfmt, 0, 0);
-      const uint32_t id_o = idesc_f16(128, 32, p.fmt, 0, 1);           // B (V, ones) MN-major
       constexpr uint32_t hi64 = desc_hi(512, kSw64), hi128 = desc_hi(1024, kSw128);
-      const uint32_t ones_lo = desc_lo(smem_u32(sOnes), 16);
-      const uint32_t tS = tbase, tP = tbase + 128, tO = tbase + 192, tL = tbase + 224;
+      const uint32_t tS = tbase;
+      const uint32_t q_base = desc_lo(smem_u32(sQ), 16), k_base = desc_lo(smem_u32(sK), 16), b_base = desc_lo(smem_u32(sB), 16);
+      const uint32_t i_lo0 = desc_lo(smem_u32(sI), 16), i_lo1 = i_lo0 + 1024 / 16;
+      const bool two_terms = p.n_alpha > 1;
       uint32_t bslot = 0, buse = 0;               // bias atoms consumed: ring slot and use count of the next one
-      auto issue_s = [&](uint32_t g, int il, int t) {      // S(g) = Q K^T + alpha * bias
+      MF_TRACE_DECL(tr, 1, blockIdx.x == 0 && warp == 8 && lane == 0);
+      const uint32_t g_total = (uint32_t)n_my * n_kt;
+      int il = 0, t = 0;
+      for (uint32_t g = 0; g < g_total; ++g) {       // S(g) = Q K^T + alpha * bias
+        tr(10);
         if (t == 0) wait_or_flag(&bar.q_full[il & 1], (il >> 1) & 1, abort_flag);
         wait_or_flag(&bar.k_full[g & 1], (g >> 1) & 1, abort_flag);
         const uint32_t slot0 = bslot, use0 = buse;
@@ -265,86 +286,106 @@ evo_fwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
         wait_or_flag(&bar.b_full[slot1], use1 & 1, abort_flag);
         bslot = slot1 + 1; buse = use1;
         if (bslot == 3) { bslot = 0; ++buse; }
+        tr(11);
         if (g > 0) wait_or_flag(&bar.s_free, (g - 1) & 1, abort_flag);
         tc_fence_after();
-        if (*abort_flag) return;
-        const uint32_t q_lo = desc_lo(smem_u32(sQ + (il & 1) * kTileB), 16), k_lo = desc_lo(smem_u32(sK + (g & 1) * kTileB), 16);
+        tr(12);
+        if (!dead()) {
+          const uint32_t q_lo = q_base + (il & 1) * (kTileB / 16), k_lo = k_base + (g & 1) * (kTileB / 16);
+          mma_ss_el(tS, q_lo, hi64, k_lo, hi64, id_s, false);
+          mma_ss_el(tS, q_lo + 2, hi64, k_lo + 2, hi64, id_s, true);
+          const uint32_t a0 = b_base + slot0 * (kAtomB / 16), a1 = b_base + slot1 * (kAtomB / 16);
 #pragma unroll
-        for (int ks = 0; ks < 2; ++ks) mma_ss_lh(tS, q_lo + ks * 2, hi64, k_lo + ks * 2, hi64, id_s, ks > 0);
-        const uint32_t a_lo[2] = {desc_lo(smem_u32(sB + slot0 * kAtomB), 16), desc_lo(smem_u32(sB + slot1 * kAtomB), 16)};
-        for (int term = 0; term < p.n_alpha; ++term) {
-          const uint32_t i_lo = desc_lo(smem_u32(sI + term * 1024), 16);
+          for (int c = 0; c < 4; ++c) mma_ss_el(tS + c * 16, a0 + c * 2, hi128, i_lo0, hi64, id_b, true);      // 16 key columns each
 #pragma unroll
-          for (int c = 0; c < 8; ++c)       // 16 key columns each
-            mma_ss_lh(tS + c * 16, a_lo[c >> 2] + (c & 3) * 2, hi128, i_lo, hi64, id_b, true);
+          for (int c = 0; c < 4; ++c) mma_ss_el(tS + 64 + c * 16, a1 + c * 2, hi128, i_lo0, hi64, id_b, true);
+          if (two_terms) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) mma_ss_el(tS + c * 16, a0 + c * 2, hi128, i_lo1, hi64, id_b, true);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) mma_ss_el(tS + 64 + c * 16, a1 + c * 2, hi128, i_lo1, hi64, id_b, true);
+          }
+          tc_commit_el(&bar.s_ready);
+          tc_commit_el(&bar.k_empty[g & 1]);
+          tc_commit_el(&bar.b_empty[slot0]);
+          tc_commit_el(&bar.b_empty[slot1]);
+          if (t == n_kt - 1) tc_commit_el(&bar.q_empty[il & 1]);
         }
-        tc_commit(&bar.s_ready);
-        tc_commit(&bar.k_empty[g & 1]);
-        tc_commit(&bar.b_empty[slot0]);
-        tc_commit(&bar.b_empty[slot1]);
-        if (t == n_kt - 1) tc_commit(&bar.q_empty[il & 1]);
-      };
-      auto issue_pv = [&](uint32_t g, int t) {             // O (+)= P V,  row sum (+)= P ones
-        wait_or_flag(&bar.p_ready, g & 1, abort_flag);
-        wait_or_flag(&bar.v_full[g & 1], (g >> 1) & 1, abort_flag);
-        tc_fence_after();
-        if (*abort_flag) return;
-        const uint32_t v_lo = desc_lo(smem_u32(sV + (g & 1) * kTileB), 16);
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) mma_ts_lh(tO, tP + ks * 8, v_lo + ks * 64, hi64, id_o, t > 0 || ks > 0);
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) mma_ts_lh(tL, tP + ks * 8, ones_lo + ks * 64, hi64, id_o, t > 0 || ks > 0);
-        tc_commit(&bar.pv_done);
-        tc_commit(&bar.v_empty[g & 1]);
-      };
-      const uint32_t g_total = (uint32_t)n_my * n_kt;
-      if (g_total > 0) issue_s(0, 0, 0);
-      int il = 0, t = 0;
-      for (uint32_t g = 0; g < g_total; ++g) {
-        int il1 = il, t1 = t + 1;
-        if (t1 == n_kt) { t1 = 0; ++il1; }
-        if (g + 1 < g_total) issue_s(g + 1, il1, t1);
-        issue_pv(g, t);
-        il = il1; t = t1;
+        tr(13);
+        if (++t == n_kt) { t = 0; ++il; }
       }
-    } else if (warp >= 10 && lane == 0) {
+    } else if (warp < 12) {
+      // ========================================================================= P V issuer of stream s
+      const uint32_t id_o = idesc_f16(128, 32, p.fmt, 0, 1);           // B (V) MN-major
+      constexpr uint32_t hi64 = desc_hi(512, kSw64);
+      const uint32_t tP = tbase + 128, tO = tbase + 192;
+      const uint32_t v_base = desc_lo(smem_u32(sV), 16);
+      MF_TRACE_DECL(tr, 2, blockIdx.x == 0 && warp == 10 && lane == 0);
+      const uint32_t g_total = (uint32_t)n_my * n_kt;
+      int t = 0;
+      for (uint32_t g = 0; g < g_total; ++g) {       // O (+)= P V
+        tr(15);
+        wait_or_flag(&bar.v_full[g & 1], (g >> 1) & 1, abort_flag);
+        wait_or_flag(&bar.p_ready, g & 1, abort_flag);
+        tc_fence_after();
+        tr(16);
+        if (!dead()) {
+          const uint32_t v_lo = v_base + (g & 1) * (kTileB / 16);
+          mma_ts_el(tO, tP, v_lo, hi64, id_o, t > 0);
+#pragma unroll
+          for (int ks = 1; ks < 8; ++ks) mma_ts_el(tO, tP + ks * 8, v_lo + ks * 64, hi64, id_o, true);
+          tc_commit_el(&bar.pv_done);
+          tc_commit_el(&bar.v_empty[g & 1]);
+        }
+        tr(17);
+        if (++t == n_kt) t = 0;
+      }
+    } else if (warp < 14) {
       // ========================================================================= TMA producer of stream s
       uint32_t g = 0, bslot = 0, buse = 0;
       uint32_t nq = 0, nk = 0, nv = 0, nb = 0;      // loads issued, for the drain on abort
       auto load_q = [&](int il) {        // the Q tile of item il (requested one key tile before the item starts)
         const ItemPos iq = item_pos(item_begin + il, p);
         if (il >= 2) wait_or_flag(&bar.q_empty[il & 1], ((il >> 1) - 1) & 1, abort_flag);
-        if (*abort_flag) return;
-        mbar_expect_tx(&bar.q_full[il & 1], kTileB);
-        tma_load_5d(sQ + (il & 1) * kTileB, &mq, &bar.q_full[il & 1], 0, iq.h, iq.qt * kT, iq.n, iq.b);
+        if (dead()) return;
+        if (elect_one()) {
+          mbar_expect_tx(&bar.q_full[il & 1], kTileB);
+          tma_load_5d(sQ + (il & 1) * kTileB, &mq, &bar.q_full[il & 1], 0, iq.h, iq.qt * kT, iq.n, iq.b);
+        }
         ++nq;
       };
       if (n_my > 0) load_q(0);
-      for (int il = 0; il < n_my && !*abort_flag; ++il) {
+      for (int il = 0; il < n_my && !dead(); ++il) {
         const ItemPos ip = item_pos(item_begin + il, p);
         for (int t = 0; t < n_kt; ++t, ++g) {
           if (t == n_kt - 1 && il + 1 < n_my) load_q(il + 1);
           if (g >= 2) wait_or_flag(&bar.k_empty[g & 1], ((g >> 1) - 1) & 1, abort_flag);
-          if (*abort_flag) break;
-          mbar_expect_tx(&bar.k_full[g & 1], kTileB);
-          tma_load_5d(sK + (g & 1) * kTileB, &mk, &bar.k_full[g & 1], 0, ip.h, t * kT, ip.n, ip.b);
+          if (dead()) break;
+          if (elect_one()) {
+            mbar_expect_tx(&bar.k_full[g & 1], kTileB);
+            tma_load_5d(sK + (g & 1) * kTileB, &mk, &bar.k_full[g & 1], 0, ip.h, t * kT, ip.n, ip.b);
+          }
           ++nk;
           for (int hf = 0; hf < 2; ++hf) {
             if (buse >= 1) wait_or_flag(&bar.b_empty[bslot], (buse - 1) & 1, abort_flag);
-            if (*abort_flag) break;
-            mbar_expect_tx(&bar.b_full[bslot], kAtomB);
-            tma_load_4d(sB + bslot * kAtomB, &mb, &bar.b_full[bslot], t * kT + hf * 64, ip.qt * kT, ip.h, ip.b * p.bias_b_mul);
+            if (dead()) break;
+            if (elect_one()) {
+              mbar_expect_tx(&bar.b_full[bslot], kAtomB);
+              tma_load_4d(sB + bslot * kAtomB, &mb, &bar.b_full[bslot], t * kT + hf * 64, ip.qt * kT, ip.h, ip.b * p.bias_b_mul);
+            }
             ++nb;
             if (++bslot == 3) { bslot = 0; ++buse; }
           }
           if (g >= 2) wait_or_flag(&bar.v_empty[g & 1], ((g >> 1) - 1) & 1, abort_flag);
-          if (*abort_flag) break;
-          mbar_expect_tx(&bar.v_full[g & 1], kTileB);
-          tma_load_5d(sV + (g & 1) * kTileB, &mv, &bar.v_full[g & 1], 0, ip.h, t * kT, ip.n, ip.b);
+          if (dead()) break;
+          if (elect_one()) {
+            mbar_expect_tx(&bar.v_full[g & 1], kTileB);
+            tma_load_5d(sV + (g & 1) * kTileB, &mv, &bar.v_full[g & 1], 0, ip.h, t * kT, ip.n, ip.b);
+          }
           ++nv;
         }
       }
-      if (*abort_flag) {
+      if (dead() && lane == 0) {
         // the copies already requested must land before the CTA's shared memory is given back (bounded)
         auto drain = [&](uint64_t* ring, uint32_t n, uint32_t depth) {
           for (uint32_t back = 0; back < depth && back < n; ++back) {
@@ -395,10 +436,13 @@ int launch_fwd_ws(const mf_evo_fwd_args& a, cudaStream_t st) {
   const int pairs = (p.n_items + 1) / 2;
   if (grid > pairs) grid = pairs;
   p.items_per_stream = (p.n_items + 2 * grid - 1) / (2 * grid);
-  const size_t smem = 1024 + 2 * (size_t)kStreamBytes + kTileB + 2048 + 2 * sizeof(float) * p.lpad;
+  const size_t smem = 1024 + 2 * (size_t)kStreamBytes + 2048 + 2 * sizeof(float) * p.lpad;
   auto kern = evo_fwd_ws_kernel<T, TB>;
+  cudaFuncAttributes fa;
+  MF_CUDA(cudaFuncGetAttributes(&fa, kern));
+  MF_REQUIRE(fa.numRegs == kLaunchRegs, MF_ERR_CUDA, "evo_fwd_ws_kernel was built with %d registers per thread, %d expected", fa.numRegs, kLaunchRegs);
   MF_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<grid, kThreads, smem, st>>>(mq, mk, mv, mb, p);
+  kern<<<grid, kThreads, smem, st>>>(mq, mk, mv, mb, p MF_TRACE_ARG);
   MF_LAUNCHED("evo_fwd_ws_kernel");
   return MF_OK;
 }

@@ -22,6 +22,10 @@ StatusWord* status_slot() {
   return &w;
 }
 
+#ifdef MF_TRACE
+long long* g_trace = nullptr;
+#endif
+
 int sm_count() {
   static int n[64] = {};
   int dev = 0;
@@ -55,3 +59,8 @@ bool debug_old_evo(int which) {
 }
 
 }  // namespace mf
+
+#ifdef MF_TRACE
+// debug builds only: device buffer of 8 * kTraceLen 64-bit words that the attention kernels' phase trace is written to
+extern "C" __attribute__((visibility("default"))) void mf_debug_set_trace(long long* p) { mf::tcx::g_trace = p; }
+#endif

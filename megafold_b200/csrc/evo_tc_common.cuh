@@ -158,6 +158,28 @@ __device__ __forceinline__ void write_alpha_identity(uint8_t* tile, float alpha,
   }
 }
 
+// ---- phase trace (debug builds only: -DMF_TRACE) -------------------------------------------------------
+// One elected thread per role of CTA 0 records (tag, clock64) pairs into a global buffer handed in through
+// mf_debug_set_trace(); role `r` owns entries [r * kTraceLen, (r + 1) * kTraceLen).  Compiled out otherwise.
+constexpr int kTraceLen = 512;
+#ifdef MF_TRACE
+extern long long* g_trace;
+struct Tracer {
+  long long* buf; int n;
+  __device__ __forceinline__ Tracer(long long* base, int role, bool on) : buf(on && base ? base + role * kTraceLen : nullptr), n(0) {}
+  __device__ __forceinline__ void operator()(int tag) {
+    if (buf && n + 2 <= kTraceLen) { buf[n] = tag; buf[n + 1] = clock64(); n += 2; }
+  }
+};
+#define MF_TRACE_DECL(name, role, on) Tracer name(g_trace_dev, (role), (on))
+#define MF_TRACE_PARAM , long long* g_trace_dev
+#define MF_TRACE_ARG , ::mf::tcx::g_trace
+#else
+#define MF_TRACE_DECL(name, role, on) auto name = [](int) {}
+#define MF_TRACE_PARAM
+#define MF_TRACE_ARG
+#endif
+
 // ---- host side ------------------------------------------------------------------------------------
 // sqrt(D) as a sum of values representable in the 16-bit type `dt`; returns the number of terms (1 when the first
 // one is within 2.5e-4 relative, which is below the rounding of the bias values themselves)
