@@ -88,8 +88,10 @@ MF_API int mf_evo_fwd(const mf_evo_fwd_args* args, void* stream);
 /*
  * Backward of the above.  d_o, o: contiguous [B,N,L,H,D].  dq,dk,dv: contiguous [B,N,L,H,D] in
  * `dtype`.  d_bias: contiguous [B,1,H,L,L] in `dbias_dtype` (MF_F32 or `dtype`), the sum of dS over
- * the N rows; it is fully overwritten (no need to zero it).  The reduction over rows is done in a
- * fixed order, so results are bit-reproducible run to run.
+ * the N rows; it is fully overwritten (no need to zero it).  d_bias is summed in a fixed order on every
+ * path and is bit-reproducible run to run; so are dk and dv.  dq is bit-reproducible except where the
+ * tensor-core path spreads one row's key tiles over several CTAs or streams dq through memory (N*B*H below
+ * the SM count, or L > 768): those partial sums meet in fp32 atomic adds whose order varies.
  * workspace: at least mf_evo_bwd_workspace_bytes() bytes, 256-byte aligned.
  *
  * Replaces EvoformerAttention.backward, evoattention.py:783-903 (kernels _attn_bwd_preprocess
@@ -234,6 +236,11 @@ MF_API const char* mf_last_path(void);
 /* Non-zero once a kernel on the current device gave up on one of its bounded waits (its outputs are
  * then invalid).  Readable without a device synchronisation; sticky until the process ends. */
 MF_API int mf_async_status(void);
+/* Self-test of that mechanism (no counterpart in the reference): launches one small kernel whose only wait, on a
+ * barrier that nobody completes, runs into its cap after a few milliseconds; the kernel then leaves through the same
+ * exit path as the attention kernels, so afterwards mf_async_status() is non-zero and the tensor-core entry points of
+ * this process refuse to launch.  Nothing faults and the context stays usable.  Meant for a throw-away process. */
+MF_API int mf_selftest_bounded_wait(void* stream);
 
 #ifdef __cplusplus
 }

@@ -95,6 +95,7 @@ SYMBOLS = {
     "mf_kernel_launch_count": (C.c_uint64, []),
     "mf_last_path": (C.c_char_p, []),
     "mf_async_status": (C.c_int, []),
+    "mf_selftest_bounded_wait": (C.c_int, [_vp]),
 }
 
 _lib = None

@@ -57,9 +57,10 @@ int mf_evo_fwd(const mf_evo_fwd_args* args, void* stream) {
   MF_REQUIRE(a.o && a.lse, MF_ERR_BAD_ARG, "o and lse must not be NULL");
   r = check_device(); if (r) return r;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (!(a.flags & MF_FLAG_FORCE_SIMT) &&
+  // the tensor-core kernels write o with 16-byte stores
+  if (!(a.flags & MF_FLAG_FORCE_SIMT) && ((uintptr_t)a.o & 15) == 0 &&
       evo_tc_supported(a.B, a.N, a.L, a.H, a.D, a.dtype, a.q_strides, a.k_strides, a.v_strides, a.q, a.k, a.v)) {
-    r = (evo_fwd_ws_supported(a) && !debug_old_evo(0)) ? evo_fwd_ws(a, st) : evo_fwd_tc(a, st);
+    r = evo_fwd_ws_supported(a) ? evo_fwd_ws(a, st) : evo_fwd_tc(a, st);
     if (r == MF_OK) set_last_path("tcgen05");
     return r;
   }
@@ -69,16 +70,15 @@ int mf_evo_fwd(const mf_evo_fwd_args* args, void* stream) {
 }
 
 static bool evo_bwd_use_tc(const mf_evo_bwd_args& a) {
-  return !(a.flags & MF_FLAG_FORCE_SIMT) && evo_bwd_tc_available() && evo_bwd_tc_shape_ok(a.L, a.D) &&
+  // the tensor-core kernels read o / d_o and write dq / dk / dv with 16-byte accesses
+  const uintptr_t align = (uintptr_t)a.o | (uintptr_t)a.d_o | (uintptr_t)a.dq | (uintptr_t)a.dk | (uintptr_t)a.dv;
+  return !(a.flags & MF_FLAG_FORCE_SIMT) && (align & 15) == 0 && evo_bwd_ws_shape_ok(a.L, a.D) &&
          evo_tc_supported(a.B, a.N, a.L, a.H, a.D, a.dtype, a.q_strides, a.k_strides, a.v_strides, a.q, a.k, a.v);
 }
 
-static bool evo_bwd_use_ws(const mf_evo_bwd_args& a) { return evo_bwd_ws_shape_ok(a.L, a.D) && !debug_old_evo(1); }
-
 size_t mf_evo_bwd_workspace_bytes(const mf_evo_bwd_args* args) {
   if (!args) return 0;
-  if (!evo_bwd_use_tc(*args)) return evo_bwd_simt_workspace(*args);
-  return evo_bwd_use_ws(*args) ? evo_bwd_ws_workspace(*args) : evo_bwd_tc_workspace(*args);
+  return evo_bwd_use_tc(*args) ? evo_bwd_ws_workspace(*args) : evo_bwd_simt_workspace(*args);
 }
 
 int mf_evo_bwd(const mf_evo_bwd_args* args, void* stream) {
@@ -96,7 +96,7 @@ int mf_evo_bwd(const mf_evo_bwd_args* args, void* stream) {
   r = check_device(); if (r) return r;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (evo_bwd_use_tc(a)) {
-    r = evo_bwd_use_ws(a) ? evo_bwd_ws(a, st) : evo_bwd_tc(a, st);
+    r = evo_bwd_ws(a, st);
     if (r == MF_OK) set_last_path("tcgen05");
     return r;
   }
@@ -163,12 +163,14 @@ int mf_lnl_bwd(const mf_lnl_bwd_args* args, void* stream) {
 
 int mf_swiglu_fwd(const void* x, void* y, int64_t M, int32_t inner, int32_t dtype, void* stream) {
   MF_REQUIRE(x && y && M >= 0 && inner > 0, MF_ERR_BAD_ARG, "bad swiglu arguments");
+  MF_REQUIRE(float_dtype(dtype), MF_ERR_BAD_ARG, "dtype %d is not a floating type", dtype);
   int r = check_device(); if (r) return r;
   return swiglu_fwd(x, y, M, inner, dtype, static_cast<cudaStream_t>(stream));
 }
 
 int mf_swiglu_bwd(const void* x, const void* dy, void* dx, int64_t M, int32_t inner, int32_t dtype, void* stream) {
   MF_REQUIRE(x && dy && dx && M >= 0 && inner > 0, MF_ERR_BAD_ARG, "bad swiglu arguments");
+  MF_REQUIRE(float_dtype(dtype), MF_ERR_BAD_ARG, "dtype %d is not a floating type", dtype);
   int r = check_device(); if (r) return r;
   return swiglu_bwd(x, dy, dx, M, inner, dtype, static_cast<cudaStream_t>(stream));
 }
@@ -220,6 +222,7 @@ int mf_transition_bwd(const mf_transition_bwd_args* args, void* stream) {
   const size_t need = mf_transition_bwd_workspace_bytes(args);
   MF_REQUIRE(a.workspace && a.workspace_bytes >= need, MF_ERR_WORKSPACE, "workspace of %zu bytes needed, %zu given", need,
              a.workspace ? a.workspace_bytes : (size_t)0);
+  MF_REQUIRE(((uintptr_t)a.workspace & 255) == 0, MF_ERR_ALIGNMENT, "workspace must be 256-byte aligned");
   int r = check_device(); if (r) return r;
   r = transition_bwd_simt(a, static_cast<cudaStream_t>(stream));
   if (r == MF_OK) set_last_path(transition_bwd_runs_on_tc(a) ? "tcgen05" : "simt");
@@ -231,5 +234,10 @@ int mf_version(void) { return MF_ABI_VERSION; }
 uint64_t mf_kernel_launch_count(void) { return g_launches.load(); }
 const char* mf_last_path(void) { return t_last_path; }
 int mf_async_status(void) { return tc_async_status(); }
+
+int mf_selftest_bounded_wait(void* stream) {
+  int r = check_device(); if (r) return r;
+  return bounded_wait_selftest(static_cast<cudaStream_t>(stream));
+}
 
 }  // extern "C"

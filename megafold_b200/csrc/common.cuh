@@ -125,15 +125,11 @@ size_t evo_bwd_noalloc_max_rows();
 
 bool evo_tc_supported(int B, int N, int L, int H, int D, int dtype, const int64_t* qs, const int64_t* ks,
                       const int64_t* vs, const void* q, const void* k, const void* v);
-bool evo_bwd_tc_available();
-bool evo_bwd_tc_shape_ok(int L, int D);   // the dQ accumulators of all query tiles must fit in TMEM
 int tc_async_status();
+int bounded_wait_selftest(cudaStream_t st);
 int evo_fwd_tc(const mf_evo_fwd_args& a, cudaStream_t st);
 bool evo_fwd_ws_supported(const mf_evo_fwd_args& a);
 int evo_fwd_ws(const mf_evo_fwd_args& a, cudaStream_t st);
-bool debug_old_evo(int which);
-int evo_bwd_tc(const mf_evo_bwd_args& a, cudaStream_t st);
-size_t evo_bwd_tc_workspace(const mf_evo_bwd_args& a);
 bool evo_bwd_ws_shape_ok(int L, int D);
 int evo_bwd_ws(const mf_evo_bwd_args& a, cudaStream_t st);
 size_t evo_bwd_ws_workspace(const mf_evo_bwd_args& a);

@@ -328,6 +328,10 @@ evo_bwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
           // ---- packed P^T / dS^T over the scores just read (A operands of the dV / dK products)
           tmem_st16(tST, pp);
           tmem_st16(tDP, dd);
+          tmem_st_wait();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bar.written[team]);
           // ---- dS^T also to the shared-memory tile of this block (A operand of the dQ product), once the dQ
           // product that read this buffer two blocks ago is complete
           if (g >= 2) wait_or_flag(&bar.dq_done[g & 1], ((g >> 1) - 1) & 1, abort_flag);
@@ -338,11 +342,9 @@ evo_bwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
             for (int c = 0; c < 4; ++c)
               *reinterpret_cast<uint4*>(atom + swz_offset(r, ch * 4 + c, 128)) = make_uint4(dd[c * 4], dd[c * 4 + 1], dd[c * 4 + 2], dd[c * 4 + 3]);
           }
-          tmem_st_wait();
           fence_async_smem();
-          tc_fence_before();
           __syncwarp();
-          if (lane == 0) { mbar_arrive(&bar.written[team]); mbar_arrive(&bar.ds_written[g & 1]); }
+          if (lane == 0) mbar_arrive(&bar.ds_written[g & 1]);
           tr(6);
           // ---- streamed dQ: the product of the previous block sits in accumulator (g - 1) & 1; the four warps with
           // w == (g - 1) & 3 add it to global memory and hand the accumulator back

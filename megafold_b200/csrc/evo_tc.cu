@@ -1,7 +1,5 @@
 // Host-side support shared by the tensor-core attention kernels: status word, device queries and the
 // test that decides whether a call can take the tensor-core path.
-#include <stdlib.h>
-
 #include "evo_tc_common.cuh"
 
 namespace mf {
@@ -37,6 +35,30 @@ int sm_count() {
 
 }  // namespace tcx
 
+namespace {
+// One CTA waits, with a short cap, on an mbarrier that nobody completes, then takes the same exit path as the
+// attention kernels: raise the CTA's flag, report through the status word, return normally.
+__global__ void bounded_wait_selftest_kernel(int* status, int cap) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_s;
+  if (threadIdx.x == 0) { abort_s = 0; tc::mbar_init(&bar, 1); tc::mbar_fence_init(); }
+  __syncthreads();
+  bool done = false;
+  for (int i = 0; i < cap && !done; ++i) done = tc::mbar_try_wait(&bar, 0);
+  if (!done) abort_s = 1;
+  __syncthreads();
+  if (threadIdx.x == 0 && abort_s) *reinterpret_cast<volatile int*>(status) = 1;
+}
+}  // namespace
+
+int bounded_wait_selftest(cudaStream_t st) {
+  int* status = tcx::status_word();
+  MF_REQUIRE(status, MF_ERR_CUDA, "could not allocate the device status word");
+  bounded_wait_selftest_kernel<<<1, 128, 0, st>>>(status, 2048);
+  MF_LAUNCHED("bounded_wait_selftest_kernel");
+  return MF_OK;
+}
+
 int tc_async_status() {
   tcx::StatusWord* w = tcx::status_slot();
   return (w && w->host) ? *reinterpret_cast<volatile int*>(w->host) : 0;
@@ -48,14 +70,6 @@ bool evo_tc_supported(int B, int N, int L, int H, int D, int dtype, const int64_
   if (D % 8 != 0 || D > 64 || L > 4096) return false;
   return tcx::qkv_strides_ok(q, qs, B, N, L, H) && tcx::qkv_strides_ok(k, ks, B, N, L, H) &&
          tcx::qkv_strides_ok(v, vs, B, N, L, H);
-}
-
-bool evo_bwd_tc_available() { return true; }
-
-bool debug_old_evo(int which) {
-  static const bool f = [] { const char* e = getenv("MF_DEBUG_OLD_EVO_FWD"); return e && e[0] == '1'; }();
-  static const bool b = [] { const char* e = getenv("MF_DEBUG_OLD_EVO_BWD"); return e && e[0] == '1'; }();
-  return which == 0 ? f : b;
 }
 
 }  // namespace mf

@@ -1,25 +1,23 @@
-// Pair-biased masked attention forward on the 5th-generation tensor cores (tcgen05 + TMEM + TMA).
+// Pair-biased masked attention forward on the tensor cores (tcgen05 + TMEM + TMA): the GENERAL kernel, for the calls
+// the warp-specialised kernel (evo_fwd_ws.cu) does not take - head sizes 33..64, an fp32 or unaligned pair bias,
+// rows longer than 2048 tokens.
 //
-// A persistent CTA (one per SM, 256 threads) runs TWO independent streams, one per warpgroup.  A
-// stream walks a contiguous range of work items (b, n, h, 128-query tile) and, per item, the key
-// tiles of 128.  Inside a stream every thread owns one query row (= one TMEM lane); thread 0 of the
-// warpgroup (the leader) also issues the stream's TMA loads and tcgen05.mma instructions, so no
-// cross-warp hand-off sits on the critical path:
+// A persistent CTA (one per SM, 256 threads) runs TWO independent streams, one per warpgroup.  A stream walks a
+// contiguous range of work items (b, n, h, 128-query tile) and, per item, the key tiles of 128.  Inside a stream every
+// thread owns one query row (= one TMEM lane); three "officer" threads of the warpgroup also issue the stream's
+// tcgen05.mma instructions (thread 0), its Q/K/V TMA loads (thread 32) and its bias TMA loads (thread 64):
 //
 //   wait S(t) in TMEM -> tcgen05.ld the whole 128-column row into registers -> group barrier ->
-//   leader issues S(t+1) = Q K(t+1)^T at once (the S buffer is free again: registers double-buffer it)
+//   S(t+1) = Q K(t+1)^T is issued at once (the S buffer is free again: registers double-buffer it)
 //   -> row thread: logits in base 2 (scale, bias from shared memory, key mask), running max, exp2,
 //   row sum, packed 16-bit P -> fold O_tile(t-1) from TMEM into the register accumulator ->
-//   tcgen05.st P -> group barrier -> leader issues O_tile(t) = P V(t) (P as TMEM A operand, V as
-//   MN-major B operand) and tops up the TMA rings.
-//
-// While one stream exponentiates, the tensor pipe and TMA work for the other.  Only O and the
-// log-sum-exp per query row reach global memory.
+//   tcgen05.st P -> group barrier -> O_tile(t) = P V(t) is issued (P as TMEM A operand, V as
+//   MN-major B operand) and the TMA rings are topped up.
 //
 // Operand tiles are [128 rows x DP] (DP = 32: 64-byte rows, 64B swizzle; DP = 64: 128-byte rows) fetched
 // from the strided [B, N, L, H, D] tensors by 5-D tensor maps; smaller head sizes are zero-filled by TMA.
-// The pair bias is staged by TMA as [128 rows x 32 columns] chunks (64-byte rows, 64B swizzle) when
-// its dtype is 16 bit and its strides allow; otherwise the row thread reads it from global memory.
+// A 16-bit pair bias with TMA-addressable rows is staged as [128 rows x 64 columns] chunks (128-byte rows, 128B
+// swizzle, DP = 32 only); otherwise the row thread reads it from global memory.
 //
 // Every wait is bounded; on expiry the CTA raises a flag that all threads honour at their next group
 // barrier, TMEM is freed and the host sees mf_async_status() != 0.
@@ -54,16 +52,7 @@ struct FwdP {
   const void* bias; int64_t bs[4]; int bias_fast;
   const void* mask; int64_t ms[3]; int mask_dtype;
   void* o; float* lse; int* status;
-  long long* timeline;   // debug builds only
 };
-
-// Phase timestamps of thread 0 of stream 0 in CTA 0; compiled in only with -DMF_TIMELINE.
-#ifdef MF_TIMELINE
-long long* g_timeline = nullptr;
-#define MF_TL(tag) do { if (p.timeline && blockIdx.x == 0 && tid == 0 && tl_n < 250) { p.timeline[2 * tl_n] = (tag); p.timeline[2 * tl_n + 1] = clock64(); ++tl_n; } } while (0)
-#else
-#define MF_TL(tag) do { } while (0)
-#endif
 
 struct StreamBars {
   uint64_t q_full, k_full[3], v_full[kVS], b_full[kBC], b_empty[kBC], s_ready, pv_done;
@@ -254,9 +243,7 @@ evo_fwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
     }
   };
 
-  int tl_n = 0; (void)tl_n;
   for (int g = 0; g < g_total; ++g) {
-    MF_TL(0);
     if (t == 0) {
       // ---------------------------------------------------------------- new item
       const int it = item_begin + item_local;
@@ -291,20 +278,16 @@ evo_fwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
       }
     }
     // ------------------------------------------------------------------ S(g) -> registers
-    MF_TL(1);
     wait_or_flag(&bar.s_ready, g & 1, abort_flag);
     tc_fence_after();
-    MF_TL(2);
     uint32_t sr[kKT];
     {
       uint32_t (*s4)[32] = reinterpret_cast<uint32_t (*)[32]>(sr);
       tmem_ld32(tS, s4[0]); tmem_ld32(tS + 32, s4[1]); tmem_ld32(tS + 64, s4[2]); tmem_ld32(tS + 96, s4[3]);
       tmem_ld_wait();
     }
-    MF_TL(3);
     tc_fence_before();
     if (named_sync_or(1 + s, 128, *abort_flag)) break;
-    MF_TL(4);
     if (leader) {
       // the S buffer is free: start the next tile's scores right away
       if (t + 1 < p.n_kt) {
@@ -318,7 +301,6 @@ evo_fwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
       pump_k(g + 1);
     }
     if (officer_b) pump_b();
-    MF_TL(5);
     // ------------------------------------------------------------------ pass 1: base-2 logits, row max
     const int j0 = t * kKT;
     float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -357,7 +339,6 @@ evo_fwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
         }
       }
     }
-    MF_TL(6);
     const float m_new = fmaxf(fmaxf(m, fmaxf(mx4[0], mx4[1])), fmaxf(mx4[2], mx4[3]));
     const float corr = ex2f(m - m_new);
     // ------------------------------------------------------------------ fold O_tile(g-1), then P(g)
@@ -365,7 +346,6 @@ evo_fwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
       wait_or_flag(&bar.pv_done, (g - 1) & 1, abort_flag);
       fold();
     }
-    MF_TL(7);
     float rs4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int cb = 0; cb < 2; ++cb) {
@@ -382,12 +362,9 @@ evo_fwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
     l = fmaf(l, corr, (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]));
     m = m_new;
     corr_prev = corr;
-    MF_TL(8);
     tmem_st_wait();
     tc_fence_before();
-    MF_TL(9);
     if (named_sync_or(1 + s, 128, *abort_flag)) break;
-    MF_TL(10);
     if (leader) {
       wait_or_flag(&bar.v_full[g % kVS], (g / kVS) & 1, abort_flag);
       tc_fence_after();
@@ -395,7 +372,6 @@ evo_fwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
     }
     if (officer_kv) pump_v(g);          // P V(g-1) and earlier are known complete
     if (officer_b) pump_b();
-    MF_TL(11);
     if (++t == p.n_kt) {
       // ---------------------------------------------------------------- item done
       wait_or_flag(&bar.pv_done, g & 1, abort_flag);
@@ -414,7 +390,9 @@ evo_fwd_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
             *reinterpret_cast<uint4*>(orow + d8 * 8) = v;
           }
         }
-        p.lse[(((int64_t)b * p.N + n) * p.H + h) * p.L + i] = (m + lg2f(l)) * kLn2;
+        // a row whose keys are all masked keeps m = -FLT_MAX: its log-sum-exp is stored as -FLT_MAX, the value the
+        // backward kernels recognise
+        p.lse[(((int64_t)b * p.N + n) * p.H + h) * p.L + i] = m <= -1e38f ? -FLT_MAX : (m + lg2f(l)) * kLn2;
       }
       t = 0;
       ++item_local;
@@ -450,9 +428,6 @@ int launch_fwd(const mf_evo_fwd_args& a, cudaStream_t st) {
   p.mask_dtype = a.mask_dtype;
   p.o = a.o; p.lse = a.lse;
   p.status = status_word();
-#ifdef MF_TIMELINE
-  p.timeline = g_timeline;
-#endif
   MF_REQUIRE(p.status, MF_ERR_CUDA, "could not allocate the device status word");
   MF_REQUIRE(tc_async_status() == 0, MF_ERR_CUDA, "an earlier tensor-core kernel gave up on a bounded wait; results are invalid");
 
@@ -493,10 +468,6 @@ int launch_fwd(const mf_evo_fwd_args& a, cudaStream_t st) {
     case MF_F16: { using TB = __half; __VA_ARGS__; } break;                   \
     default: return fail(MF_ERR_BAD_ARG, "unknown bias dtype %d", (int)(dt)); \
   }
-
-#ifdef MF_TIMELINE
-extern "C" __attribute__((visibility("default"))) void mf_debug_set_timeline(long long* p) { g_timeline = p; }
-#endif
 
 int evo_fwd_tc(const mf_evo_fwd_args& a, cudaStream_t st) {
   int r = MF_OK;

@@ -12,8 +12,10 @@ Differences from the reference, all on purpose:
   * a boolean (or uint8) ``res_mask`` is a keep-mask with the semantics of the reference's PyTorch
     attention (``masked_fill(~mask, -finfo.max)``, megafold/model/attention.py:522-524); a floating
     ``res_mask`` is added to the logits, which is what the reference kernel does (evoattention.py:66);
-  * ``d_pair_bias`` is accumulated in fp32 in a fixed order (bit-reproducible) and returned in
-    ``pair_bias.dtype``; the reference rounds it to ``dO.dtype`` first (evoattention.py:903).
+  * ``d_pair_bias`` is accumulated in fp32 in a fixed order on every kernel path (bit-reproducible; the
+    reference adds rows with atomics, evoattention.py:465) and returned in ``pair_bias.dtype``; the reference
+    rounds it to ``dO.dtype`` first (evoattention.py:903).  ``dQ`` is bit-reproducible too unless the
+    tensor-core path has to sum partial rows with fp32 atomics (very few rows, or L > 768).
 """
 from __future__ import annotations
 

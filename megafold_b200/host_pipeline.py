@@ -42,7 +42,7 @@ def _row_spans(n_rows, chunks):
 class HostPipeline:
     """Reusable state (streams, device staging buffers, pinned outputs) for one problem shape."""
 
-    def __init__(self, shape, dtype, bias_shape, bias_dtype, device, chunks=4):
+    def __init__(self, shape, dtype, bias_shape, bias_dtype, device, chunks=4, mask_dtype=torch.bool):
         B, N, L, H, D = shape
         self.shape, self.dtype, self.device = tuple(shape), dtype, torch.device(device)
         self.spans = _row_spans(N, max(1, min(chunks, N)))
@@ -52,7 +52,7 @@ class HostPipeline:
         self.s_in, self.s_cmp, self.s_out = (torch.cuda.Stream(dev) for _ in range(3))
         mk = lambda: torch.empty((B, rows, L, H, D), dtype=dtype, device=dev)      # noqa: E731
         self.dev_in = [dict(q=mk(), k=mk(), v=mk(), d_out=mk(),
-                            mask=torch.empty((B, rows, 1, 1, L), dtype=torch.bool, device=dev)) for _ in range(2)]
+                            mask=torch.empty((B, rows, 1, 1, L), dtype=mask_dtype, device=dev)) for _ in range(2)]
         self.d_bias = torch.zeros(bias_shape, dtype=torch.float32, device=dev)
         self.bias = torch.empty(bias_shape, dtype=bias_dtype, device=dev)
         pin = lambda shp, dt: torch.empty(shp, dtype=dt, pin_memory=True)         # noqa: E731
@@ -65,12 +65,11 @@ class HostPipeline:
     def run(self, q, k, v, res_mask, pair_bias, d_out, group=None):
         """All arguments are pinned host tensors ([B,N,L,H,D], mask [B,N,1,1,L] bool, bias [B,1,H,L,L]).
         Returns the dict of pinned host results (valid after the call: it waits for the downloads).
+        The returned tensors are this object's own buffers: the next call overwrites them.
         With ``group`` the tensors hold this rank's rows and d_pair_bias is all-reduced over the group on the device
-        before it is downloaded (the schedule is then issued directly, not replayed from a graph)."""
+        before it is downloaded (the collective is part of the replayed graph; every rank must call in step)."""
         host = dict(q=q, k=k, v=v, d_out=d_out, mask=res_mask, bias=pair_bias)
         self.group = group
-        if group is not None:
-            self.use_graph = False
         key = tuple(t.data_ptr() for t in host.values())
         cur = torch.cuda.current_stream(self.device)
         if self.graph is not None and key == self.graph_key:
@@ -86,12 +85,19 @@ class HostPipeline:
                     self._schedule(host, self.s_cap)
                 self.graph, self.graph_key = g, key
                 cur.wait_stream(self.s_cap)
-                return self.run(q, k, v, res_mask, pair_bias, d_out)
             except Exception as e:                   # capture not possible here: keep the direct schedule
                 warnings.warn(f"CUDA graph capture of the host pipeline failed ({type(e).__name__}: {e}); issuing the schedule directly")
                 self.use_graph = False
                 self.graph = None
                 torch.cuda.synchronize(self.device)
+            if group is not None:                    # every rank replays, or none does
+                import torch.distributed as dist
+                ok = torch.tensor([1 if self.graph is not None else 0], device=self.device)
+                dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+                if not int(ok):
+                    self.graph, self.use_graph = None, False
+            if self.graph is not None:
+                return self.run(q, k, v, res_mask, pair_bias, d_out, group)
         self._schedule(host, cur)
         cur.synchronize()
         return self.out
@@ -151,7 +157,8 @@ _cache = {}
 def evoformer_fwd_bwd_host(q, k, v, res_mask, pair_bias, d_out, device="cuda", chunks=4, group=None):
     """Forward and backward of the pair-biased attention with pinned HOST operands and results.
 
-    Returns ``dict(o, dq, dk, dv, d_bias)`` of pinned host tensors; d_bias has ``pair_bias``'s dtype.  ``group``: a
+    Returns ``dict(o, dq, dk, dv, d_bias)`` of pinned host tensors (buffers owned by the pipeline: the next call with
+    the same shapes overwrites them); d_bias has ``pair_bias``'s dtype.  ``group``: a
     process group over which the rows are sharded (each rank passes its own rows; d_bias comes back summed)."""
     for t in (q, k, v, d_out, res_mask, pair_bias):
         if t.is_cuda:
@@ -159,9 +166,11 @@ def evoformer_fwd_bwd_host(q, k, v, res_mask, pair_bias, d_out, device="cuda", c
     dev = torch.device(device)
     if dev.index is None:
         dev = torch.device("cuda", torch.cuda.current_device())
-    key = (tuple(q.shape), q.dtype, tuple(pair_bias.shape), pair_bias.dtype, dev, chunks)
+    if res_mask.dtype not in (torch.bool, torch.uint8) and not res_mask.is_floating_point():
+        raise TypeError(f"res_mask must be bool / uint8 (keep-mask) or floating (additive), got {res_mask.dtype}")
+    key = (tuple(q.shape), q.dtype, tuple(pair_bias.shape), pair_bias.dtype, dev, chunks, res_mask.dtype)
     pipe = _cache.get(key)
     if pipe is None:
         _cache.clear()
-        pipe = _cache[key] = HostPipeline(q.shape, q.dtype, pair_bias.shape, pair_bias.dtype, dev, chunks)
+        pipe = _cache[key] = HostPipeline(q.shape, q.dtype, pair_bias.shape, pair_bias.dtype, dev, chunks, res_mask.dtype)
     return pipe.run(q, k, v, res_mask, pair_bias, d_out, group)

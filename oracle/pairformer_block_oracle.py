@@ -50,13 +50,14 @@ def block(pair, single, mask, params):
     return x, s
 
 
-def params_of(module):
-    """The parameter dictionaries of a ``megafold_b200.pairformer_block.PairformerBlock`` as fp32 CPU leaf tensors."""
+def params_of(module, device="cpu"):
+    """The parameter dictionaries of a ``megafold_b200.pairformer_block.PairformerBlock`` as fp32 leaf tensors on
+    ``device`` (the fp32 block is evaluated on the GPU for the benchmark-sized test, on the host otherwise)."""
     def attn(a):
-        d = {k: getattr(a, k).detach().float().cpu().clone().requires_grad_(True)
+        d = {k: getattr(a, k).detach().float().to(device).clone().requires_grad_(True)
              for k in ("ln_w", "ln_b", "w_qkvg", "b_qkvg", "pair_ln_w", "pair_ln_b", "w_pair_bias", "w_out")}
         d["heads"], d["dim_head"] = a.heads, a.dim_head
         return d
-    tr = {k: getattr(module, "tr_" + k).detach().float().cpu().clone().requires_grad_(True) for k in ("ln_w", "ln_b", "w1", "w2")}
+    tr = {k: getattr(module, "tr_" + k).detach().float().to(device).clone().requires_grad_(True) for k in ("ln_w", "ln_b", "w1", "w2")}
     return {"tri_start": attn(module.tri_start), "tri_end": attn(module.tri_end), "single_attn": attn(module.single_attn),
             "transition": tr}

@@ -11,6 +11,13 @@ from megafold_b200 import _lib
 from oracle import pairformer_oracle as orc
 from util import assert_close_fp32, assert_close_lowp
 
+# gradients that are sums over the M rows: their absolute floor grows like sqrt(M) (see util.assert_close_lowp)
+SUMMED = {"dw", "db", "d_ln_w", "d_ln_b", "dw1", "dw2"}
+
+
+def lowp(g_, r_, n, M):
+    assert_close_lowp(g_, r_, n, summed_over=M if n.split()[0] in SUMMED else 1)
+
 pytestmark = pytest.mark.gpu
 G = os.path.join(os.path.dirname(__file__), "golden")
 DEV = "cuda"
@@ -80,7 +87,7 @@ def test_lnl_bf16_against_fp32_oracle(M, N, K):
     r = [t.to(torch.bfloat16).float() for t in (x, ln_w, ln_b, w, b, dy)]
     ref = orc.layernorm_linear_fwd_bwd(*r)
     for g_, r_, n in zip(got, ref, LNL_NAMES):
-        assert_close_lowp(g_, r_, n)
+        lowp(g_, r_, n, M)
 
 
 def test_swiglu_fp32_and_bf16():
@@ -172,7 +179,7 @@ def test_transition_bf16_against_fp32_oracle(M, dim, ef):
     r = [t.to(torch.bfloat16).float() for t in (x, ln_w, ln_b, w1, w2, dy)]
     ref = orc.transition_fwd_bwd(*r)
     for g_, r_, n in zip(got, ref, T_NAMES):
-        assert_close_lowp(g_, r_, n)
+        lowp(g_, r_, n, M)
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
@@ -187,11 +194,11 @@ def test_lnl_backward_tensor_core_path(M, N, K, dtype):
     ref = orc.layernorm_linear_fwd_bwd(*[t.float().cpu() for t in (x, ln_w, ln_b, w, b, dy)])
     _, dx, dlw, dlb, dw, db = ref
     for g_, r_, n in zip(got, (dx, dw, db, dlw, dlb), ("dx", "dw", "db", "d_ln_w", "d_ln_b")):
-        assert_close_lowp(g_, r_, n)
+        lowp(g_, r_, n, M)
     simt = mfb.layernorm_linear_backward(dy, x, w, ln_w, ln_b, mean, rstd, True, flags=_lib.MF_FLAG_FORCE_SIMT)
     assert _lib.last_path() == "simt"
     for g_, r_, n in zip(got, simt, ("dx", "dw", "db", "d_ln_w", "d_ln_b")):
-        assert_close_lowp(g_, r_.float(), n + " vs CUDA cores")
+        lowp(g_, r_.float(), n + " vs CUDA cores", M)
 
 
 @pytest.mark.parametrize("M,dim,ef,dtype", [(12000, 128, 4, torch.bfloat16), (777, 64, 2, torch.bfloat16),
@@ -206,4 +213,4 @@ def test_transition_backward_tensor_core_path(M, dim, ef, dtype):
     assert _lib.last_path() == "tcgen05"
     ref = orc.transition_fwd_bwd(*[t.float().cpu() for t in (x, ln_w, ln_b, w1, w2, dy)])
     for g_, r_, n in zip(got, ref[1:], ("dx", "d_ln_w", "d_ln_b", "dw1", "dw2")):
-        assert_close_lowp(g_, r_, n)
+        lowp(g_, r_, n, M)

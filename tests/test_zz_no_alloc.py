@@ -56,6 +56,13 @@ def test_noalloc_backward_matches_regular_entry_point_twice():
         o, lse = mfb.evo_attention_forward(q, k, v, mask, bias, flags=_lib.MF_FLAG_FORCE_SIMT)
         ref = _backward(L_.mf_evo_bwd, q, k, v, mask, bias, d_o, o, lse, with_workspace=True)
         got = _backward(L_.mf_evo_bwd_noalloc, q, k, v, mask, bias, d_o, o, lse, with_workspace=False)
+        # against the fp32 oracle on the inputs as stored (bf16), at the tolerance of the other low-precision tests
+        from oracle import pairformer_oracle as orc
+        f = lambda t: t.float().cpu()      # noqa: E731
+        oracle = orc.evo_attention_fwd_bwd(f(q), f(k), f(v), mask.cpu(), f(bias), f(d_o))
+        for name, g_, r_ in zip(("dq", "dk", "dv", "dbias"), got, oracle[1:]):
+            torch.testing.assert_close(g_.float().cpu(), r_, rtol=2e-2, atol=2e-2 * (3 ** 0.5 if name == "dbias" else 1.0),
+                                       msg=lambda m: f"seed {seed} {name} vs oracle: {m}")
         for name, g_, r_ in zip(("dq", "dk", "dv", "dbias"), got, ref):
             # same kernels, same summation order: 2e-2 is the bf16 tolerance of the other tests, equality is expected
             torch.testing.assert_close(g_.float(), r_.float(), rtol=2e-2, atol=2e-2, msg=lambda m: f"seed {seed} {name}: {m}")
