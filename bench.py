@@ -11,7 +11,11 @@ all-reduced over NCCL inside the timed region ("weak" scaling: per-GPU work is f
 
 Prints ONE JSON line (rank 0).  `value` is algorithmic TFLOP/s (14*B*N*H*L^2*D per step) of the whole
 job with inputs resident in HBM; `e2e` is the same metric through the public operator with pinned
-HOST buffers, host<->device copies inside the timed region.  `--impl reference` times the
+HOST buffers, host<->device copies inside the timed region.  Each of the K timed steps repeats the
+forward + backward pass often enough for the timed region to last about a second (`config.inner_repeats`;
+`ms_per_step` stays the time of ONE pass), so that the clocks are those of sustained load.
+`config.strong_L768` is the strong-scaling case (768 rows of L = 768 split over the ranks) and
+`config.block_L768_ms` the long-crop block, both measured in the same run.  `--impl reference` times the
 reference's PyTorch path (restated in oracle/) on the host cores on a bounded sample of the rows.
 """
 from __future__ import annotations
@@ -34,9 +38,16 @@ L, H, D, ROWS = 384, 4, 32, 384
 METRIC, UNIT = "triangle_attention_fwd_bwd_throughput", "TFLOP/s"
 
 
-# DRAM bytes per launch (read + write) of evo_fwd_tc_kernel / evo_bwd_tc_kernel at 384 rows, L = 384, H = 4, D = 32, bf16:
-# one ncu --set full capture each, summarised under profiles/ in the files named for these kernels
-NCU_DRAM_BYTES = {"forward": 140071168 + 21487872, "backward": 160271104 + 76499456}
+def profiled_dram_bytes(kernel):
+    """dram__bytes_read.sum + dram__bytes_write.sum of one launch of `kernel` at the benchmark size, parsed from the
+    ncu summary committed under profiles/ (None when there is none): measured by ncu, not in this run."""
+    import glob
+    import re
+    for path in sorted(glob.glob(os.path.join(ROOT, "profiles", f"{kernel}_cfg2_L384.md"))):
+        m = re.search(r"dram__bytes_read\.sum \+ dram__bytes_write\.sum\D+([0-9.]+)\s*MB", open(path).read())
+        if m:
+            return float(m.group(1)) * 1e6
+    return None
 
 
 def flops_per_step(rows):
@@ -153,6 +164,7 @@ def run_ours(args):
     import torch.distributed as dist
     import megafold_b200 as mfb
     from megafold_b200 import _lib, workloads
+    from megafold_b200.sharded import evo_attention_backward_sharded, row_shard
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -163,18 +175,17 @@ def run_ours(args):
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    group = None
 
     host = workloads.triangle_attention(L=L, N=ROWS, H=H, D=D, seed=rank)      # the metric's workload: always 384 rows per GPU
     host["bias"] = workloads.triangle_attention(L=L, N=1, H=H, D=D, seed=0)["bias"]     # shared by all ranks
     pinned = {k: v.pin_memory() for k, v in host.items()}
     c = {k: v.to(dev) for k, v in host.items()}
 
-    def step_resident():
-        o, lse = mfb.evo_attention_forward(c["q"], c["k"], c["v"], c["mask"], c["bias"])
-        dq, dk, dv, db = mfb.evo_attention_backward(c["d_out"], c["q"], c["k"], c["v"], c["mask"], c["bias"], o, lse)
-        if world > 1:
-            dist.all_reduce(db, group=group)
+    def fwd_bwd(t):
+        """One pass on device-resident tensors; with several ranks dBias is all-reduced on a side stream while dQ / dK / dV
+        are computed (the collective is inside the timed region)."""
+        o, lse = mfb.evo_attention_forward(t["q"], t["k"], t["v"], t["mask"], t["bias"])
+        dq, dk, dv, db = evo_attention_backward_sharded(t["d_out"], t["q"], t["k"], t["v"], t["mask"], t["bias"], o, lse)
         return o, dq, dk, dv, db
 
     out_host = None
@@ -187,7 +198,8 @@ def run_ours(args):
         out_host = list(out.values())
         return out
 
-    def timed(fn, steps, warmup, sampler=None):
+    def timed(fn, steps, warmup, sampler=None, inner=1):
+        """`steps` timed steps of `inner` calls each, CUDA events on the launching stream, max over ranks; ms per call."""
         for _ in range(warmup):
             fn()
         torch.cuda.synchronize()
@@ -198,23 +210,26 @@ def run_ours(args):
         ctx = sampler if sampler is not None else _Null()
         with ctx:
             e0.record()
-            for _ in range(steps):
+            for _ in range(steps * inner):
                 fn()
             e1.record()
             torch.cuda.synchronize()
             if world > 1:
                 dist.barrier()
-        ms = e0.elapsed_time(e1) / steps
+        ms = e0.elapsed_time(e1) / (steps * inner)
         if world > 1:
             t = torch.tensor([ms], device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = float(t.item())
         return ms
 
+    # how many passes per step make the timed region last about a second (same number on every rank)
+    probe_ms = timed(lambda: fwd_bwd(c), 5, 3)
+    inner = max(1, min(400, int(round(1000.0 / (args.steps * probe_ms)))))
     sampler = ClockSampler(local) if rank == 0 else None
     launches0 = _lib.launch_count()
-    ms = timed(step_resident, args.steps, args.warmup, sampler)
-    launches = (_lib.launch_count() - launches0) // (args.steps + args.warmup) * args.steps
+    ms = timed(lambda: fwd_bwd(c), args.steps, args.warmup, sampler, inner)
+    launches = (_lib.launch_count() - launches0) * args.steps * inner // (args.steps * inner + args.warmup)
     path_bwd = _lib.last_path()
     status = _lib.lib().mf_async_status()
     ms_e2e = timed(step_e2e, max(2, min(args.steps, 5)), 2)
@@ -222,9 +237,28 @@ def run_ours(args):
     # per-kernel-family timing on the launching stream: forward call and backward call separately
     o, lse = mfb.evo_attention_forward(c["q"], c["k"], c["v"], c["mask"], c["bias"])
     path_fwd = _lib.last_path()
-    ms_fwd = timed(lambda: mfb.evo_attention_forward(c["q"], c["k"], c["v"], c["mask"], c["bias"]), args.steps, 2)
+    ms_fwd = timed(lambda: mfb.evo_attention_forward(c["q"], c["k"], c["v"], c["mask"], c["bias"]), args.steps, 3, None, inner)
     ms_bwd = timed(lambda: mfb.evo_attention_backward(c["d_out"], c["q"], c["k"], c["v"], c["mask"], c["bias"], o, lse),
-                   args.steps, 2)
+                   args.steps, 3, None, inner)
+    del o, lse
+
+    # strong scaling: 768 rows of L = 768 (H 4, D 32) split over the ranks, dBias all-reduced
+    L2 = 768
+    a, b = row_shard(L2, rank, world)
+    big = workloads.triangle_attention(L=L2, N=L2, H=H, D=D, pad=38, seed=1)
+    s = {k: (v[:, a:b].to(dev) if k != "bias" else v.to(dev)) for k, v in big.items()}
+    del big
+    ms_strong = timed(lambda: fwd_bwd(s), 5, 3)
+    strong = {"ms": ms_strong, "tflops": 14.0 * L2 * H * L2 * L2 * D / (ms_strong * 1e-3) / 1e12, "rows_per_gpu": b - a,
+              "note": "triangle attention fwd+bwd, N = L = 768, H = 4, D = 32, rows split over the ranks, dBias all-reduce inside"}
+    del s
+    torch.cuda.empty_cache()
+    # the long-crop block (benchmark configuration 5) at L = 768, rows sharded the same way
+    ms_block = block_bench(dev, 768, group=dist.group.WORLD if world > 1 else None)
+    if world > 1:
+        t = torch.tensor([ms_block], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_block = float(t.item())
 
     if rank != 0:
         if world > 1:
@@ -236,39 +270,70 @@ def run_ours(args):
     e2e_value = flops_per_step(total_rows) / (ms_e2e * 1e-3) / 1e12
     h2d = sum(v.numel() * v.element_size() for v in pinned.values())
     d2h = sum(t.numel() * t.element_size() for t in out_host)
-    # dominant kernel family = the slower of the two calls; the roofline that bounds it: the tensor pipe
+    clocks = sampler.summary() if sampler else None
+    # dominant kernel family = the slower of the two calls; the roofline that bounds it: the tensor pipe by the
+    # benchmark's FLOP convention.  The timed region lasts about a second, so the sustained peak is the denominator.
     dom = "backward" if ms_bwd >= ms_fwd else "forward"
     dom_ms = max(ms_bwd, ms_fwd)
     dom_flops = (10.0 if dom == "backward" else 4.0) * ROWS * H * L * L * D
     achieved = dom_flops / (dom_ms * 1e-3) / 1e12
+    peak = peaks["tflops_sustained"] or peaks["tflops"]
     cfg = {"workload": "cfg2_triangle_L384", "B": 1, "rows_per_gpu": ROWS, "L": L, "H": H, "D": D,
-           "pad_tokens": 32, "l2": "inputs+outputs of one step (~490 MB) exceed the 126 MB L2",
-           "parallelism": f"rows sharded over {world} GPU(s); dBias all-reduced (NCCL)" if world > 1 else "single GPU",
+           "pad_tokens": 32, "l2": "inputs+outputs of one pass (~490 MB) exceed the 126 MB L2",
+           "inner_repeats": inner, "timed_region_s": ms * args.steps * inner * 1e-3,
+           "parallelism": f"rows sharded over {world} GPU(s); dBias all-reduced (NCCL) on a side stream while dQ/dK/dV are computed" if world > 1 else "single GPU",
            "kernel_path": {"forward": path_fwd, "backward": path_bwd}, "ms_forward": ms_fwd, "ms_backward": ms_bwd,
+           "ms_times_sm_mhz": (ms * clocks["sm_mhz"] if clocks and clocks.get("sm_mhz") else None),
            "hbm_gbs_algorithmic": algorithmic_bytes(ROWS) / (ms * 1e-3) / 1e9, "peaks": peaks["src"],
+           "strong_L768": strong, "block_L768_ms": ms_block, "block_L768_tflops": block_flops(768) / (ms_block * 1e-3) / 1e12,
            "async_status": status}
+    kern = "evo_bwd_ws_kernel" if dom == "backward" else "evo_fwd_ws_kernel"
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic", "config": cfg,
-        "clocks": sampler.summary() if sampler else None,
+        "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": int(launches),
-        "roofline": {"bound": "tensor", "kernel": f"attention {dom} ({path_bwd if dom == 'backward' else path_fwd})",
-                     "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["tflops"],
-                     # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the main kernel of that call at this
-                     # size, from the ncu captures summarised under profiles/ (not measured in this run)
-                     "traffic": (NCU_DRAM_BYTES[dom] if ROWS == 384 else None), "traffic_unit": "bytes per launch",
-                     "peak_source": peaks["src"] + " bf16 burst"},
+        "roofline": {"bound": "tensor", "kernel": f"attention {dom} call ({path_bwd if dom == 'backward' else path_fwd}); largest kernel {kern}",
+                     "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                     # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the call's largest kernel at this size,
+                     # from the ncu capture summarised under profiles/ (measured by ncu, not in this run)
+                     "traffic": (profiled_dram_bytes(kern) if ROWS == 384 else None), "traffic_unit": "bytes per launch",
+                     "peak_source": peaks["src"] + " bf16 sustained (the timed region lasts ~1 s)"},
         "cpu_baseline": cpu_baseline() if world == 1 else None,
     }
     if world == 1 and not args.no_extras:
+        line["parity"] = parity_cfg2(c, dev)
         del c
         torch.cuda.empty_cache()
         line["extras"] = extras(dev)
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def parity_cfg2(c, dev):
+    """Largest absolute / relative error of every output of the benchmark pass against the fp32 oracle evaluated on the
+    GPU (TF32 off) on the same bf16 inputs: the oracle is the checker here, nothing of it is timed."""
+    import megafold_b200 as mfb
+    from oracle import pairformer_oracle as orc
+    tf32 = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        o, lse = mfb.evo_attention_forward(c["q"], c["k"], c["v"], c["mask"], c["bias"])
+        got = (o,) + tuple(mfb.evo_attention_backward(c["d_out"], c["q"], c["k"], c["v"], c["mask"], c["bias"], o, lse))
+        ref = orc.evo_attention_fwd_bwd(c["q"].float(), c["k"].float(), c["v"].float(), c["mask"], c["bias"].float(), c["d_out"].float())
+        out = {"tolerance": "rtol = atol = 2e-2 (atol x sqrt(384) for d_pair_bias, a sum over the 384 rows)"}
+        for n, g_, r_ in zip(("o", "dq", "dk", "dv", "d_pair_bias"), got, ref):
+            err = (g_.float() - r_).abs()
+            big = r_.abs() > 0.1 * r_.abs().max()
+            atol = 2e-2 * (384 ** 0.5 if n == "d_pair_bias" else 1.0)
+            out[n] = {"max_abs_err": float(err.max()), "max_rel_err_large": float((err[big] / r_.abs()[big]).max()),
+                      "within_tolerance": bool((err <= atol + 2e-2 * r_.abs()).all())}
+        return out
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = tf32
 
 
 def _time_cuda(fn, steps, warmup):
@@ -343,6 +408,18 @@ def extras(dev, steps=5):
     from megafold_b200.fused_transition import transition_backward, transition_forward
     peaks = measured_peaks()
     out = {}
+    # same-box comparator: the reference's PyTorch attention path (oracle restatement) in bf16 on this GPU, torch eager
+    try:
+        from oracle import pairformer_oracle as orc
+        c = {k: v.to(dev) for k, v in workloads.triangle_attention().items()}
+        eager = lambda: orc.evo_attention_fwd_bwd(c["q"], c["k"], c["v"], c["mask"], c["bias"], c["d_out"], compute_dtype=torch.bfloat16)  # noqa: E731
+        ms_e = _time_cuda(eager, 3, 2)
+        out["torch_eager_gpu_cfg2"] = {"ms_fwd_bwd": ms_e, "tflops": flops_per_step(ROWS) / (ms_e * 1e-3) / 1e12,
+                                       "note": "PyTorch eager bf16 on the same GPU: einsum, masked_fill, softmax, einsum + autograd"}
+        del c
+        torch.cuda.empty_cache()
+    except Exception as e:      # noqa: BLE001
+        out["torch_eager_gpu_cfg2"] = {"error": f"{type(e).__name__}: {e}"}
     # config 3: single-representation attention with pair bias, D = 24
     c = {k: v.to(dev) for k, v in workloads.single_attention().items()}
     o, lse = mfb.evo_attention_forward(c["q"], c["k"], c["v"], c["mask"], c["bias"])
@@ -393,11 +470,6 @@ def extras(dev, steps=5):
         "note": "forward keeps the hidden activation on chip; backward recomputes it (workspace counted in the peak)"}
     del c, y, mean, rstd
     torch.cuda.empty_cache()
-    # config 5 on one GPU: the whole block at L = 768
-    ms_blk = block_bench(dev, 768)
-    out["cfg5_pairformer_block_L768_1gpu"] = {
-        "ms_fwd_bwd": ms_blk, "tflops": block_flops(768) / (ms_blk * 1e-3) / 1e12, "cuda_graph": bool(getattr(block_bench, "graphed", False)),
-        "note": "fused operators + torch glue (gating, output projections, residuals); rows shard over ranks with --only block"}
     return out
 
 

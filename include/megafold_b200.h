@@ -25,7 +25,7 @@
 extern "C" {
 #endif
 
-#define MF_ABI_VERSION 1
+#define MF_ABI_VERSION 2
 
 #if defined(__GNUC__)
 #define MF_API __attribute__((visibility("default")))
@@ -112,6 +112,10 @@ typedef struct mf_evo_bwd_args {
   void* dq; void* dk; void* dv;
   void* d_bias;
   void* workspace; size_t workspace_bytes;
+  /* Optional cudaEvent_t (NULL = none), recorded on `stream` as soon as d_bias is final.  The tensor-core path
+   * computes d_bias first, so a caller that shards the rows over GPUs can all-reduce d_bias on another stream
+   * while dq / dk / dv are still being computed; on the CUDA-core path the event is recorded at the end. */
+  void* dbias_ready_event;
 } mf_evo_bwd_args;
 
 MF_API size_t mf_evo_bwd_workspace_bytes(const mf_evo_bwd_args* args);

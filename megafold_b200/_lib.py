@@ -42,7 +42,8 @@ class EvoBwdArgs(C.Structure):
                 ("bias", _vp), ("bias_strides", _i64 * 4),
                 ("o", _vp), ("d_o", _vp), ("lse", _vp),
                 ("dq", _vp), ("dk", _vp), ("dv", _vp), ("d_bias", _vp),
-                ("workspace", _vp), ("workspace_bytes", _sz)]
+                ("workspace", _vp), ("workspace_bytes", _sz),
+                ("dbias_ready_event", _vp)]
 
 
 class LnlFwdArgs(C.Structure):

@@ -101,6 +101,7 @@ int mf_evo_bwd(const mf_evo_bwd_args* args, void* stream) {
     return r;
   }
   r = evo_bwd_simt(a, st);
+  if (r == MF_OK && a.dbias_ready_event) MF_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(a.dbias_ready_event), st));
   if (r == MF_OK) set_last_path("simt");
   return r;
 }
@@ -115,6 +116,8 @@ int mf_evo_bwd_noalloc(const mf_evo_bwd_args* args, void* stream) {
              "d_bias dtype must be fp32 or the q/k/v dtype");
   r = check_device(); if (r) return r;
   r = evo_bwd_simt_noalloc(a, static_cast<cudaStream_t>(stream));
+  if (r == MF_OK && a.dbias_ready_event)
+    MF_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(a.dbias_ready_event), static_cast<cudaStream_t>(stream)));
   if (r == MF_OK) set_last_path("simt");
   return r;
 }

@@ -960,6 +960,38 @@ int launch_bwd_ws(const mf_evo_bwd_args& a, cudaStream_t st) {
 
   float alpha[2];
   const int n_alpha = split_alpha(a.D, bt_dtype, alpha);
+  // ---- dBias first: a caller that all-reduces it over row shards can start while dQ / dK / dV are computed
+  {
+    DbP p{};
+    p.B = a.B; p.N = a.N; p.L = a.L; p.H = a.H; p.D = a.D;
+    p.n_t = pl.nt; p.lpad = lpad; p.nsplit = pl.nsplit;
+    p.n_units = a.B * a.H * pl.nt * pl.nt * pl.nsplit;
+    p.c1 = kLog2e / sqrtf((float)a.D);
+    p.fmt = a.dtype == MF_BF16 ? 1u : 0u; p.bfmt = bt_dtype == MF_BF16 ? 1u : 0u;
+    p.n_alpha = n_alpha; p.alpha[0] = alpha[0]; p.alpha[1] = alpha[1];
+    p.bias_b_mul = 1;
+    p.mask = a.mask; for (int i = 0; i < 3; ++i) p.ms[i] = a.mask_strides[i];
+    p.mask_dtype = a.mask_dtype;
+    p.stats = stats;
+    p.part = part;
+    p.status = status;
+    const size_t smem = 1024 + 2 * (size_t)kAtomB + 12 * kTileB + 2048 + 3 * 256 * sizeof(float);
+    int grid = sm_count();
+    if (grid > p.n_units) grid = p.n_units;
+    auto kern = evo_dbias_ws_kernel<T, TT>;
+    MF_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kern<<<grid, kThreads, smem, st>>>(mq, mk, mv, mg, mbt, p MF_TRACE_ARG);
+    MF_LAUNCHED("evo_dbias_ws_kernel");
+    if (!pl.part_direct) {
+      const int64_t n_out = (int64_t)a.B * a.H * a.L * a.L;
+      if (a.dbias_dtype == MF_F32)
+        dbias_finish_kernel<float><<<(unsigned)((n_out + 255) / 256), 256, 0, st>>>(part, static_cast<float*>(a.d_bias), n_out, pl.nsplit);
+      else
+        dbias_finish_kernel<T><<<(unsigned)((n_out + 255) / 256), 256, 0, st>>>(part, static_cast<T*>(a.d_bias), n_out, pl.nsplit);
+      MF_LAUNCHED("dbias_finish_kernel");
+    }
+  }
+  if (a.dbias_ready_event) MF_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(a.dbias_ready_event), st));
   // ---- dQ, dK, dV
   {
     BwdWsP p{};
@@ -993,37 +1025,6 @@ int launch_bwd_ws(const mf_evo_bwd_args& a, cudaStream_t st) {
   if (pl.dq_fp32) {
     cast_rows_ws_kernel<T><<<(unsigned)((n_dq + 255) / 256), 256, 0, st>>>(dq_acc, static_cast<T*>(a.dq), n_dq);
     MF_LAUNCHED("cast_rows_ws_kernel");
-  }
-  // ---- dBias
-  {
-    DbP p{};
-    p.B = a.B; p.N = a.N; p.L = a.L; p.H = a.H; p.D = a.D;
-    p.n_t = pl.nt; p.lpad = lpad; p.nsplit = pl.nsplit;
-    p.n_units = a.B * a.H * pl.nt * pl.nt * pl.nsplit;
-    p.c1 = kLog2e / sqrtf((float)a.D);
-    p.fmt = a.dtype == MF_BF16 ? 1u : 0u; p.bfmt = bt_dtype == MF_BF16 ? 1u : 0u;
-    p.n_alpha = n_alpha; p.alpha[0] = alpha[0]; p.alpha[1] = alpha[1];
-    p.bias_b_mul = 1;
-    p.mask = a.mask; for (int i = 0; i < 3; ++i) p.ms[i] = a.mask_strides[i];
-    p.mask_dtype = a.mask_dtype;
-    p.stats = stats;
-    p.part = part;
-    p.status = status;
-    const size_t smem = 1024 + 2 * (size_t)kAtomB + 12 * kTileB + 2048 + 3 * 256 * sizeof(float);
-    int grid = sm_count();
-    if (grid > p.n_units) grid = p.n_units;
-    auto kern = evo_dbias_ws_kernel<T, TT>;
-    MF_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<grid, kThreads, smem, st>>>(mq, mk, mv, mg, mbt, p MF_TRACE_ARG);
-    MF_LAUNCHED("evo_dbias_ws_kernel");
-    if (!pl.part_direct) {
-      const int64_t n_out = (int64_t)a.B * a.H * a.L * a.L;
-      if (a.dbias_dtype == MF_F32)
-        dbias_finish_kernel<float><<<(unsigned)((n_out + 255) / 256), 256, 0, st>>>(part, static_cast<float*>(a.d_bias), n_out, pl.nsplit);
-      else
-        dbias_finish_kernel<T><<<(unsigned)((n_out + 255) / 256), 256, 0, st>>>(part, static_cast<T*>(a.d_bias), n_out, pl.nsplit);
-      MF_LAUNCHED("dbias_finish_kernel");
-    }
   }
   return MF_OK;
 }

@@ -79,8 +79,11 @@ def evo_attention_forward(q, k, v, res_mask, pair_bias, flags: int = 0):
     return o, lse
 
 
-def evo_attention_backward(d_o, q, k, v, res_mask, pair_bias, o, lse, flags: int = 0):
-    """Returns ``(dQ, dK, dV, dBias)``; dBias has ``pair_bias``'s shape and dtype. ``mf_evo_bwd``."""
+def evo_attention_backward(d_o, q, k, v, res_mask, pair_bias, o, lse, flags: int = 0, dbias_ready=None):
+    """Returns ``(dQ, dK, dV, dBias)``; dBias has ``pair_bias``'s shape and dtype. ``mf_evo_bwd``.
+
+    ``dbias_ready``: an optional ``torch.cuda.Event`` that the library records on the current stream as soon as dBias is
+    final (before dQ / dK / dV on the tensor-core path), for callers that reduce dBias over row shards on another stream."""
     _lib.require_cuda(d_o, q, k, v, res_mask, pair_bias, o, lse)
     B, N, L, H, D = _check_shapes(q, k, v, res_mask, pair_bias)
     d_o = d_o.contiguous()
@@ -96,6 +99,9 @@ def evo_attention_backward(d_o, q, k, v, res_mask, pair_bias, o, lse, flags: int
     a.dq, a.dk, a.dv, a.d_bias = dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), d_bias.data_ptr()
     L_ = _lib.lib()
     with torch.cuda.device(q.device):
+        if dbias_ready is not None:
+            dbias_ready.record()                     # creates the underlying cudaEvent_t; the library records it again
+            a.dbias_ready_event = dbias_ready.cuda_event
         need = L_.mf_evo_bwd_workspace_bytes(C.byref(a))
         ws = _lib.workspace(need, q.device)
         a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()

@@ -12,7 +12,7 @@ from __future__ import annotations
 import torch
 import torch.distributed as dist
 
-__all__ = ["AllReduceGradient", "row_shard", "sharded_evoformer"]
+__all__ = ["AllReduceGradient", "ShardedEvoformerAttention", "evo_attention_backward_sharded", "row_shard", "sharded_evoformer"]
 
 
 class AllReduceGradient(torch.autograd.Function):
@@ -31,6 +31,59 @@ class AllReduceGradient(torch.autograd.Function):
         return g, None
 
 
+def evo_attention_backward_sharded(d_o, q, k, v, res_mask, pair_bias, o, lse, group=None):
+    """Backward of the attention on this rank's rows with the all-reduce of d_pair_bias overlapped: the library computes
+    d_pair_bias first and signals an event; the collective then runs on a side stream while dQ / dK / dV are computed on
+    the current one, which waits for the collective at the end.  Returns ``(dQ, dK, dV, dBias)`` with dBias summed over
+    the group."""
+    from .evoattention import evo_attention_backward
+    if not (dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1):
+        return evo_attention_backward(d_o, q, k, v, res_mask, pair_bias, o, lse)
+    dev = q.device
+    cur = torch.cuda.current_stream(dev)
+    side = _side_stream(dev)
+    ready = torch.cuda.Event()
+    dq, dk, dv, db = evo_attention_backward(d_o, q, k, v, res_mask, pair_bias, o, lse, dbias_ready=ready)
+    if pair_bias.shape[0] != q.shape[0] or pair_bias.dtype not in (torch.float32, q.dtype):
+        side.wait_stream(cur)        # dBias was post-processed on the current stream (batch broadcast / dtype change)
+    else:
+        side.wait_event(ready)
+    with torch.cuda.stream(side):
+        db.record_stream(side)
+        dist.all_reduce(db, op=dist.ReduceOp.SUM, group=group)
+    cur.wait_stream(side)
+    return dq, dk, dv, db
+
+
+_side_streams = {}
+
+
+def _side_stream(dev):
+    s = _side_streams.get(dev)
+    if s is None:
+        s = _side_streams[dev] = torch.cuda.Stream(dev)
+    return s
+
+
+class ShardedEvoformerAttention(torch.autograd.Function):
+    """``EvoformerAttention`` on this rank's rows; the gradient of the replicated ``pair_bias`` comes back summed over the
+    group, the collective hidden behind the dQ / dK / dV kernels (see ``evo_attention_backward_sharded``)."""
+
+    @staticmethod
+    def forward(ctx, Q, K, V, res_mask, pair_bias, group=None):
+        from .evoattention import evo_attention_forward
+        o, lse = evo_attention_forward(Q, K, V, res_mask, pair_bias)
+        ctx.save_for_backward(Q, K, V, res_mask, pair_bias, o, lse)
+        ctx.group = group
+        return o
+
+    @staticmethod
+    def backward(ctx, dO):
+        Q, K, V, res_mask, pair_bias, o, lse = ctx.saved_tensors
+        dq, dk, dv, d_bias = evo_attention_backward_sharded(dO.contiguous(), Q, K, V, res_mask, pair_bias, o, lse, ctx.group)
+        return dq, dk, dv, None, d_bias, None
+
+
 def row_shard(n_rows: int, rank: int, world: int):
     """Contiguous block ``[start, stop)`` of the N rows owned by ``rank`` (the first ``n_rows % world``
     ranks get one extra row)."""
@@ -45,5 +98,5 @@ def sharded_evoformer(q, k, v, res_mask, pair_bias, group=None, attention=None):
     """``TritonEvoformer`` on this rank's rows; ``pair_bias`` is replicated and receives the
     all-reduced gradient.  ``attention`` defaults to the CUDA operator (the CPU tests pass an oracle)."""
     if attention is None:
-        from .evoattention import TritonEvoformer as attention
+        return ShardedEvoformerAttention.apply(q, k, v, res_mask, pair_bias, group)
     return attention(q, k, v, res_mask, AllReduceGradient.apply(pair_bias, group))

@@ -27,7 +27,7 @@ def test_header_symbols_all_bound_and_exported():
 
 def test_version_and_error_string():
     L = _lib.lib()
-    assert L.mf_version() == 1
+    assert L.mf_version() == 2
     assert isinstance(L.mf_last_error_string(), bytes)
 
 
