@@ -261,8 +261,7 @@ def run_ours(args):
         ms_block = float(t.item())
 
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
+        _teardown(world)
         return
     peaks = measured_peaks()
     total_rows = ROWS * world
@@ -308,9 +307,26 @@ def run_ours(args):
         del c
         torch.cuda.empty_cache()
         line["extras"] = extras(dev)
-    print(json.dumps(line))
-    if world > 1:
-        dist.destroy_process_group()
+    print(json.dumps(line), flush=True)
+    _teardown(world)
+
+
+def _teardown(world):
+    """Leave the process group in an orderly way: CUDA graphs that captured NCCL collectives (host pipeline, block) must
+    be gone before the communicator is destroyed.  A timer ends the process if the teardown itself blocks."""
+    if world <= 1:
+        return
+    import gc
+    from megafold_b200 import host_pipeline
+    timer = threading.Timer(60.0, lambda: os._exit(0))
+    timer.daemon = True
+    timer.start()
+    host_pipeline._cache.clear()
+    gc.collect()
+    torch.cuda.synchronize()
+    dist.barrier()
+    dist.destroy_process_group()
+    timer.cancel()
 
 
 def parity_cfg2(c, dev):
@@ -386,8 +402,7 @@ def run_only(args):
             print(json.dumps({"workload": f"cfg5_pairformer_block_L{args.L}", "n_gpus": world, "scaling": "strong",
                               "ms_fwd_bwd": ms, "tflops": block_flops(args.L) / (ms * 1e-3) / 1e12,
                               "cuda_graph": bool(getattr(block_bench, "graphed", False))}))
-        if world > 1:
-            dist.destroy_process_group()
+        _teardown(world)
         return
     else:
         c = {k: v.to(dev) for k, v in workloads.transition(M=args.rows * L).items()}
