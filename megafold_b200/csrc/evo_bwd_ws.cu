@@ -37,6 +37,8 @@ constexpr int kThreads = (kComputeWarps + 4) * 32;
 constexpr int kTileB = 128 * 64;    // [128 x 32] 16-bit operand tile, 64-byte rows, 64B swizzle
 constexpr int kAtomB = 128 * 128;   // [128 x 64] 16-bit tile, 128-byte rows, 128B swizzle (bias^T atoms, dS^T atoms)
 constexpr int kDP = 32;             // padded head size
+constexpr int kStageB = 2 * kTileB + 4096;             // main kernel: a (K, V, XK) or (Q, dO, XQ) stage
+constexpr int kDbStageB = 4 * kTileB + 2 * 4096;      // dBias kernel: one row's Q, dO, K, V tiles and its two rank-one term tiles
 // registers per thread: at launch (640 threads) / compute warps / helper warps after setmaxnreg.  The raise of the
 // compute warps can only draw on what the helper warps release inside the CTA - otherwise it never returns.
 constexpr int kLaunchRegs = 96, kComputeRegs = 104, kHelperRegs = 64;
@@ -53,8 +55,8 @@ struct BwdWsP {
   uint32_t fmt, bfmt;
   int n_alpha; float alpha[2];
   int bias_b_mul;
-  const void* mask; int64_t ms[3]; int mask_dtype;
-  const float* stats; const int* flags;     // per-query statistics and per-(b,n,h) careful-path flags (evo_stats_ws_kernel)
+  const uint8_t* xq; const uint8_t* xk;     // rank-one term tiles (evo_extras_ws_kernel)
+  const int* flags;                         // per (b, n, h): every key of the row is masked
   void *dq, *dk, *dv;
   int* status;
 };
@@ -64,7 +66,7 @@ struct Bars {
   uint64_t sd_ready[2], written[2], buf_free[2];
   uint64_t ds_written[2], dq_done[2];        // per block parity: dS^T tile complete in shared memory / its dQ product complete
   uint64_t kv_done;                          // the dK / dV accumulation of a key tile is complete
-  uint64_t st_full[2], st_empty[2];          // per-item statistics (lse, delta) in two buffers
+  uint64_t item_done[2];                     // the compute warps have read the item's on-chip dQ accumulators
   uint64_t kv_drained, dq_drained[2];
 };
 
@@ -74,23 +76,54 @@ __device__ __forceinline__ void bulk_load_1d(void* dst, const void* src, uint32_
                ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
 
-// Per-query statistics for the backward kernels, in the layout they fetch with bulk copies:
-//   st[bnh][0][i] = lse * log2(e)   (+inf for padding rows i >= L and for fully masked rows, so that P = 0 there)
-//   st[bnh][1][i] = delta = sum_d dO * O   (0 for padding rows)
-// with rows padded to `lpad`; flags[bnh] is raised when the (b, n, h) row has a fully masked query (lse = -FLT_MAX).
-// One thread per (b, n, i, h), 16-byte loads (D is a multiple of 8).
+// ---- rank-one terms of the scores through the tensor core --------------------------------------------------
+// x[j,i] = c1 * (K Q^T + sqrt(D) bias^T)[j,i] + mask2_j - lse2_i  and  dP[j,i] - delta_i  both contain terms that depend on
+// the key or on the query alone.  Read per logit from shared memory they cost two wavefronts of the shared-memory
+// pipe per logit-warp - as much as the exponential costs on its pipe.  Instead they ride on one extra K = 16 MMA step:
+//
+//   XK[j, 0:3] = split3(mask_j * sqrt(D))     XK[j, 3:6] = 1                          (per (b, n), key tile)
+//   XQ[i, 0:3] = 1                            XQ[i, 3:6] = split3(-lse_i * sqrt(D))   XQ[i, 6:9] = split3(-delta_i)
+//   XC[j, 6:9] = 1                            (constant)
+//
+//   S''^T += XK XQ^T   (mask + lse terms; c1 * sqrt(D) = log2 e brings them into the base-2 domain)
+//   dP^T  += XC XQ^T   (-delta)
+//
+// split3 writes an fp32 value as the sum of three bf16 numbers (24 significant bits); the products are exact and the
+// accumulation is fp32.  Masked keys, keys and queries beyond L and fully masked query rows get -1e30 (finite: no NaN can
+// arise from 0 * inf), which the exponential turns into exactly 0.  Tiles are bf16 [128 rows x 16 columns], 32-byte rows,
+// 32B swizzle (4 KB), written here in the shared-memory layout so that a plain bulk copy fetches them.
+constexpr int kXTileB = 128 * 32;
+constexpr float kMinusBig = -1e30f;
+
+__device__ __forceinline__ void split3(float v, __nv_bfloat16 (&o)[3]) {
+  o[0] = __float2bfloat16_rn(v);
+  const float r1 = v - __bfloat162float(o[0]);
+  o[1] = __float2bfloat16_rn(r1);
+  o[2] = __float2bfloat16_rn(r1 - __bfloat162float(o[1]));
+}
+__device__ __forceinline__ uint32_t pack_bf(__nv_bfloat16 a, __nv_bfloat16 b) {
+  return (uint32_t)__bfloat16_as_ushort(a) | ((uint32_t)__bfloat16_as_ushort(b) << 16);
+}
+
+// One thread per (b, n, i < lpad, h): delta = sum_d dO * O (16-byte loads; D is a multiple of 8), the XQ row of query i
+// and, for h == 0, the XK row of key i.  flags[bnh] is raised when the row (b, n) has every key masked (lse = -FLT_MAX).
 template <typename T>
-__global__ void evo_stats_ws_kernel(const T* __restrict__ o, const T* __restrict__ d_o, const float* __restrict__ lse,
-                                    float* __restrict__ st, int* __restrict__ flags, int64_t rows_pad, int L, int lpad, int H, int D) {
+__global__ void evo_extras_ws_kernel(const T* __restrict__ o, const T* __restrict__ d_o, const float* __restrict__ lse,
+                                     const void* __restrict__ mask, int64_t ms_b, int64_t ms_n, int64_t ms_l, int mask_dtype,
+                                     uint8_t* __restrict__ xq, uint8_t* __restrict__ xk, int* __restrict__ flags,
+                                     int64_t rows_pad, int N, int L, int lpad, int H, int D) {
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= rows_pad) return;
   const int h = (int)(idx % H); const int64_t t = idx / H; const int i = (int)(t % lpad); const int64_t bn = t / lpad;
   const int64_t bnh = bn * H + h;
-  float l2 = INFINITY, dl = 0.f;
+  const float sqrt_d = sqrtf((float)D);
+  const __nv_bfloat16 one = __float2bfloat16_rn(1.f), zero = __float2bfloat16_rn(0.f);
+  float nl = kMinusBig, nd = 0.f;
   if (i < L) {
     const int64_t row = (bn * L + i) * H + h;
     const uint4* po = reinterpret_cast<const uint4*>(o + row * D);
     const uint4* pg = reinterpret_cast<const uint4*>(d_o + row * D);
+    float dl = 0.f;
     for (int c = 0; c < D / 8; ++c) {
       const uint4 a = __ldg(po + c), g = __ldg(pg + c);
       const uint32_t av[4] = {a.x, a.y, a.z, a.w}, gv[4] = {g.x, g.y, g.z, g.w};
@@ -100,11 +133,40 @@ __global__ void evo_stats_ws_kernel(const T* __restrict__ o, const T* __restrict
         dl = fmaf(x.x, y.x, dl); dl = fmaf(x.y, y.y, dl);
       }
     }
+    nd = -dl;
     const float lv = lse[bnh * L + i];
-    if (lv <= -3e38f) flags[bnh] = 1; else l2 = lv * kLog2e;
+    if (lv <= -3e38f) flags[bnh] = 1; else nl = -lv * sqrt_d;
   }
-  st[bnh * 2 * lpad + i] = l2;
-  st[bnh * 2 * lpad + lpad + i] = dl;
+  const int nt = lpad / 128, tile = i >> 7, r = i & 127;
+  {
+    __nv_bfloat16 a[3], b[3];
+    split3(nl, a); split3(nd, b);
+    uint8_t* base = xq + ((int64_t)bnh * nt + tile) * kXTileB;
+    *reinterpret_cast<uint4*>(base + swz_offset(r, 0, 32)) = make_uint4(pack_bf(one, one), pack_bf(one, a[0]), pack_bf(a[1], a[2]), pack_bf(b[0], b[1]));
+    *reinterpret_cast<uint4*>(base + swz_offset(r, 1, 32)) = make_uint4(pack_bf(b[2], zero), 0u, 0u, 0u);
+  }
+  if (h == 0) {
+    float mv = kMinusBig;
+    if (i < L) {
+      const int n = (int)(bn % N); const int64_t b = bn / N;
+      const int64_t mi = b * ms_b + n * ms_n + (int64_t)i * ms_l;
+      mv = mask_dtype == MF_U8 ? (static_cast<const uint8_t*>(mask)[mi] ? 0.f : kMinusBig) : fmaxf(load_rt(mask, mi, mask_dtype) * sqrt_d, kMinusBig);
+    }
+    __nv_bfloat16 m[3];
+    split3(mv, m);
+    uint8_t* base = xk + ((int64_t)bn * nt + tile) * kXTileB;
+    *reinterpret_cast<uint4*>(base + swz_offset(r, 0, 32)) = make_uint4(pack_bf(m[0], m[1]), pack_bf(m[2], one), pack_bf(one, one), 0u);
+    *reinterpret_cast<uint4*>(base + swz_offset(r, 1, 32)) = make_uint4(0u, 0u, 0u, 0u);
+  }
+}
+
+// XC: ones in columns 6..8 of every row
+__device__ __forceinline__ void write_xc_tile(uint8_t* tile, int tid, int nthreads) {
+  const uint32_t one = 0x3f80u;      // bf16 1.0
+  for (int r = tid; r < 128; r += nthreads) {
+    *reinterpret_cast<uint4*>(tile + swz_offset(r, 0, 32)) = make_uint4(0u, 0u, 0u, one | (one << 16));
+    *reinterpret_cast<uint4*>(tile + swz_offset(r, 1, 32)) = make_uint4(one, 0u, 0u, 0u);
+  }
 }
 
 // biasT[b][h][j][i] = bias[b][h][i][j] in the 16-bit type TO, rows padded to `lpad` entries (the padding is zeroed by
@@ -126,33 +188,26 @@ __global__ void transpose_bias_ws_kernel(const TB* __restrict__ bias, TO* __rest
   }
 }
 
-// P^T and dS^T of one thread: key row (mask term `mk`), 16 query columns whose statistics sit at l2 / dl.
-// sr: c1-unscaled scores S''^T, dr: dP^T.  Results packed two queries per word.
-template <typename T, bool CAREFUL>
-__device__ __forceinline__ void p_and_ds(const uint32_t (&sr)[16], const uint32_t (&dr)[16], const float* __restrict__ l2,
-                                         const float* __restrict__ dl, float c1, float mk, bool key_ok, bool masked_key,
-                                         float inv_L, uint32_t* __restrict__ pp, uint32_t* __restrict__ dd) {
-  const float2 c1c1 = make_float2(c1, c1), mm = make_float2(mk, mk);
+// P^T and dS^T of one thread for 16 query columns.  sr: scores S''^T with the bias, mask and log-sum-exp terms already
+// inside (see the rank-one terms above), dr: dP^T - delta.  Results packed two queries per word.  `careful`: the row (b, n)
+// has every key masked - P is uniform over the keys of the row and no gradient passes through the (masked) logits.
+template <typename T>
+__device__ __forceinline__ void p_and_ds(const uint32_t (&sr)[16], const uint32_t (&dr)[16], float c1, bool careful,
+                                         float p_uniform, uint32_t* __restrict__ pp, uint32_t* __restrict__ dd) {
+  const float2 c1c1 = make_float2(c1, c1);
+  if (careful) {
+    const uint32_t pu = Pack2<T>::pack(p_uniform, p_uniform);
 #pragma unroll
-  for (int c4 = 0; c4 < 4; ++c4) {
-    const float4 l4 = *reinterpret_cast<const float4*>(l2 + c4 * 4);
-    const float4 d4 = *reinterpret_cast<const float4*>(dl + c4 * 4);
-    const float2 x0 = fma2(make_float2(__uint_as_float(sr[c4 * 4]), __uint_as_float(sr[c4 * 4 + 1])), c1c1, sub2(mm, make_float2(l4.x, l4.y)));
-    const float2 x1 = fma2(make_float2(__uint_as_float(sr[c4 * 4 + 2]), __uint_as_float(sr[c4 * 4 + 3])), c1c1, sub2(mm, make_float2(l4.z, l4.w)));
-    float2 p0 = make_float2(ex2f(x0.x), ex2f(x0.y)), p1 = make_float2(ex2f(x1.x), ex2f(x1.y));
-    if (CAREFUL) {       // a fully masked query row (statistic +inf) is uniform over the keys of the row; padding rows
-                         // share the mark, harmlessly: their dO, dP and delta are zero
-      const float u = key_ok ? inv_L : 0.f;
-      if (l4.x >= 3e38f) p0.x = u;
-      if (l4.y >= 3e38f) p0.y = u;
-      if (l4.z >= 3e38f) p1.x = u;
-      if (l4.w >= 3e38f) p1.y = u;
-    }
-    float2 s0 = mul2(p0, sub2(make_float2(__uint_as_float(dr[c4 * 4]), __uint_as_float(dr[c4 * 4 + 1])), make_float2(d4.x, d4.y)));
-    float2 s1 = mul2(p1, sub2(make_float2(__uint_as_float(dr[c4 * 4 + 2]), __uint_as_float(dr[c4 * 4 + 3])), make_float2(d4.z, d4.w)));
-    if (CAREFUL && masked_key) { s0 = make_float2(0.f, 0.f); s1 = s0; }      // no gradient through a masked logit
-    pp[c4 * 2] = Pack2<T>::pack(p0.x, p0.y); pp[c4 * 2 + 1] = Pack2<T>::pack(p1.x, p1.y);
-    dd[c4 * 2] = Pack2<T>::pack(s0.x, s0.y); dd[c4 * 2 + 1] = Pack2<T>::pack(s1.x, s1.y);
+    for (int c = 0; c < 8; ++c) { pp[c] = pu; dd[c] = 0u; }
+    return;
+  }
+#pragma unroll
+  for (int c2 = 0; c2 < 8; ++c2) {
+    const float2 xx = mul2(make_float2(__uint_as_float(sr[c2 * 2]), __uint_as_float(sr[c2 * 2 + 1])), c1c1);
+    const float2 pr = make_float2(ex2f(xx.x), ex2f(xx.y));
+    const float2 ds = mul2(pr, make_float2(__uint_as_float(dr[c2 * 2]), __uint_as_float(dr[c2 * 2 + 1])));
+    pp[c2] = Pack2<T>::pack(pr.x, pr.y);
+    dd[c2] = Pack2<T>::pack(ds.x, ds.y);
   }
 }
 
@@ -165,10 +220,10 @@ evo_bwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* sDS = smem;                          // [2 blocks][2 atoms]: dS^T tiles for the dQ product
   uint8_t* sBT = sDS + 4 * kAtomB;              // bias^T atoms, ring of 3
-  uint8_t* sKV = sBT + 3 * kAtomB;              // [2 stages][K, V]
-  uint8_t* sQD = sKV + 4 * kTileB;              // [3 stages][Q, dO]
-  uint8_t* sI = sQD + 6 * kTileB;               // alpha * I, two terms
-  float* sST = reinterpret_cast<float*>(sI + 2048);     // [2 items][lse2 x lpad | delta x lpad]
+  uint8_t* sKV = sBT + 3 * kAtomB;              // [2 stages][K, V, XK]
+  uint8_t* sQD = sKV + 2 * kStageB;             // [3 stages][Q, dO, XQ]
+  uint8_t* sI = sQD + 3 * kStageB;              // alpha * I, two terms
+  uint8_t* sXC = sI + 2048;                     // constant tile of the -delta term
 
   __shared__ Bars bar;
   __shared__ uint32_t tmem_base_s;
@@ -182,7 +237,7 @@ evo_bwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
       mbar_init(&bar.sd_ready[i], 1); mbar_init(&bar.written[i], kComputeWarps / 2);
       mbar_init(&bar.buf_free[i], 1);
       mbar_init(&bar.ds_written[i], kComputeWarps); mbar_init(&bar.dq_done[i], 1);
-      mbar_init(&bar.st_full[i], 1); mbar_init(&bar.st_empty[i], kComputeWarps);
+      mbar_init(&bar.item_done[i], kComputeWarps);
       mbar_init(&bar.dq_drained[i], 4);
     }
     for (int i = 0; i < 3; ++i) {
@@ -195,6 +250,7 @@ evo_bwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
   }
   write_alpha_identity<TB>(sI, p.alpha[0], tid, kThreads);
   write_alpha_identity<TB>(sI + 1024, p.alpha[1], tid, kThreads);
+  write_xc_tile(sXC, tid, kThreads);
   fence_async_smem();
   if (warp == 0) { tmem_alloc(&tmem_base_s, 512); tmem_relinquish(); }
   tc_fence_before();
@@ -278,36 +334,12 @@ evo_bwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
       int jt0, jt1; item_range(item, jt0, jt1);
       const int h = bnh % p.H, bn = bnh / p.H, n = bn % p.N, b = bn / p.N;
       const int sbuf = item_no & 1;
-      const bool special = special_next != 0;      // a fully masked row: the item takes the careful path
+      const bool special = special_next != 0;      // every key of the row is masked: the item takes the careful path
       if (item + (int)gridDim.x < p.n_items) special_next = p.flags[(item + (int)gridDim.x) / p.ksplit];
-      wait_or_flag(&bar.st_full[sbuf], (item_no >> 1) & 1, abort_flag);
-      const float* lse2c = sST + sbuf * 2 * p.lpad;
-      const float* dltc = lse2c + p.lpad;
-      float mask2_next = -INFINITY;
-      {
-        const int j0r = jt0 * kT + r;
-        if (j0r < p.L) {
-          const int64_t mi = b * p.ms[0] + n * p.ms[1] + (int64_t)j0r * p.ms[2];
-          mask2_next = p.mask_dtype == MF_U8 ? (static_cast<const uint8_t*>(p.mask)[mi] ? 0.f : -FLT_MAX)
-                                             : load_rt(p.mask, mi, p.mask_dtype) * kLog2e;
-        }
-      }
       for (int jt = jt0; jt < jt1; ++jt, ++kv_cnt) {
         const int j = jt * kT + r;
-        const bool j_ok = j < p.L;
-        const float mask2 = mask2_next;          // fetched one key tile ahead
-        if (jt + 1 < jt1) {
-          const int jn = (jt + 1) * kT + r;
-          mask2_next = -INFINITY;
-          if (jn < p.L) {
-            const int64_t mi = b * p.ms[0] + n * p.ms[1] + (int64_t)jn * p.ms[2];
-            mask2_next = p.mask_dtype == MF_U8 ? (static_cast<const uint8_t*>(p.mask)[mi] ? 0.f : -FLT_MAX)
-                                               : load_rt(p.mask, mi, p.mask_dtype) * kLog2e;
-          }
-        }
-        const bool masked_key = mask2 <= -FLT_MAX;
+        const float p_uniform = j < p.L ? p.inv_L : 0.f;       // careful path: P of a fully masked row
         for (int it = 0; it < nt; ++it, ++g) {
-          const int i0 = it * kT + team * kHalf + ch * 32;
           // ---- S''^T, dP^T of my half block -> registers
           tr(1);
           wait_or_flag(&bar.sd_ready[team], g & 1, abort_flag);
@@ -321,8 +353,7 @@ evo_bwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
             tmem_ld16(tDP + hf * 16, dr);
             tmem_ld_wait();
             if (hf == 0) tr(3);
-            if (special) p_and_ds<T, true>(sr, dr, lse2c + i0 + hf * 16, dltc + i0 + hf * 16, p.c1, mask2, j_ok, masked_key, p.inv_L, pp + hf * 8, dd + hf * 8);
-            else p_and_ds<T, false>(sr, dr, lse2c + i0 + hf * 16, dltc + i0 + hf * 16, p.c1, mask2, j_ok, masked_key, p.inv_L, pp + hf * 8, dd + hf * 8);
+            p_and_ds<T>(sr, dr, p.c1, special, p_uniform, pp + hf * 8, dd + hf * 8);
           }
           tr(4);
           // ---- packed P^T / dS^T over the scores just read (A operands of the dV / dK products)
@@ -412,10 +443,10 @@ evo_bwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
           }
         }
       }
-      // this item's statistics and on-chip dQ accumulators are no longer needed by this warp
+      // this item's on-chip dQ accumulators have been read out by this warp
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bar.st_empty[sbuf]);
+      if (lane == 0) mbar_arrive(&bar.item_done[sbuf]);
       tr(8);
     }
   } else {
@@ -424,6 +455,7 @@ evo_bwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
     auto dead = [&] { return __any_sync(0xffffffffu, *abort_flag) != 0; };
     constexpr uint32_t hi64 = desc_hi(512, kSw64), hi128 = desc_hi(1024, kSw128);
     constexpr uint32_t kTile16 = kTileB / 16, kAtom16 = kAtomB / 16;      // descriptor address units
+    constexpr uint32_t hi32 = desc_hi(256, kSw32), kStage16 = kStageB / 16, kX16 = kXTileB / 16;
     const uint32_t kv_base = desc_lo(smem_u32(sKV), 16), qd_base = desc_lo(smem_u32(sQD), 16);
     if (warp == kComputeWarps) {
       // ========================================================================== dV / dK issuer: per half block
@@ -437,7 +469,7 @@ evo_bwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
           if (!dbuf && kv > 0) wait_or_flag(&bar.kv_drained, (kv - 1) & 1, abort_flag);
           const uint32_t tdk = tKV + (kv & 1) * kv_set, tdv = tdk + 32;
           for (int it = 0; it < nt && !dead(); ++it, ++g) {
-            const uint32_t q_lo = qd_base + qslot * 2 * kTile16, do_lo = q_lo + kTile16;
+            const uint32_t q_lo = qd_base + qslot * kStage16, do_lo = q_lo + kTile16;
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
               tr(20);
@@ -474,9 +506,9 @@ evo_bwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
       for (int item = blockIdx.x; item < p.n_items && !dead(); item += gridDim.x, ++item_no) {
         int jt0, jt1; item_range(item, jt0, jt1);
         // the on-chip dQ accumulators of the previous item must have been read out before they start afresh
-        if (!DQS && item_no > 0) wait_or_flag(&bar.st_empty[(item_no - 1) & 1], ((item_no - 1) >> 1) & 1, abort_flag);
+        if (!DQS && item_no > 0) wait_or_flag(&bar.item_done[(item_no - 1) & 1], ((item_no - 1) >> 1) & 1, abort_flag);
         for (int jt = jt0; jt < jt1 && !dead(); ++jt, ++kv) {
-          const uint32_t k_lo = kv_base + (kv & 1) * 2 * kTile16;
+          const uint32_t k_lo = kv_base + (kv & 1) * kStage16;
           for (int it = 0; it < nt && !dead(); ++it, ++g) {
             wait_or_flag(&bar.ds_written[g & 1], (g >> 1) & 1, abort_flag);
             if constexpr (DQS) { if (g >= 2) wait_or_flag(&bar.dq_drained[g & 1], ((g >> 1) - 1) & 1, abort_flag); }
@@ -496,6 +528,8 @@ evo_bwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
       //   S''^T = K_j Q_i^T + alpha * bias^T,  dP^T = V_j dO_i^T
       const uint32_t id_s = idesc_f16(128, kHalf, p.fmt, 0, 0);
       const uint32_t id_b = idesc_f16(128, 16, p.bfmt, 0, 0);
+      const uint32_t id_x = idesc_f16(128, kHalf, 1u, 0, 0);        // the rank-one term tiles are bf16 whatever q/k/v are
+      const uint32_t xc_lo = desc_lo(smem_u32(sXC), 16);
       const uint32_t bt_base = desc_lo(smem_u32(sBT), 16);
       const uint32_t i_lo0 = desc_lo(smem_u32(sI), 16), i_lo1 = i_lo0 + 1024 / 16;
       const bool two_terms = p.n_alpha > 1;
@@ -505,10 +539,10 @@ evo_bwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
         int jt0, jt1; item_range(item, jt0, jt1);
         for (int jt = jt0; jt < jt1 && !dead(); ++jt, ++kv) {
           wait_or_flag(&bar.kv_full[kv & 1], (kv >> 1) & 1, abort_flag);
-          const uint32_t k_lo = kv_base + (kv & 1) * 2 * kTile16, v_lo = k_lo + kTile16;
+          const uint32_t k_lo = kv_base + (kv & 1) * kStage16, v_lo = k_lo + kTile16, xk_lo = k_lo + 2 * kTile16;
           for (int it = 0; it < nt && !dead(); ++it, ++g) {
             wait_or_flag(&bar.qd_full[qslot], quse & 1, abort_flag);
-            const uint32_t q_blk = qd_base + qslot * 2 * kTile16;
+            const uint32_t q_blk = qd_base + qslot * kStage16;
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
               tr(30);
@@ -517,9 +551,10 @@ evo_bwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
               tc_fence_after();
               tr(31);
               const uint32_t tS = tm0 + half * 128, tD = tS + 64;
-              const uint32_t q_lo = q_blk + half * 256, g_lo = q_lo + kTile16;
+              const uint32_t q_lo = q_blk + half * 256, g_lo = q_lo + kTile16, xq_lo = q_blk + 2 * kTile16 + half * (kX16 / 2);
               mma_ss_el(tS, k_lo, hi64, q_lo, hi64, id_s, false);
               mma_ss_el(tS, k_lo + 2, hi64, q_lo + 2, hi64, id_s, true);
+              mma_ss_el(tS, xk_lo, hi32, xq_lo, hi32, id_x, true);               // + mask_j - lse_i
               const uint32_t a_lo = bt_base + bslot * kAtom16;
 #pragma unroll
               for (int c = 0; c < 4; ++c) mma_ss_el(tS + c * 16, a_lo + c * 2, hi128, i_lo0, hi64, id_b, true);
@@ -529,6 +564,7 @@ evo_bwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
               }
               mma_ss_el(tD, v_lo, hi64, g_lo, hi64, id_s, false);
               mma_ss_el(tD, v_lo + 2, hi64, g_lo + 2, hi64, id_s, true);
+              mma_ss_el(tD, xc_lo, hi32, xq_lo, hi32, id_x, true);               // - delta_i
               tc_commit_el(&bar.sd_ready[half]);
               tc_commit_el(&bar.bt_empty[bslot]);
               if (++bslot == 3) { bslot = 0; ++buse; }
@@ -546,36 +582,27 @@ evo_bwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
         const int bnh = item / p.ksplit;
         int jt0, jt1; item_range(item, jt0, jt1);
         const int h = bnh % p.H, bn = bnh / p.H, n = bn % p.N, b = bn / p.N;
-        {
-          // the item's statistics: lse2 | delta, 2 * lpad floats
-          const int sb = item_no & 1;
-          if (item_no >= 2) wait_or_flag(&bar.st_empty[sb], ((item_no >> 1) - 1) & 1, abort_flag);
-          if (dead()) break;
-          const uint32_t bytes = 2u * p.lpad * sizeof(float);
-          if (elect_one()) {
-            mbar_expect_tx(&bar.st_full[sb], bytes);
-            bulk_load_1d(sST + sb * 2 * p.lpad, p.stats + (int64_t)bnh * 2 * p.lpad, bytes, &bar.st_full[sb]);
-          }
-        }
         for (int jt = jt0; jt < jt1 && !dead(); ++jt, ++kv) {
           if (kv >= 2) wait_or_flag(&bar.kv_empty[kv & 1], ((kv >> 1) - 1) & 1, abort_flag);
           if (dead()) break;
           if (elect_one()) {
             uint64_t* fb = &bar.kv_full[kv & 1];
-            uint8_t* st = sKV + (kv & 1) * 2 * kTileB;
-            mbar_expect_tx(fb, 2 * kTileB);
+            uint8_t* st = sKV + (kv & 1) * kStageB;
+            mbar_expect_tx(fb, kStageB);
             tma_load_5d(st, &mk, fb, 0, h, jt * kT, n, b);
             tma_load_5d(st + kTileB, &mv, fb, 0, h, jt * kT, n, b);
+            bulk_load_1d(st + 2 * kTileB, p.xk + ((int64_t)bn * nt + jt) * kXTileB, kXTileB, fb);
           }
           for (int it = 0; it < nt; ++it, ++g) {
             if (quse >= 1) wait_or_flag(&bar.qd_empty[qslot], (quse - 1) & 1, abort_flag);
             if (dead()) break;
             if (elect_one()) {
               uint64_t* fb = &bar.qd_full[qslot];
-              uint8_t* st = sQD + qslot * 2 * kTileB;
-              mbar_expect_tx(fb, 2 * kTileB);
+              uint8_t* st = sQD + qslot * kStageB;
+              mbar_expect_tx(fb, kStageB);
               tma_load_5d(st, &mq, fb, 0, h, it * kT, n, b);
               tma_load_5d(st + kTileB, &mg, fb, 0, h, it * kT, n, b);
+              bulk_load_1d(st + 2 * kTileB, p.xq + ((int64_t)bnh * nt + it) * kXTileB, kXTileB, fb);
             }
             if (++qslot == 3) { qslot = 0; ++quse; }
             for (int half = 0; half < 2; ++half) {
@@ -596,7 +623,6 @@ evo_bwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
         for (uint32_t back = 0; back < 2 && back < kv; ++back) { const uint32_t c = kv - 1 - back; mbar_wait(&bar.kv_full[c & 1], (c >> 1) & 1); }
         for (uint32_t back = 0; back < 3 && back < g; ++back) { const uint32_t c = g - 1 - back; mbar_wait(&bar.qd_full[c % 3], (c / 3) & 1); }
         for (uint32_t back = 0; back < 3 && back < nbt; ++back) { const uint32_t c = nbt - 1 - back; mbar_wait(&bar.bt_full[c % 3], (c / 3) & 1); }
-        for (int back = 0; back < 2 && back < item_no; ++back) { const int c = item_no - 1 - back; mbar_wait(&bar.st_full[c & 1], (c >> 1) & 1); }
       }
     }
   }
@@ -614,15 +640,13 @@ struct DbP {
   uint32_t fmt, bfmt;
   int n_alpha; float alpha[2];
   int bias_b_mul;
-  const void* mask; int64_t ms[3]; int mask_dtype;
-  const float* stats;     // per-query statistics (evo_stats_ws_kernel)
+  const uint8_t* xq; const uint8_t* xk;      // rank-one term tiles (evo_extras_ws_kernel)
   float* part;            // fp32 [nsplit][B][H][L][L] partial sums
   int* status;
 };
 
 struct DbBars {
-  uint64_t op_full[3], op_empty[3];          // Q, dO, K, V and the statistics of one row n
-  uint64_t st_empty[3];                      // the compute warps are done with the stage's statistics
+  uint64_t op_full[3], op_empty[3];          // Q, dO, K, V, XQ, XK of one row n
   uint64_t bt_full, bt_free;                 // the unit's two bias^T atoms
   uint64_t sd_ready[2], loaded[2];
 };
@@ -635,9 +659,9 @@ evo_dbias_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constan
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* sBT = smem;                          // two bias^T atoms (queries 0-63 | 64-127 of the tile)
-  uint8_t* sOP = sBT + 2 * kAtomB;              // [3 stages][Q, dO, K, V]
-  uint8_t* sI = sOP + 12 * kTileB;
-  float* sST = reinterpret_cast<float*>(sI + 2048);     // [3 stages][lse2 x 128 | delta x 128]
+  uint8_t* sOP = sBT + 2 * kAtomB;              // [3 stages][Q, dO, K, V, XQ, XK]
+  uint8_t* sI = sOP + 3 * kDbStageB;
+  uint8_t* sXC = sI + 2048;                     // constant tile of the -delta term
 
   __shared__ DbBars bar;
   __shared__ uint32_t tmem_base_s;
@@ -648,7 +672,6 @@ evo_dbias_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constan
     abort_s = 0;
     for (int i = 0; i < 3; ++i) {
       mbar_init(&bar.op_full[i], 1); mbar_init(&bar.op_empty[i], 2);      // two issuers commit
-      mbar_init(&bar.st_empty[i], kComputeWarps);
     }
     mbar_init(&bar.bt_full, 1); mbar_init(&bar.bt_free, 1);
     for (int i = 0; i < 2; ++i) { mbar_init(&bar.sd_ready[i], 2); mbar_init(&bar.loaded[i], kComputeWarps); }
@@ -657,6 +680,7 @@ evo_dbias_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constan
   }
   write_alpha_identity<TB>(sI, p.alpha[0], tid, kThreads);
   write_alpha_identity<TB>(sI + 1024, p.alpha[1], tid, kThreads);
+  write_xc_tile(sXC, tid, kThreads);
   fence_async_smem();
   if (warp == 0) { tmem_alloc(&tmem_base_s, 512); tmem_relinquish(); }
   tc_fence_before();
@@ -680,7 +704,7 @@ evo_dbias_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constan
     const int w = warp >> 2;                          // query quarter (32 columns) handled by this thread
     const int r = (warp & 3) * 32 + lane;             // TMEM lane = key row inside the tile
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
-    uint32_t g = 0, stage = 0, suse = 0;              // rows processed by this CTA (TMEM buffer g & 1, stage g % 3)
+    uint32_t g = 0;                                   // rows processed by this CTA (TMEM buffer g & 1)
     const float2 c1c1 = make_float2(p.c1, p.c1);
     MF_TRACE_DECL(tr, 0, blockIdx.x == 0 && tid == 0);
     for (int u = blockIdx.x; u < p.n_units; u += gridDim.x) {
@@ -689,29 +713,12 @@ evo_dbias_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constan
       float2 acc[16];
 #pragma unroll
       for (int c = 0; c < 16; ++c) acc[c] = make_float2(0.f, 0.f);
-      const int64_t mrow = x.b * p.ms[0] + (int64_t)j * p.ms[2];
-      auto load_mask = [&](int n) {
-        float m2 = -INFINITY;
-        if (j < p.L) {
-          const int64_t mi = mrow + n * p.ms[1];
-          m2 = p.mask_dtype == MF_U8 ? (static_cast<const uint8_t*>(p.mask)[mi] ? 0.f : -FLT_MAX)
-                                     : load_rt(p.mask, mi, p.mask_dtype) * kLog2e;
-        }
-        return m2;
-      };
-      float mask_next = load_mask(x.n0);
       for (int n = x.n0; n < x.n1; ++n, ++g) {
-        const float mask2 = mask_next;                 // fetched one row ahead
-        if (n + 1 < x.n1) mask_next = load_mask(n + 1);
         const uint32_t tST = tm0 + (g & 1) * 256 + w * 32 + lane_addr, tDP = tST + 128;
         tr(1);
-        wait_or_flag(&bar.sd_ready[g & 1], (g >> 1) & 1, abort_flag);     // implies the stage's statistics have landed
+        wait_or_flag(&bar.sd_ready[g & 1], (g >> 1) & 1, abort_flag);
         tc_fence_after();
         tr(2);
-        wait_or_flag(&bar.op_full[stage], suse & 1, abort_flag);      // complete long ago: the bulk-copied statistics become visible to this thread
-        const float* l2 = sST + stage * 256 + w * 32;
-        const float* dl = l2 + 128;
-        const float2 mm = make_float2(mask2, mask2);
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {          // 16 query columns at a time keeps the live registers down
           uint32_t sr[16], dr[16];
@@ -724,20 +731,14 @@ evo_dbias_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constan
             if (lane == 0) mbar_arrive(&bar.loaded[g & 1]);
             tr(3);
           }
+          // mask, lse and delta are already inside the accumulators: P = 2^(c1 S''), dS = P dP''
 #pragma unroll
-          for (int c4 = 0; c4 < 4; ++c4) {
-            const float4 l4 = *reinterpret_cast<const float4*>(l2 + hf * 16 + c4 * 4);
-            const float4 d4 = *reinterpret_cast<const float4*>(dl + hf * 16 + c4 * 4);
-            const float2 x0 = fma2(make_float2(__uint_as_float(sr[c4 * 4]), __uint_as_float(sr[c4 * 4 + 1])), c1c1, sub2(mm, make_float2(l4.x, l4.y)));
-            const float2 x1 = fma2(make_float2(__uint_as_float(sr[c4 * 4 + 2]), __uint_as_float(sr[c4 * 4 + 3])), c1c1, sub2(mm, make_float2(l4.z, l4.w)));
-            const float2 p0 = make_float2(ex2f(x0.x), ex2f(x0.y)), p1 = make_float2(ex2f(x1.x), ex2f(x1.y));
-            acc[hf * 8 + c4 * 2] = fma2(p0, sub2(make_float2(__uint_as_float(dr[c4 * 4]), __uint_as_float(dr[c4 * 4 + 1])), make_float2(d4.x, d4.y)), acc[hf * 8 + c4 * 2]);
-            acc[hf * 8 + c4 * 2 + 1] = fma2(p1, sub2(make_float2(__uint_as_float(dr[c4 * 4 + 2]), __uint_as_float(dr[c4 * 4 + 3])), make_float2(d4.z, d4.w)), acc[hf * 8 + c4 * 2 + 1]);
+          for (int c2 = 0; c2 < 8; ++c2) {
+            const float2 xx = mul2(make_float2(__uint_as_float(sr[c2 * 2]), __uint_as_float(sr[c2 * 2 + 1])), c1c1);
+            const float2 pr = make_float2(ex2f(xx.x), ex2f(xx.y));
+            acc[hf * 8 + c2] = fma2(pr, make_float2(__uint_as_float(dr[c2 * 2]), __uint_as_float(dr[c2 * 2 + 1])), acc[hf * 8 + c2]);
           }
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bar.st_empty[stage]);
-        if (++stage == 3) { stage = 0; ++suse; }
         tr(4);
       }
       // the unit's partial sum: part[sp][b][h][i][j], lanes = consecutive keys
@@ -758,8 +759,10 @@ evo_dbias_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constan
     auto dead = [&] { return __any_sync(0xffffffffu, *abort_flag) != 0; };
     constexpr uint32_t hi64 = desc_hi(512, kSw64), hi128 = desc_hi(1024, kSw128);
     constexpr uint32_t kTile16 = kTileB / 16, kAtom16 = kAtomB / 16;
+    constexpr uint32_t hi32 = desc_hi(256, kSw32), kStage16 = kDbStageB / 16;
     const uint32_t op_base = desc_lo(smem_u32(sOP), 16);
     const uint32_t id_s = idesc_f16(128, 128, p.fmt, 0, 0);
+    const uint32_t id_x = idesc_f16(128, 128, 1u, 0, 0);          // the rank-one term tiles are bf16 whatever q/k/v are
     if (warp == kComputeWarps) {
       // ========================================================================== score issuer: S''^T = K Q^T + alpha * bias^T
       const uint32_t id_b = idesc_f16(128, 16, p.bfmt, 0, 0);
@@ -777,10 +780,12 @@ evo_dbias_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constan
           if (g >= 2) wait_or_flag(&bar.loaded[g & 1], ((g >> 1) - 1) & 1, abort_flag);
           tc_fence_after();
           tr(21);
-          const uint32_t q_lo = op_base + stage * 4 * kTile16, k_lo = q_lo + 2 * kTile16;
+          const uint32_t q_lo = op_base + stage * kStage16, k_lo = q_lo + 2 * kTile16;
+          const uint32_t xq_lo = q_lo + 4 * kTile16, xk_lo = xq_lo + kXTileB / 16;
           const uint32_t tST = tm0 + (g & 1) * 256;
           mma_ss_el(tST, k_lo, hi64, q_lo, hi64, id_s, false);
           mma_ss_el(tST, k_lo + 2, hi64, q_lo + 2, hi64, id_s, true);
+          mma_ss_el(tST, xk_lo, hi32, xq_lo, hi32, id_x, true);                 // + mask_j - lse_i
 #pragma unroll
           for (int c = 0; c < 8; ++c) mma_ss_el(tST + c * 16, bt_lo + (c >> 2) * kAtom16 + (c & 3) * 2, hi128, i_lo0, hi64, id_b, true);
           if (two_terms) {
@@ -803,10 +808,12 @@ evo_dbias_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constan
           wait_or_flag(&bar.op_full[stage], suse & 1, abort_flag);
           if (g >= 2) wait_or_flag(&bar.loaded[g & 1], ((g >> 1) - 1) & 1, abort_flag);
           tc_fence_after();
-          const uint32_t g_lo = op_base + stage * 4 * kTile16 + kTile16, v_lo = g_lo + 2 * kTile16;
+          const uint32_t g_lo = op_base + stage * kStage16 + kTile16, v_lo = g_lo + 2 * kTile16;
+          const uint32_t xq_lo = op_base + stage * kStage16 + 4 * kTile16;
           const uint32_t tDP = tm0 + (g & 1) * 256 + 128;
           mma_ss_el(tDP, v_lo, hi64, g_lo, hi64, id_s, false);
           mma_ss_el(tDP, v_lo + 2, hi64, g_lo + 2, hi64, id_s, true);
+          mma_ss_el(tDP, desc_lo(smem_u32(sXC), 16), hi32, xq_lo, hi32, id_x, true);      // - delta_i
           tc_commit_el(&bar.sd_ready[g & 1]);
           tc_commit_el(&bar.op_empty[stage]);
           if (++stage == 3) { stage = 0; ++suse; }
@@ -825,23 +832,19 @@ evo_dbias_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constan
           tma_load_4d(sBT + kAtomB, &mbt, &bar.bt_full, x.it * kT + kHalf, x.jt * kT, x.h, x.b * p.bias_b_mul);
         }
         for (int n = x.n0; n < x.n1; ++n, ++g) {
-          if (suse >= 1) {
-            wait_or_flag(&bar.op_empty[stage], (suse - 1) & 1, abort_flag);
-            wait_or_flag(&bar.st_empty[stage], (suse - 1) & 1, abort_flag);
-          }
+          if (suse >= 1) wait_or_flag(&bar.op_empty[stage], (suse - 1) & 1, abort_flag);
           if (dead()) break;
           if (elect_one()) {
             uint64_t* fb = &bar.op_full[stage];
-            uint8_t* st = sOP + stage * 4 * kTileB;
-            mbar_expect_tx(fb, 4 * kTileB + 1024);
+            uint8_t* st = sOP + stage * kDbStageB;
+            mbar_expect_tx(fb, kDbStageB);
             tma_load_5d(st, &mq, fb, 0, x.h, x.it * kT, n, x.b);
             tma_load_5d(st + kTileB, &mg, fb, 0, x.h, x.it * kT, n, x.b);
             tma_load_5d(st + 2 * kTileB, &mk, fb, 0, x.h, x.jt * kT, n, x.b);
             tma_load_5d(st + 3 * kTileB, &mv, fb, 0, x.h, x.jt * kT, n, x.b);
-            // lse2 | delta of the tile's 128 queries
-            const float* src = p.stats + ((((int64_t)x.b * p.N + n) * p.H + x.h) * 2) * p.lpad + x.it * kT;
-            bulk_load_1d(sST + stage * 256, src, 512, fb);
-            bulk_load_1d(sST + stage * 256 + 128, src + p.lpad, 512, fb);
+            const int64_t bn = (int64_t)x.b * p.N + n;
+            bulk_load_1d(st + 4 * kTileB, p.xq + ((bn * p.H + x.h) * nt + x.it) * kXTileB, kXTileB, fb);
+            bulk_load_1d(st + 4 * kTileB + kXTileB, p.xk + (bn * nt + x.jt) * kXTileB, kXTileB, fb);
           }
           if (++stage == 3) { stage = 0; ++suse; }
         }
@@ -886,7 +889,7 @@ int bwd_ksplit(int64_t bnh, int nt, int sms) {
 struct BwdPlan {
   int nt, lpad, ksplit, dq_stream, dbuf, nsplit;
   bool dq_fp32, part_direct;
-  size_t off_stats, off_flags, off_part, off_dq, off_biasT, total;
+  size_t off_flags, off_xq, off_xk, off_part, off_dq, off_biasT, total;
 };
 
 BwdPlan plan_bwd(const mf_evo_bwd_args& a) {
@@ -907,8 +910,9 @@ BwdPlan plan_bwd(const mf_evo_bwd_args& a) {
   pl.nsplit = (int)ns;
   pl.part_direct = pl.nsplit == 1 && a.dbias_dtype == MF_F32;      // a single range writes d_bias itself
   size_t off = 0;
-  pl.off_stats = off; off += align_up(sizeof(float) * (size_t)a.B * a.N * a.H * 2 * pl.lpad, 256);
   pl.off_flags = off; off += align_up(sizeof(int) * (size_t)a.B * a.N * a.H, 256);
+  pl.off_xq = off; off += (size_t)a.B * a.N * a.H * pl.nt * kXTileB;
+  pl.off_xk = off; off += (size_t)a.B * a.N * pl.nt * kXTileB;
   pl.off_part = off; if (!pl.part_direct) off += align_up(sizeof(float) * (size_t)pl.nsplit * a.B * a.H * a.L * a.L, 256);
   pl.off_dq = off; if (pl.dq_fp32) off += align_up(sizeof(float) * (size_t)a.B * a.N * a.L * a.H * a.D, 256);
   pl.off_biasT = off; off += align_up(2 * (size_t)a.B * a.H * a.L * pl.lpad, 256);
@@ -930,8 +934,9 @@ int launch_bwd_ws(const mf_evo_bwd_args& a, cudaStream_t st) {
   MF_REQUIRE(status, MF_ERR_CUDA, "could not allocate the device status word");
   MF_REQUIRE(tc_async_status() == 0, MF_ERR_CUDA, "an earlier tensor-core kernel gave up on a bounded wait; results are invalid");
   char* ws = static_cast<char*>(a.workspace);
-  float* stats = reinterpret_cast<float*>(ws + pl.off_stats);
   int* flags = reinterpret_cast<int*>(ws + pl.off_flags);
+  uint8_t* xq = reinterpret_cast<uint8_t*>(ws + pl.off_xq);
+  uint8_t* xk = reinterpret_cast<uint8_t*>(ws + pl.off_xk);
   float* part = pl.part_direct ? static_cast<float*>(a.d_bias) : reinterpret_cast<float*>(ws + pl.off_part);
   float* dq_acc = reinterpret_cast<float*>(ws + pl.off_dq);
   // the transposed bias copy is kept in a 16-bit type: the bias dtype when that is one, else the q/k/v dtype
@@ -952,9 +957,10 @@ int launch_bwd_ws(const mf_evo_bwd_args& a, cudaStream_t st) {
   }
   MF_CUDA(cudaMemsetAsync(flags, 0, sizeof(int) * (size_t)a.B * a.N * a.H, st));
   const int64_t rows_pad = (int64_t)a.B * a.N * lpad * a.H;
-  evo_stats_ws_kernel<T><<<(unsigned)((rows_pad + 255) / 256), 256, 0, st>>>(static_cast<const T*>(a.o), static_cast<const T*>(a.d_o), a.lse,
-                                                                          stats, flags, rows_pad, a.L, lpad, a.H, a.D);
-  MF_LAUNCHED("evo_stats_ws_kernel");
+  evo_extras_ws_kernel<T><<<(unsigned)((rows_pad + 255) / 256), 256, 0, st>>>(static_cast<const T*>(a.o), static_cast<const T*>(a.d_o), a.lse,
+                                                                           a.mask, a.mask_strides[0], a.mask_strides[1], a.mask_strides[2], a.mask_dtype,
+                                                                           xq, xk, flags, rows_pad, a.N, a.L, lpad, a.H, a.D);
+  MF_LAUNCHED("evo_extras_ws_kernel");
   const int64_t n_dq = (int64_t)a.B * a.N * a.L * a.H * a.D;
   if (pl.dq_fp32) MF_CUDA(cudaMemsetAsync(dq_acc, 0, sizeof(float) * (size_t)n_dq, st));
 
@@ -970,12 +976,10 @@ int launch_bwd_ws(const mf_evo_bwd_args& a, cudaStream_t st) {
     p.fmt = a.dtype == MF_BF16 ? 1u : 0u; p.bfmt = bt_dtype == MF_BF16 ? 1u : 0u;
     p.n_alpha = n_alpha; p.alpha[0] = alpha[0]; p.alpha[1] = alpha[1];
     p.bias_b_mul = 1;
-    p.mask = a.mask; for (int i = 0; i < 3; ++i) p.ms[i] = a.mask_strides[i];
-    p.mask_dtype = a.mask_dtype;
-    p.stats = stats;
+    p.xq = xq; p.xk = xk;
     p.part = part;
     p.status = status;
-    const size_t smem = 1024 + 2 * (size_t)kAtomB + 12 * kTileB + 2048 + 3 * 256 * sizeof(float);
+    const size_t smem = 1024 + 2 * (size_t)kAtomB + 3 * kDbStageB + 2048 + kXTileB;
     int grid = sm_count();
     if (grid > p.n_units) grid = p.n_units;
     auto kern = evo_dbias_ws_kernel<T, TT>;
@@ -1003,12 +1007,10 @@ int launch_bwd_ws(const mf_evo_bwd_args& a, cudaStream_t st) {
     p.fmt = a.dtype == MF_BF16 ? 1u : 0u; p.bfmt = bt_dtype == MF_BF16 ? 1u : 0u;
     p.n_alpha = n_alpha; p.alpha[0] = alpha[0]; p.alpha[1] = alpha[1];
     p.bias_b_mul = 1;
-    p.mask = a.mask; for (int i = 0; i < 3; ++i) p.ms[i] = a.mask_strides[i];
-    p.mask_dtype = a.mask_dtype;
-    p.stats = stats; p.flags = flags;
+    p.xq = xq; p.xk = xk; p.flags = flags;
     p.dq = a.dq; p.dk = a.dk; p.dv = a.dv;
     p.status = status;
-    const size_t smem = 1024 + 4 * (size_t)kAtomB + 3 * kAtomB + 10 * kTileB + 2048 + 4 * sizeof(float) * lpad;
+    const size_t smem = 1024 + 4 * (size_t)kAtomB + 3 * kAtomB + 5 * kStageB + 2048 + kXTileB;
     int grid = sm_count();
     if (grid > p.n_items) grid = p.n_items;
     if (pl.dq_stream) {
