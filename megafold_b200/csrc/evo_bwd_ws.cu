@@ -76,35 +76,6 @@ __device__ __forceinline__ void bulk_load_1d(void* dst, const void* src, uint32_
                ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
 
-// ---- rank-one terms of the scores through the tensor core --------------------------------------------------
-// x[j,i] = c1 * (K Q^T + sqrt(D) bias^T)[j,i] + mask2_j - lse2_i  and  dP[j,i] - delta_i  both contain terms that depend on
-// the key or on the query alone.  Read per logit from shared memory they cost two wavefronts of the shared-memory
-// pipe per logit-warp - as much as the exponential costs on its pipe.  Instead they ride on one extra K = 16 MMA step:
-//
-//   XK[j, 0:3] = split3(mask_j * sqrt(D))     XK[j, 3:6] = 1                          (per (b, n), key tile)
-//   XQ[i, 0:3] = 1                            XQ[i, 3:6] = split3(-lse_i * sqrt(D))   XQ[i, 6:9] = split3(-delta_i)
-//   XC[j, 6:9] = 1                            (constant)
-//
-//   S''^T += XK XQ^T   (mask + lse terms; c1 * sqrt(D) = log2 e brings them into the base-2 domain)
-//   dP^T  += XC XQ^T   (-delta)
-//
-// split3 writes an fp32 value as the sum of three bf16 numbers (24 significant bits); the products are exact and the
-// accumulation is fp32.  Masked keys, keys and queries beyond L and fully masked query rows get -1e30 (finite: no NaN can
-// arise from 0 * inf), which the exponential turns into exactly 0.  Tiles are bf16 [128 rows x 16 columns], 32-byte rows,
-// 32B swizzle (4 KB), written here in the shared-memory layout so that a plain bulk copy fetches them.
-constexpr int kXTileB = 128 * 32;
-constexpr float kMinusBig = -1e30f;
-
-__device__ __forceinline__ void split3(float v, __nv_bfloat16 (&o)[3]) {
-  o[0] = __float2bfloat16_rn(v);
-  const float r1 = v - __bfloat162float(o[0]);
-  o[1] = __float2bfloat16_rn(r1);
-  o[2] = __float2bfloat16_rn(r1 - __bfloat162float(o[1]));
-}
-__device__ __forceinline__ uint32_t pack_bf(__nv_bfloat16 a, __nv_bfloat16 b) {
-  return (uint32_t)__bfloat16_as_ushort(a) | ((uint32_t)__bfloat16_as_ushort(b) << 16);
-}
-
 // One thread per (b, n, i < lpad, h): delta = sum_d dO * O (16-byte loads; D is a multiple of 8), the XQ row of query i
 // and, for h == 0, the XK row of key i.  flags[bnh] is raised when the row (b, n) has every key masked (lse = -FLT_MAX).
 template <typename T>
@@ -157,15 +128,6 @@ __global__ void evo_extras_ws_kernel(const T* __restrict__ o, const T* __restric
     uint8_t* base = xk + ((int64_t)bn * nt + tile) * kXTileB;
     *reinterpret_cast<uint4*>(base + swz_offset(r, 0, 32)) = make_uint4(pack_bf(m[0], m[1]), pack_bf(m[2], one), pack_bf(one, one), 0u);
     *reinterpret_cast<uint4*>(base + swz_offset(r, 1, 32)) = make_uint4(0u, 0u, 0u, 0u);
-  }
-}
-
-// XC: ones in columns 6..8 of every row
-__device__ __forceinline__ void write_xc_tile(uint8_t* tile, int tid, int nthreads) {
-  const uint32_t one = 0x3f80u;      // bf16 1.0
-  for (int r = tid; r < 128; r += nthreads) {
-    *reinterpret_cast<uint4*>(tile + swz_offset(r, 0, 32)) = make_uint4(0u, 0u, 0u, one | (one << 16));
-    *reinterpret_cast<uint4*>(tile + swz_offset(r, 1, 32)) = make_uint4(one, 0u, 0u, 0u);
   }
 }
 

@@ -11,8 +11,9 @@
 //
 // Per key tile the issuer builds   S = Q K^T + sqrt(D) * bias   entirely on the tensor core: two MMAs for Q K^T and
 // eight [128 x 16] x [16 x 16] MMAs that add the bias tile (A operand, straight from the TMA-loaded tile) times
-// alpha * I (B operand) - see evo_tc_common.cuh.  The softmax thread reads its 128 logits, scales them into the base-2
-// domain with the key mask added (one packed FMA per two logits), takes the maximum with three-input max, and writes
+// alpha * I (B operand), plus one K = 16 step that adds the key-mask term (a [128 x 16] tile per key tile, written by
+// the producer warp, times a constant tile) - see evo_tc_common.cuh.  The softmax thread reads its 128 logits, takes
+// the maximum with three-input max (the positive scale commutes with it), and writes
 // packed 16-bit P = 2^(x - m) back to TMEM while adding up the row sum (packed adds that hide under the
 // exponentials).  P V accumulates into O in TMEM over the key tiles; O and the sum are only multiplied by
 // 2^(m_old - m_new) when the running maximum has grown by more than 8 (rare after the first tile; P then stays
@@ -30,8 +31,8 @@ constexpr int kT = 128;                      // tile edge (queries and keys)
 constexpr int kThreads = 512;             // registers are allocated to warps in groups of four
 constexpr int kTileB = 128 * 64;             // [128 x 32] 16-bit tile, 64-byte rows, 64B swizzle
 constexpr int kAtomB = 128 * 128;            // bias atom: [128 rows x 64 columns] 16-bit, 128-byte rows, 128B swizzle
-constexpr int kStreamBytes = 6 * kTileB + 3 * kAtomB;     // Q x2, K x2, V x2, three bias atoms
-constexpr float kRescaleStep = 8.f;          // O is rescaled only when the running maximum grows by more than this (base 2)
+constexpr int kStreamBytes = 6 * kTileB + 3 * kAtomB + 2 * kXTileB;     // Q x2, K x2, V x2, three bias atoms, mask-term tile x2
+constexpr float kRescaleStep = 8.f;          // O is rescaled only when the running maximum grows by more than this (base-2 logits)
 
 struct FwdWsP {
   int B, N, L, H, D;
@@ -45,6 +46,7 @@ struct FwdWsP {
 
 struct StreamBars {
   uint64_t q_full[2], q_empty[2], k_full[2], k_empty[2], v_full[2], v_empty[2], b_full[3], b_empty[3];
+  uint64_t xk_full[2];       // the key tile's mask-term tile has been written (by the producer warp)
   uint64_t s_ready, s_free, p_ready, pv_done;
 };
 
@@ -69,7 +71,7 @@ evo_fwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* sI = smem + 2 * kStreamBytes;              // alpha * I tiles, 1 KB each
-  float* mask2_all = reinterpret_cast<float*>(sI + 2048);
+  uint8_t* sXO = sI + 2048;                           // constant partner tile of the mask term
 
   __shared__ StreamBars bars[2];
   __shared__ uint32_t tmem_base_s;
@@ -83,6 +85,7 @@ evo_fwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
       for (int i = 0; i < 2; ++i) {
         mbar_init(&b.q_full[i], 1); mbar_init(&b.q_empty[i], 1); mbar_init(&b.k_full[i], 1); mbar_init(&b.k_empty[i], 1);
         mbar_init(&b.v_full[i], 1); mbar_init(&b.v_empty[i], 1);
+        mbar_init(&b.xk_full[i], 1);
       }
       for (int i = 0; i < 3; ++i) { mbar_init(&b.b_full[i], 1); mbar_init(&b.b_empty[i], 1); }
       mbar_init(&b.s_ready, 1); mbar_init(&b.pv_done, 1);
@@ -94,6 +97,7 @@ evo_fwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
   // constant MMA operand: alpha * I (bias)
   write_alpha_identity<TB>(sI, p.alpha[0], tid, kThreads);
   write_alpha_identity<TB>(sI + 1024, p.alpha[1], tid, kThreads);
+  write_xo_tile(sXO, tid, kThreads);
   fence_async_smem();
   if (warp == 0) { tmem_alloc(&tmem_base_s, 512); tmem_relinquish(); }
   tc_fence_before();
@@ -108,6 +112,7 @@ evo_fwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
   uint8_t* sK = sb + 2 * kTileB;
   uint8_t* sV = sb + 4 * kTileB;
   uint8_t* sB = sb + 6 * kTileB;
+  uint8_t* sXK = sB + 3 * kAtomB;
   const uint32_t tbase = tmem_base_s + s * 256;               // S [0,128) | P [128,192) | O [192,224)
 
   const int stream = blockIdx.x * 2 + s;
@@ -123,35 +128,17 @@ evo_fwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
     // kHelperRegs and the softmax warpgroups rise to kSoftmaxRegs.  The raise can only draw on what the drop releases
     // inside this CTA (otherwise it never returns): the launcher checks the launch figure.
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kSoftmaxRegs));
-    const int wg_tid = tid & 127;
     const int r = (warp & 3) * 32 + lane;
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t tS = tbase + lane_addr, tP = tS + 128, tO = tS + 192;
-    float* mask2 = mask2_all + s * p.lpad;
     const float2 c1c1 = make_float2(p.c1, p.c1);
-    int prev_bn = -1;
     uint32_t g = 0;
     MF_TRACE_DECL(tr, 0, blockIdx.x == 0 && tid == 0);
     for (int il = 0; il < n_my; ++il) {
       const ItemPos ip = item_pos(item_begin + il, p);
       const int i = ip.qt * kT + r;
-      if (ip.bn != prev_bn) {
-        // additive key terms of row (b, n) in the base-2 domain; columns beyond L are -inf
-        named_sync(1 + s, 128);
-        for (int j = wg_tid; j < p.lpad; j += 128) {
-          float v = -INFINITY;
-          if (j < p.L) {
-            const int64_t mi = ip.b * p.ms[0] + ip.n * p.ms[1] + j * p.ms[2];
-            v = p.mask_dtype == MF_U8 ? (static_cast<const uint8_t*>(p.mask)[mi] ? 0.f : -FLT_MAX)
-                                      : load_rt(p.mask, mi, p.mask_dtype) * kLog2e;
-          }
-          mask2[j] = v;
-        }
-        named_sync(1 + s, 128);
-        prev_bn = ip.bn;
-      }
       float m_used = 0.f;
-      float2 lsum = make_float2(0.f, 0.f);        // row sum of P relative to m_used (two partial sums)
+      float2 lsum0 = make_float2(0.f, 0.f), lsum1 = lsum0;        // row sum of P relative to m_used (four partial sums)
       for (int t = 0; t < n_kt; ++t, ++g) {
         // ---------------------------------------------------------------- S(g) -> registers
         tr(1);
@@ -168,30 +155,25 @@ evo_fwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
         __syncwarp();
         if (lane == 0) mbar_arrive(&bar.s_free);          // the issuer may overwrite S with the next tile's scores
         tr(3);
-        // ---------------------------------------------------------------- pass 1: base-2 logits and their maximum
-        const float* mk = mask2 + t * kT;
+        // ---------------------------------------------------------------- pass 1: the maximum.  Bias and key mask are
+        // already inside S (tensor core), and the scale c1 > 0 commutes with the maximum: nothing but three-input maxima
         float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
         for (int c4 = 0; c4 < kT / 4; ++c4) {
-          const float4 m4 = *reinterpret_cast<const float4*>(mk + c4 * 4);
-          const float2 a = fma2(make_float2(__uint_as_float(sr[c4 * 4]), __uint_as_float(sr[c4 * 4 + 1])), c1c1, make_float2(m4.x, m4.y));
-          const float2 b2 = fma2(make_float2(__uint_as_float(sr[c4 * 4 + 2]), __uint_as_float(sr[c4 * 4 + 3])), c1c1, make_float2(m4.z, m4.w));
-          sr[c4 * 4] = __float_as_uint(a.x); sr[c4 * 4 + 1] = __float_as_uint(a.y);
-          sr[c4 * 4 + 2] = __float_as_uint(b2.x); sr[c4 * 4 + 3] = __float_as_uint(b2.y);
-          mx[c4 & 1 ? 2 : 0] = max3f(mx[c4 & 1 ? 2 : 0], a.x, a.y);
-          mx[c4 & 1 ? 3 : 1] = max3f(mx[c4 & 1 ? 3 : 1], b2.x, b2.y);
+          mx[c4 & 1 ? 2 : 0] = max3f(mx[c4 & 1 ? 2 : 0], __uint_as_float(sr[c4 * 4]), __uint_as_float(sr[c4 * 4 + 1]));
+          mx[c4 & 1 ? 3 : 1] = max3f(mx[c4 & 1 ? 3 : 1], __uint_as_float(sr[c4 * 4 + 2]), __uint_as_float(sr[c4 * 4 + 3]));
         }
-        const float m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+        const float m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));      // in units of the unscaled scores
         tr(4);
         if (t == 0) {
           m_used = m_blk;
         } else {
-          const bool grow = m_blk > m_used + kRescaleStep;
+          const bool grow = (m_blk - m_used) * p.c1 > kRescaleStep;
           if (__any_sync(0xffffffffu, grow)) {
             // rare: bring O and the row sum of this warp's rows to the new maximum
             wait_or_flag(&bar.pv_done, (g - 1) & 1, abort_flag);
             tc_fence_after();
-            const float f = grow ? ex2f(m_used - m_blk) : 1.f;
+            const float f = grow ? ex2f((m_used - m_blk) * p.c1) : 1.f;
             if (grow) m_used = m_blk;
 #pragma unroll
             for (int hf = 0; hf < 2; ++hf) {
@@ -203,22 +185,25 @@ evo_fwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
               tmem_st16(tO + hf * 16, o16);
             }
             tmem_st_wait();
-            lsum.x *= f; lsum.y *= f;
+            lsum0.x *= f; lsum0.y *= f; lsum1.x *= f; lsum1.y *= f;
           }
         }
         // ---------------------------------------------------------------- pass 2: P = 2^(x - m) as packed 16-bit
         if (g > 0) wait_or_flag(&bar.pv_done, (g - 1) & 1, abort_flag);      // the previous product has read P
         tr(5);
+        // x = c1 * (s - m): the difference first, so that logits equal to the maximum give exactly 0 whatever their size
+        // (a fully masked row sits at about -1e30, where a fused c1 * s - c1 * m would leave a huge rounding residue)
         const float2 mm = make_float2(m_used, m_used);
 #pragma unroll
         for (int qr = 0; qr < 4; ++qr) {
           uint32_t pk[16];
 #pragma unroll
-          for (int jj = 0; jj < 16; ++jj) {
-            const float2 x = sub2(make_float2(__uint_as_float(sr[qr * 32 + 2 * jj]), __uint_as_float(sr[qr * 32 + 2 * jj + 1])), mm);
-            const float2 e = make_float2(ex2f(x.x), ex2f(x.y));
-            lsum = add2(lsum, e);
-            pk[jj] = Pack2<T>::pack(e.x, e.y);
+          for (int jj = 0; jj < 16; jj += 2) {
+            const float2 xa = mul2(sub2(make_float2(__uint_as_float(sr[qr * 32 + 2 * jj]), __uint_as_float(sr[qr * 32 + 2 * jj + 1])), mm), c1c1);
+            const float2 xb = mul2(sub2(make_float2(__uint_as_float(sr[qr * 32 + 2 * jj + 2]), __uint_as_float(sr[qr * 32 + 2 * jj + 3])), mm), c1c1);
+            const float2 ea = make_float2(ex2f(xa.x), ex2f(xa.y)), eb = make_float2(ex2f(xb.x), ex2f(xb.y));
+            lsum0 = add2(lsum0, ea); lsum1 = add2(lsum1, eb);
+            pk[jj] = Pack2<T>::pack(ea.x, ea.y); pk[jj + 1] = Pack2<T>::pack(eb.x, eb.y);
           }
           tmem_st16(tP + qr * 16, pk);
         }
@@ -234,7 +219,7 @@ evo_fwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
       tr(7);
       uint32_t o32[32];
       tmem_ld32(tO, o32);
-      const float l = lsum.x + lsum.y;
+      const float l = (lsum0.x + lsum0.y) + (lsum1.x + lsum1.y);
       tmem_ld_wait();
       tc_fence_before();
       tr(8);
@@ -252,9 +237,9 @@ evo_fwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
             *reinterpret_cast<uint4*>(orow + d8 * 8) = v;
           }
         }
-        // a row whose keys are all masked keeps m = -FLT_MAX: its log-sum-exp is stored as -FLT_MAX, the value the
-        // backward kernels recognise
-        p.lse[(((int64_t)ip.b * p.N + ip.n) * p.H + ip.h) * p.L + i] = m_used <= -1e38f ? -FLT_MAX : (m_used + lg2f(l)) * kLn2;
+        // a row whose keys are all masked has every logit at the mask term (about -1e30): uniform attention over its L
+        // keys; its log-sum-exp is stored as -FLT_MAX, the value the backward kernels recognise
+        p.lse[(((int64_t)ip.b * p.N + ip.n) * p.H + ip.h) * p.L + i] = m_used <= -1e28f ? -FLT_MAX : (m_used * p.c1 + lg2f(l)) * kLn2;
       }
       tr(9);
     }
@@ -266,7 +251,9 @@ evo_fwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
       // ========================================================================= score-MMA issuer of stream s
       const uint32_t id_s = idesc_f16(128, 128, p.fmt, 0, 0);
       const uint32_t id_b = idesc_f16(128, 16, p.bfmt, 0, 0);
-      constexpr uint32_t hi64 = desc_hi(512, kSw64), hi128 = desc_hi(1024, kSw128);
+      const uint32_t id_x = idesc_f16(128, 128, 1u, 0, 0);         // the mask-term tiles are bf16 whatever q/k/v are
+      constexpr uint32_t hi64 = desc_hi(512, kSw64), hi128 = desc_hi(1024, kSw128), hi32 = desc_hi(256, kSw32);
+      const uint32_t xo_lo = desc_lo(smem_u32(sXO), 16), xk_base = desc_lo(smem_u32(sXK), 16);
       const uint32_t tS = tbase;
       const uint32_t q_base = desc_lo(smem_u32(sQ), 16), k_base = desc_lo(smem_u32(sK), 16), b_base = desc_lo(smem_u32(sB), 16);
       const uint32_t i_lo0 = desc_lo(smem_u32(sI), 16), i_lo1 = i_lo0 + 1024 / 16;
@@ -279,6 +266,7 @@ evo_fwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
         tr(10);
         if (t == 0) wait_or_flag(&bar.q_full[il & 1], (il >> 1) & 1, abort_flag);
         wait_or_flag(&bar.k_full[g & 1], (g >> 1) & 1, abort_flag);
+        wait_or_flag(&bar.xk_full[g & 1], (g >> 1) & 1, abort_flag);
         const uint32_t slot0 = bslot, use0 = buse;
         uint32_t slot1 = slot0 + 1, use1 = use0;
         if (slot1 == 3) { slot1 = 0; ++use1; }
@@ -294,6 +282,7 @@ evo_fwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
           const uint32_t q_lo = q_base + (il & 1) * (kTileB / 16), k_lo = k_base + (g & 1) * (kTileB / 16);
           mma_ss_el(tS, q_lo, hi64, k_lo, hi64, id_s, false);
           mma_ss_el(tS, q_lo + 2, hi64, k_lo + 2, hi64, id_s, true);
+          mma_ss_el(tS, xo_lo, hi32, xk_base + (g & 1) * (kXTileB / 16), hi32, id_x, true);        // + key mask
           const uint32_t a0 = b_base + slot0 * (kAtomB / 16), a1 = b_base + slot1 * (kAtomB / 16);
 #pragma unroll
           for (int c = 0; c < 4; ++c) mma_ss_el(tS + c * 16, a0 + c * 2, hi128, i_lo0, hi64, id_b, true);      // 16 key columns each
@@ -354,6 +343,21 @@ evo_fwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
         }
         ++nq;
       };
+      // Mask term of key j of row (b, n), in units of the unscaled scores (x sqrt(D)): 0 / -1e30 for a keep-mask, the value
+      // for an additive mask; keys beyond L get -2e30 so that even a fully masked row (all its keys at -1e30) excludes them.
+      const float sqrt_d = sqrtf((float)p.D);
+      auto mask_term = [&](const ItemPos& x, int j) {
+        if (j >= p.L) return 2.f * kMinusBig;
+        const int64_t mi = x.b * p.ms[0] + x.n * p.ms[1] + (int64_t)j * p.ms[2];
+        return p.mask_dtype == MF_U8 ? (static_cast<const uint8_t*>(p.mask)[mi] ? 0.f : kMinusBig)
+                                     : fmaxf(load_rt(p.mask, mi, p.mask_dtype) * sqrt_d, kMinusBig);
+      };
+      float mterm[4];            // this lane's four keys of the NEXT key tile, fetched one tile ahead
+      if (n_my > 0) {
+        const ItemPos i0 = item_pos(item_begin, p);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) mterm[k] = mask_term(i0, k * 32 + lane);
+      }
       if (n_my > 0) load_q(0);
       for (int il = 0; il < n_my && !dead(); ++il) {
         const ItemPos ip = item_pos(item_begin + il, p);
@@ -361,6 +365,30 @@ evo_fwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
           if (t == n_kt - 1 && il + 1 < n_my) load_q(il + 1);
           if (g >= 2) wait_or_flag(&bar.k_empty[g & 1], ((g >> 1) - 1) & 1, abort_flag);
           if (dead()) break;
+          {
+            // the key tile's mask-term tile XK (rows = keys; columns 0..2 = split3 of the term), written by the whole warp
+            uint8_t* xt = sXK + (g & 1) * kXTileB;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              __nv_bfloat16 m3[3];
+              split3(mterm[k], m3);
+              const int r = k * 32 + lane;
+              *reinterpret_cast<uint4*>(xt + swz_offset(r, 0, 32)) = make_uint4(pack_bf(m3[0], m3[1]), pack_bf(m3[2], __float2bfloat16_rn(0.f)), 0u, 0u);
+              *reinterpret_cast<uint4*>(xt + swz_offset(r, 1, 32)) = make_uint4(0u, 0u, 0u, 0u);
+            }
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bar.xk_full[g & 1]);
+            // next tile's terms: same item, or the first tile of the next item
+            if (t + 1 < n_kt) {
+#pragma unroll
+              for (int k = 0; k < 4; ++k) mterm[k] = mask_term(ip, (t + 1) * kT + k * 32 + lane);
+            } else if (il + 1 < n_my) {
+              const ItemPos nx = item_pos(item_begin + il + 1, p);
+#pragma unroll
+              for (int k = 0; k < 4; ++k) mterm[k] = mask_term(nx, k * 32 + lane);
+            }
+          }
           if (elect_one()) {
             mbar_expect_tx(&bar.k_full[g & 1], kTileB);
             tma_load_5d(sK + (g & 1) * kTileB, &mk, &bar.k_full[g & 1], 0, ip.h, t * kT, ip.n, ip.b);
@@ -436,7 +464,7 @@ int launch_fwd_ws(const mf_evo_fwd_args& a, cudaStream_t st) {
   const int pairs = (p.n_items + 1) / 2;
   if (grid > pairs) grid = pairs;
   p.items_per_stream = (p.n_items + 2 * grid - 1) / (2 * grid);
-  const size_t smem = 1024 + 2 * (size_t)kStreamBytes + 2048 + 2 * sizeof(float) * p.lpad;
+  const size_t smem = 1024 + 2 * (size_t)kStreamBytes + 2048 + kXTileB;
   auto kern = evo_fwd_ws_kernel<T, TB>;
   cudaFuncAttributes fa;
   MF_CUDA(cudaFuncGetAttributes(&fa, kern));

@@ -158,6 +158,53 @@ __device__ __forceinline__ void write_alpha_identity(uint8_t* tile, float alpha,
   }
 }
 
+// ---- rank-one terms of the scores through the tensor core --------------------------------------------------
+// x[j,i] = c1 * (K Q^T + sqrt(D) bias^T)[j,i] + mask2_j - lse2_i  and  dP[j,i] - delta_i  both contain terms that depend on
+// the key or on the query alone.  Read per logit from shared memory they cost two wavefronts of the shared-memory
+// pipe per logit-warp - as much as the exponential costs on its pipe.  Instead they ride on one extra K = 16 MMA step:
+//
+//   XK[j, 0:3] = split3(mask_j * sqrt(D))     XK[j, 3:6] = 1                          (per (b, n), key tile)
+//   XQ[i, 0:3] = 1                            XQ[i, 3:6] = split3(-lse_i * sqrt(D))   XQ[i, 6:9] = split3(-delta_i)
+//   XC[j, 6:9] = 1                            (constant)
+//
+//   S''^T += XK XQ^T   (mask + lse terms; c1 * sqrt(D) = log2 e brings them into the base-2 domain)
+//   dP^T  += XC XQ^T   (-delta)
+//
+// split3 writes an fp32 value as the sum of three bf16 numbers (24 significant bits); the products are exact and the
+// accumulation is fp32.  Masked keys, keys and queries beyond L and fully masked query rows get -1e30 (finite: no NaN can
+// arise from 0 * inf), which the exponential turns into exactly 0.  Tiles are bf16 [128 rows x 16 columns], 32-byte rows,
+// 32B swizzle (4 KB), written here in the shared-memory layout so that a plain bulk copy fetches them.
+constexpr int kXTileB = 128 * 32;
+constexpr float kMinusBig = -1e30f;
+
+__device__ __forceinline__ void split3(float v, __nv_bfloat16 (&o)[3]) {
+  o[0] = __float2bfloat16_rn(v);
+  const float r1 = v - __bfloat162float(o[0]);
+  o[1] = __float2bfloat16_rn(r1);
+  o[2] = __float2bfloat16_rn(r1 - __bfloat162float(o[1]));
+}
+__device__ __forceinline__ uint32_t pack_bf(__nv_bfloat16 a, __nv_bfloat16 b) {
+  return (uint32_t)__bfloat16_as_ushort(a) | ((uint32_t)__bfloat16_as_ushort(b) << 16);
+}
+
+// XC: ones in columns 6..8 of every row
+__device__ __forceinline__ void write_xc_tile(uint8_t* tile, int tid, int nthreads) {
+  const uint32_t one = 0x3f80u;      // bf16 1.0
+  for (int r = tid; r < 128; r += nthreads) {
+    *reinterpret_cast<uint4*>(tile + swz_offset(r, 0, 32)) = make_uint4(0u, 0u, 0u, one | (one << 16));
+    *reinterpret_cast<uint4*>(tile + swz_offset(r, 1, 32)) = make_uint4(one, 0u, 0u, 0u);
+  }
+}
+
+// XO: ones in columns 0..2 of every row (the forward kernel's partner of the mask columns of XK)
+__device__ __forceinline__ void write_xo_tile(uint8_t* tile, int tid, int nthreads) {
+  const uint32_t one = 0x3f80u;      // bf16 1.0
+  for (int r = tid; r < 128; r += nthreads) {
+    *reinterpret_cast<uint4*>(tile + swz_offset(r, 0, 32)) = make_uint4(one | (one << 16), one, 0u, 0u);
+    *reinterpret_cast<uint4*>(tile + swz_offset(r, 1, 32)) = make_uint4(0u, 0u, 0u, 0u);
+  }
+}
+
 // ---- phase trace (debug builds only: -DMF_TRACE) -------------------------------------------------------
 // One elected thread per role of CTA 0 records (tag, clock64) pairs into a global buffer handed in through
 // mf_debug_set_trace(); role `r` owns entries [r * kTraceLen, (r + 1) * kTraceLen).  Compiled out otherwise.
