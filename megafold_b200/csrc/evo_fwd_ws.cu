@@ -345,20 +345,45 @@ evo_fwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
       };
       // Mask term of key j of row (b, n), in units of the unscaled scores (x sqrt(D)): 0 / -1e30 for a keep-mask, the value
       // for an additive mask; keys beyond L get -2e30 so that even a fully masked row (all its keys at -1e30) excludes them.
+      // The mask values of a tile are fetched one tile ahead as raw bits (four independent loads) and converted when the
+      // tile is written, so that their latency is never waited for.
       const float sqrt_d = sqrtf((float)p.D);
-      auto mask_term = [&](const ItemPos& x, int j) {
-        if (j >= p.L) return 2.f * kMinusBig;
-        const int64_t mi = x.b * p.ms[0] + x.n * p.ms[1] + (int64_t)j * p.ms[2];
-        return p.mask_dtype == MF_U8 ? (static_cast<const uint8_t*>(p.mask)[mi] ? 0.f : kMinusBig)
-                                     : fmaxf(load_rt(p.mask, mi, p.mask_dtype) * sqrt_d, kMinusBig);
-      };
-      float mterm[4];            // this lane's four keys of the NEXT key tile, fetched one tile ahead
-      if (n_my > 0) {
-        const ItemPos i0 = item_pos(item_begin, p);
+      uint32_t raw[4] = {0u, 0u, 0u, 0u};
+      auto fetch = [&](const ItemPos& x, int j0) {
+        int64_t mi[4];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) mterm[k] = mask_term(i0, k * 32 + lane);
-      }
+        for (int k = 0; k < 4; ++k) {
+          int j = j0 + k * 32 + lane;
+          if (j >= p.L) j = p.L - 1;
+          mi[k] = x.b * p.ms[0] + x.n * p.ms[1] + (int64_t)j * p.ms[2];
+        }
+        if (p.mask_dtype == MF_U8) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) raw[k] = static_cast<const uint8_t*>(p.mask)[mi[k]];
+        } else if (p.mask_dtype == MF_F32) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) raw[k] = static_cast<const uint32_t*>(p.mask)[mi[k]];
+        } else {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) raw[k] = static_cast<const uint16_t*>(p.mask)[mi[k]];
+        }
+      };
+      auto term = [&](uint32_t bits, int j) {
+        float v;
+        if (p.mask_dtype == MF_U8) v = bits ? 0.f : kMinusBig;
+        else {
+          const float x = p.mask_dtype == MF_F32 ? __uint_as_float(bits)
+                          : p.mask_dtype == MF_BF16 ? __uint_as_float(bits << 16) : __half2float(__ushort_as_half((unsigned short)bits));
+          v = fmaxf(x * sqrt_d, kMinusBig);
+        }
+        return j < p.L ? v : 2.f * kMinusBig;
+      };
+      if (n_my > 0) fetch(item_pos(item_begin, p), 0);
       if (n_my > 0) load_q(0);
+      // A bulk-tensor copy keeps the thread that issues it busy for a few hundred cycles whatever its size; several lanes of
+      // one warp issuing in the same instruction cost little more than one.  So the K tile and the two bias atoms of a key
+      // tile are requested by lanes 0, 1 and 2 together (the waits before them are taken by the whole warp).
+      const CUtensorMap* map3 = lane == 0 ? &mk : &mb;
       for (int il = 0; il < n_my && !dead(); ++il) {
         const ItemPos ip = item_pos(item_begin + il, p);
         for (int t = 0; t < n_kt; ++t, ++g) {
@@ -371,39 +396,36 @@ evo_fwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
               __nv_bfloat16 m3[3];
-              split3(mterm[k], m3);
               const int r = k * 32 + lane;
+              split3(term(raw[k], t * kT + r), m3);
               *reinterpret_cast<uint4*>(xt + swz_offset(r, 0, 32)) = make_uint4(pack_bf(m3[0], m3[1]), pack_bf(m3[2], __float2bfloat16_rn(0.f)), 0u, 0u);
               *reinterpret_cast<uint4*>(xt + swz_offset(r, 1, 32)) = make_uint4(0u, 0u, 0u, 0u);
             }
             fence_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bar.xk_full[g & 1]);
-            // next tile's terms: same item, or the first tile of the next item
-            if (t + 1 < n_kt) {
-#pragma unroll
-              for (int k = 0; k < 4; ++k) mterm[k] = mask_term(ip, (t + 1) * kT + k * 32 + lane);
-            } else if (il + 1 < n_my) {
-              const ItemPos nx = item_pos(item_begin + il + 1, p);
-#pragma unroll
-              for (int k = 0; k < 4; ++k) mterm[k] = mask_term(nx, k * 32 + lane);
-            }
+            // next tile's mask values: same item, or the first tile of the next item
+            if (t + 1 < n_kt) fetch(ip, (t + 1) * kT);
+            else if (il + 1 < n_my) fetch(item_pos(item_begin + il + 1, p), 0);
           }
-          if (elect_one()) {
+          const uint32_t slot0 = bslot, use0 = buse;
+          uint32_t slot1 = slot0 + 1, use1 = use0;
+          if (slot1 == 3) { slot1 = 0; ++use1; }
+          if (use0 >= 1) wait_or_flag(&bar.b_empty[slot0], (use0 - 1) & 1, abort_flag);
+          if (use1 >= 1) wait_or_flag(&bar.b_empty[slot1], (use1 - 1) & 1, abort_flag);
+          if (dead()) break;
+          if (lane == 0) {
             mbar_expect_tx(&bar.k_full[g & 1], kTileB);
-            tma_load_5d(sK + (g & 1) * kTileB, &mk, &bar.k_full[g & 1], 0, ip.h, t * kT, ip.n, ip.b);
+            tma_load_5d(sK + (g & 1) * kTileB, map3, &bar.k_full[g & 1], 0, ip.h, t * kT, ip.n, ip.b);
+          } else if (lane <= 2) {
+            const uint32_t slot = lane == 1 ? slot0 : slot1;
+            mbar_expect_tx(&bar.b_full[slot], kAtomB);
+            tma_load_5d(sB + slot * kAtomB, map3, &bar.b_full[slot], t * kT + (lane - 1) * 64, ip.qt * kT, ip.h, ip.b * p.bias_b_mul, 0);
           }
-          ++nk;
-          for (int hf = 0; hf < 2; ++hf) {
-            if (buse >= 1) wait_or_flag(&bar.b_empty[bslot], (buse - 1) & 1, abort_flag);
-            if (dead()) break;
-            if (elect_one()) {
-              mbar_expect_tx(&bar.b_full[bslot], kAtomB);
-              tma_load_4d(sB + bslot * kAtomB, &mb, &bar.b_full[bslot], t * kT + hf * 64, ip.qt * kT, ip.h, ip.b * p.bias_b_mul);
-            }
-            ++nb;
-            if (++bslot == 3) { bslot = 0; ++buse; }
-          }
+          __syncwarp();
+          ++nk; nb += 2;
+          bslot = slot1 + 1; buse = use1;
+          if (bslot == 3) { bslot = 0; ++buse; }
           if (g >= 2) wait_or_flag(&bar.v_empty[g & 1], ((g >> 1) - 1) & 1, abort_flag);
           if (dead()) break;
           if (elect_one()) {
@@ -455,10 +477,11 @@ int launch_fwd_ws(const mf_evo_fwd_args& a, cudaStream_t st) {
   MF_REQUIRE(tc_async_status() == 0, MF_ERR_CUDA, "an earlier tensor-core kernel gave up on a bounded wait; results are invalid");
   p.bias_b_mul = a.bias_strides[0] == 0 ? 0 : 1;
   {
-    const int64_t dims[4] = {a.L, a.L, a.H, p.bias_b_mul ? a.B : 1};
-    const int64_t str[4] = {1, a.bias_strides[2], a.bias_strides[1], a.bias_strides[0]};
-    const int box[4] = {64, 128, 1, 1};
-    if ((r = make_tiled_map(&mb, a.bias, a.bias_dtype, 4, dims, str, box, 128))) return r;
+    // five dimensions (the last one a dummy) so that one instruction, issued by several lanes, loads K and bias tiles alike
+    const int64_t dims[5] = {a.L, a.L, a.H, p.bias_b_mul ? a.B : 1, 1};
+    const int64_t str[5] = {1, a.bias_strides[2], a.bias_strides[1], a.bias_strides[0], 0};
+    const int box[5] = {64, 128, 1, 1, 1};
+    if ((r = make_tiled_map(&mb, a.bias, a.bias_dtype, 5, dims, str, box, 128))) return r;
   }
   int grid = sm_count();
   const int pairs = (p.n_items + 1) / 2;
