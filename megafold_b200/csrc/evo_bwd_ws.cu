@@ -136,17 +136,41 @@ __global__ void evo_extras_ws_kernel(const T* __restrict__ o, const T* __restric
 template <typename TB, typename TO>
 __global__ void transpose_bias_ws_kernel(const TB* __restrict__ bias, TO* __restrict__ biasT, int H, int L, int lpad,
                                          int64_t sb, int64_t sh, int64_t si, int64_t sj) {
-  __shared__ float tile[32][33];
+  // 64 x 64 tiles; a thread moves two neighbouring entries at a time, on the way in (two keys of one query) and on the
+  // way out (two queries of one key), so that a warp reads and writes 128 or more contiguous bytes
+  __shared__ float tile[64][65];
   const int bh = blockIdx.z, b = bh / H, h = bh % H;
-  const int i0 = blockIdx.y * 32, j0 = blockIdx.x * 32;
-  for (int k = threadIdx.y; k < 32; k += blockDim.y) {
-    const int i = i0 + k, j = j0 + threadIdx.x;
-    if (i < L && j < L) tile[k][threadIdx.x] = to_f(bias[b * sb + h * sh + (int64_t)i * si + (int64_t)j * sj]);
+  const int i0 = blockIdx.y * 64, j0 = blockIdx.x * 64;
+  const TB* src = bias + b * sb + h * sh;
+  const bool pair_in = sj == 1 && sizeof(TB) == 2 && (si & 1) == 0 && (((sb | sh) & 1) == 0) && (reinterpret_cast<uintptr_t>(bias) & 3) == 0;
+  for (int k = threadIdx.y; k < 64; k += blockDim.y) {
+    const int i = i0 + k, j = j0 + 2 * threadIdx.x;
+    if (i >= L) continue;
+    bool done = false;
+    if constexpr (sizeof(TB) == 2) {
+      if (pair_in && j + 1 < L) {
+        const uint32_t v = *reinterpret_cast<const uint32_t*>(src + (int64_t)i * si + j);
+        TB lo, hi;
+        *reinterpret_cast<unsigned short*>(&lo) = (unsigned short)(v & 0xffffu);
+        *reinterpret_cast<unsigned short*>(&hi) = (unsigned short)(v >> 16);
+        tile[k][2 * threadIdx.x] = to_f(lo); tile[k][2 * threadIdx.x + 1] = to_f(hi);
+        done = true;
+      }
+    }
+    if (!done) {
+      if (j < L) tile[k][2 * threadIdx.x] = to_f(src[(int64_t)i * si + (int64_t)j * sj]);
+      if (j + 1 < L) tile[k][2 * threadIdx.x + 1] = to_f(src[(int64_t)i * si + (int64_t)(j + 1) * sj]);
+    }
   }
   __syncthreads();
-  for (int k = threadIdx.y; k < 32; k += blockDim.y) {
-    const int j = j0 + k, i = i0 + threadIdx.x;
-    if (i < L && j < L) biasT[((int64_t)bh * L + j) * lpad + i] = from_f<TO>(tile[threadIdx.x][k]);
+  for (int k = threadIdx.y; k < 64; k += blockDim.y) {
+    const int j = j0 + k, i = i0 + 2 * threadIdx.x;
+    if (j >= L || i >= L) continue;
+    TO* dst = biasT + ((int64_t)bh * L + j) * lpad + i;         // lpad is a multiple of 128 and i is even: 4-byte aligned
+    const TO a = from_f<TO>(tile[2 * threadIdx.x][k]);
+    const TO c = i + 1 < L ? from_f<TO>(tile[2 * threadIdx.x + 1][k]) : from_f<TO>(0.f);
+    uint32_t v = (uint32_t)*reinterpret_cast<const unsigned short*>(&a) | ((uint32_t)*reinterpret_cast<const unsigned short*>(&c) << 16);
+    *reinterpret_cast<uint32_t*>(dst) = v;
   }
 }
 
@@ -604,6 +628,7 @@ struct DbP {
   int bias_b_mul;
   const uint8_t* xq; const uint8_t* xk;      // rank-one term tiles (evo_extras_ws_kernel)
   float* part;            // fp32 [nsplit][B][H][L][L] partial sums
+  void* out16;            // with a single row range and a 16-bit d_bias: the result itself, [B][H][L][L] in the q/k/v type
   int* status;
 };
 
@@ -706,12 +731,22 @@ evo_dbias_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constan
       // the unit's partial sum: part[sp][b][h][i][j], lanes = consecutive keys
       if (j < p.L && !*abort_flag) {
         const int sp = u % p.nsplit;
-        float* dst = p.part + ((((int64_t)sp * p.B + x.b) * p.H + x.h) * p.L) * (int64_t)p.L + j;
+        const int64_t at = ((((int64_t)sp * p.B + x.b) * p.H + x.h) * p.L) * (int64_t)p.L + j;
         const int i0 = x.it * kT + w * 32;
+        if (p.out16) {
+          T* dst = static_cast<T*>(p.out16) + at;
 #pragma unroll
-        for (int c = 0; c < 16; ++c) {
-          if (i0 + 2 * c < p.L) dst[(int64_t)(i0 + 2 * c) * p.L] = acc[c].x;
-          if (i0 + 2 * c + 1 < p.L) dst[(int64_t)(i0 + 2 * c + 1) * p.L] = acc[c].y;
+          for (int c = 0; c < 16; ++c) {
+            if (i0 + 2 * c < p.L) dst[(int64_t)(i0 + 2 * c) * p.L] = from_f<T>(acc[c].x);
+            if (i0 + 2 * c + 1 < p.L) dst[(int64_t)(i0 + 2 * c + 1) * p.L] = from_f<T>(acc[c].y);
+          }
+        } else {
+          float* dst = p.part + at;
+#pragma unroll
+          for (int c = 0; c < 16; ++c) {
+            if (i0 + 2 * c < p.L) dst[(int64_t)(i0 + 2 * c) * p.L] = acc[c].x;
+            if (i0 + 2 * c + 1 < p.L) dst[(int64_t)(i0 + 2 * c + 1) * p.L] = acc[c].y;
+          }
         }
       }
     }
@@ -826,11 +861,22 @@ evo_dbias_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constan
 // d_bias[b][h][i][j] = sum over the row ranges, in order, cast to the output type
 template <typename TO>
 __global__ void dbias_finish_kernel(const float* __restrict__ part, TO* __restrict__ out, int64_t n, int nsplit) {
-  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
   if (i >= n) return;
-  float s = part[i];
-  for (int k = 1; k < nsplit; ++k) s += part[(int64_t)k * n + i];
-  out[i] = from_f<TO>(s);
+  if (i + 4 <= n && (n & 3) == 0) {            // four entries per thread; every range starts on a 16-byte boundary
+    float4 s = *reinterpret_cast<const float4*>(part + i);
+    for (int k = 1; k < nsplit; ++k) {
+      const float4 t = *reinterpret_cast<const float4*>(part + (int64_t)k * n + i);
+      s.x += t.x; s.y += t.y; s.z += t.z; s.w += t.w;
+    }
+    out[i] = from_f<TO>(s.x); out[i + 1] = from_f<TO>(s.y); out[i + 2] = from_f<TO>(s.z); out[i + 3] = from_f<TO>(s.w);
+    return;
+  }
+  for (int64_t e = i; e < n && e < i + 4; ++e) {
+    float s = part[e];
+    for (int k = 1; k < nsplit; ++k) s += part[(int64_t)k * n + e];
+    out[e] = from_f<TO>(s);
+  }
 }
 
 template <typename T>
@@ -870,7 +916,7 @@ BwdPlan plan_bwd(const mf_evo_bwd_args& a) {
   if (ns < 1) ns = 1;
   if (ns > a.N) ns = a.N;
   pl.nsplit = (int)ns;
-  pl.part_direct = pl.nsplit == 1 && a.dbias_dtype == MF_F32;      // a single range writes d_bias itself
+  pl.part_direct = pl.nsplit == 1;      // a single range writes d_bias itself, in its own type
   size_t off = 0;
   pl.off_flags = off; off += align_up(sizeof(int) * (size_t)a.B * a.N * a.H, 256);
   pl.off_xq = off; off += (size_t)a.B * a.N * a.H * pl.nt * kXTileB;
@@ -899,7 +945,7 @@ int launch_bwd_ws(const mf_evo_bwd_args& a, cudaStream_t st) {
   int* flags = reinterpret_cast<int*>(ws + pl.off_flags);
   uint8_t* xq = reinterpret_cast<uint8_t*>(ws + pl.off_xq);
   uint8_t* xk = reinterpret_cast<uint8_t*>(ws + pl.off_xk);
-  float* part = pl.part_direct ? static_cast<float*>(a.d_bias) : reinterpret_cast<float*>(ws + pl.off_part);
+  float* part = !pl.part_direct ? reinterpret_cast<float*>(ws + pl.off_part) : (a.dbias_dtype == MF_F32 ? static_cast<float*>(a.d_bias) : nullptr);
   float* dq_acc = reinterpret_cast<float*>(ws + pl.off_dq);
   // the transposed bias copy is kept in a 16-bit type: the bias dtype when that is one, else the q/k/v dtype
   using TT = typename std::conditional<sizeof(TB) == 2, TB, T>::type;
@@ -907,8 +953,8 @@ int launch_bwd_ws(const mf_evo_bwd_args& a, cudaStream_t st) {
   TT* biasT = reinterpret_cast<TT*>(ws + pl.off_biasT);
   const int lpad = pl.lpad;
   {
-    MF_CUDA(cudaMemsetAsync(biasT, 0, 2 * (size_t)a.B * a.H * a.L * lpad, st));
-    dim3 grid((a.L + 31) / 32, (a.L + 31) / 32, a.B * a.H), block(32, 8);
+    if (lpad != a.L) MF_CUDA(cudaMemsetAsync(biasT, 0, 2 * (size_t)a.B * a.H * a.L * lpad, st));      // the row padding
+    dim3 grid((a.L + 63) / 64, (a.L + 63) / 64, a.B * a.H), block(32, 8);
     transpose_bias_ws_kernel<TB, TT><<<grid, block, 0, st>>>(static_cast<const TB*>(a.bias), biasT, a.H, a.L, lpad, a.bias_strides[0],
                                                              a.bias_strides[1], a.bias_strides[2], a.bias_strides[3]);
     MF_LAUNCHED("transpose_bias_ws_kernel");
@@ -940,6 +986,7 @@ int launch_bwd_ws(const mf_evo_bwd_args& a, cudaStream_t st) {
     p.bias_b_mul = 1;
     p.xq = xq; p.xk = xk;
     p.part = part;
+    p.out16 = pl.part_direct && a.dbias_dtype != MF_F32 ? a.d_bias : nullptr;
     p.status = status;
     const size_t smem = 1024 + 2 * (size_t)kAtomB + 3 * kDbStageB + 2048 + kXTileB;
     int grid = sm_count();
@@ -951,9 +998,9 @@ int launch_bwd_ws(const mf_evo_bwd_args& a, cudaStream_t st) {
     if (!pl.part_direct) {
       const int64_t n_out = (int64_t)a.B * a.H * a.L * a.L;
       if (a.dbias_dtype == MF_F32)
-        dbias_finish_kernel<float><<<(unsigned)((n_out + 255) / 256), 256, 0, st>>>(part, static_cast<float*>(a.d_bias), n_out, pl.nsplit);
+        dbias_finish_kernel<float><<<(unsigned)((n_out + 1023) / 1024), 256, 0, st>>>(part, static_cast<float*>(a.d_bias), n_out, pl.nsplit);
       else
-        dbias_finish_kernel<T><<<(unsigned)((n_out + 255) / 256), 256, 0, st>>>(part, static_cast<T*>(a.d_bias), n_out, pl.nsplit);
+        dbias_finish_kernel<T><<<(unsigned)((n_out + 1023) / 1024), 256, 0, st>>>(part, static_cast<T*>(a.d_bias), n_out, pl.nsplit);
       MF_LAUNCHED("dbias_finish_kernel");
     }
   }
