@@ -22,7 +22,7 @@ TRACE = os.environ.get("MF_TRACE") == "1"
 LIB = os.path.join(PKG, "libmegafold_b200_trace.so" if TRACE else "libmegafold_b200.so")
 OBJ_DIR = os.path.join(PKG, "build_trace" if TRACE else "build")
 
-SOURCES = ["api.cu", "evo_simt.cu", "evo_tc.cu", "evo_tc_fwd.cu", "evo_fwd_ws.cu", "evo_bwd_ws.cu", "lnl_simt.cu", "lnl_tc.cu", "transition_tc.cu", "gemm_tc.cu", "transition_bwd_tc.cu"]
+SOURCES = ["api.cu", "evo_simt.cu", "evo_tc.cu", "evo_tc_fwd.cu", "evo_fwd_ws.cu", "evo_bwd_ws.cu", "lnl_ops.cu", "lnl_tc.cu", "transition_tc.cu", "gemm_tc.cu", "transition_bwd_tc.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr",
@@ -76,7 +76,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
                 print(out)
     objs = [os.path.join(OBJ_DIR, s.replace(".cu", ".o")) for s in SOURCES]
     if force or jobs or _stale(LIB, objs):
-        run([nvcc, "-shared", "-o", LIB, *objs, "-Xcompiler", "-fPIC", "-cudart", "static"])
+        run([nvcc, "-shared", "-o", LIB, *objs, "-Xcompiler", "-fPIC", "-cudart", "static", "-ldl"])
     return LIB
 
 

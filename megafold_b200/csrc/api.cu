@@ -1,6 +1,8 @@
 // C ABI of the library: argument validation and dispatch to the kernel families.
 #include "common.cuh"
 
+#include <nvtx3/nvToolsExt.h>
+
 namespace mf {
 
 char* last_error_buf() {
@@ -12,6 +14,15 @@ void set_last_path(const char* p) { t_last_path = p; }
 std::atomic<uint64_t> g_launches{0};
 
 namespace {
+
+// One NVTX range per entry point (the reference marks its fused operators the same way for its timeline traces); without
+// a profiler attached the calls return at once.
+struct Range {
+  explicit Range(const char* name) { nvtxRangePushA(name); }
+  ~Range() { nvtxRangePop(); }
+  Range(const Range&) = delete;
+  Range& operator=(const Range&) = delete;
+};
 
 bool float_dtype(int dt) { return dt == MF_F32 || dt == MF_BF16 || dt == MF_F16; }
 
@@ -51,6 +62,7 @@ using namespace mf;
 extern "C" {
 
 int mf_evo_fwd(const mf_evo_fwd_args* args, void* stream) {
+  Range nvtx_range("mf_evo_fwd");
   MF_REQUIRE(args, MF_ERR_BAD_ARG, "args is NULL");
   const mf_evo_fwd_args& a = *args;
   int r = check_evo_common(a); if (r) return r;
@@ -82,6 +94,7 @@ size_t mf_evo_bwd_workspace_bytes(const mf_evo_bwd_args* args) {
 }
 
 int mf_evo_bwd(const mf_evo_bwd_args* args, void* stream) {
+  Range nvtx_range("mf_evo_bwd");
   MF_REQUIRE(args, MF_ERR_BAD_ARG, "args is NULL");
   const mf_evo_bwd_args& a = *args;
   int r = check_evo_common(a); if (r) return r;
@@ -107,6 +120,7 @@ int mf_evo_bwd(const mf_evo_bwd_args* args, void* stream) {
 }
 
 int mf_evo_bwd_noalloc(const mf_evo_bwd_args* args, void* stream) {
+  Range nvtx_range("mf_evo_bwd_noalloc");
   MF_REQUIRE(args, MF_ERR_BAD_ARG, "args is NULL");
   const mf_evo_bwd_args& a = *args;
   int r = check_evo_common(a); if (r) return r;
@@ -125,6 +139,7 @@ int mf_evo_bwd_noalloc(const mf_evo_bwd_args* args, void* stream) {
 size_t mf_evo_bwd_noalloc_max_rows(void) { return evo_bwd_noalloc_max_rows(); }
 
 int mf_lnl_fwd(const mf_lnl_fwd_args* args, void* stream) {
+  Range nvtx_range("mf_lnl_fwd");
   MF_REQUIRE(args, MF_ERR_BAD_ARG, "args is NULL");
   const mf_lnl_fwd_args& a = *args;
   MF_REQUIRE(a.M >= 0 && a.K > 0 && a.N > 0, MF_ERR_BAD_ARG, "bad sizes M=%lld K=%d N=%d", (long long)a.M, a.K, a.N);
@@ -144,10 +159,11 @@ int mf_lnl_fwd(const mf_lnl_fwd_args* args, void* stream) {
 
 size_t mf_lnl_bwd_workspace_bytes(const mf_lnl_bwd_args* args) {
   if (!args) return 0;
-  return lnl_bwd_simt_workspace(*args);
+  return lnl_bwd_workspace(*args);
 }
 
 int mf_lnl_bwd(const mf_lnl_bwd_args* args, void* stream) {
+  Range nvtx_range("mf_lnl_bwd");
   MF_REQUIRE(args, MF_ERR_BAD_ARG, "args is NULL");
   const mf_lnl_bwd_args& a = *args;
   MF_REQUIRE(a.M > 0 && a.K > 0 && a.N > 0, MF_ERR_BAD_ARG, "bad sizes M=%lld K=%d N=%d", (long long)a.M, a.K, a.N);
@@ -159,12 +175,13 @@ int mf_lnl_bwd(const mf_lnl_bwd_args* args, void* stream) {
              a.workspace ? a.workspace_bytes : (size_t)0);
   MF_REQUIRE(((uintptr_t)a.workspace & 255) == 0, MF_ERR_ALIGNMENT, "workspace must be 256-byte aligned");
   int r = check_device(); if (r) return r;
-  r = lnl_bwd_simt(a, static_cast<cudaStream_t>(stream));
+  r = lnl_bwd(a, static_cast<cudaStream_t>(stream));
   if (r == MF_OK) set_last_path(lnl_bwd_runs_on_tc(a) ? "tcgen05" : "simt");
   return r;
 }
 
 int mf_swiglu_fwd(const void* x, void* y, int64_t M, int32_t inner, int32_t dtype, void* stream) {
+  Range nvtx_range("mf_swiglu_fwd");
   MF_REQUIRE(x && y && M >= 0 && inner > 0, MF_ERR_BAD_ARG, "bad swiglu arguments");
   MF_REQUIRE(float_dtype(dtype), MF_ERR_BAD_ARG, "dtype %d is not a floating type", dtype);
   int r = check_device(); if (r) return r;
@@ -172,6 +189,7 @@ int mf_swiglu_fwd(const void* x, void* y, int64_t M, int32_t inner, int32_t dtyp
 }
 
 int mf_swiglu_bwd(const void* x, const void* dy, void* dx, int64_t M, int32_t inner, int32_t dtype, void* stream) {
+  Range nvtx_range("mf_swiglu_bwd");
   MF_REQUIRE(x && dy && dx && M >= 0 && inner > 0, MF_ERR_BAD_ARG, "bad swiglu arguments");
   MF_REQUIRE(float_dtype(dtype), MF_ERR_BAD_ARG, "dtype %d is not a floating type", dtype);
   int r = check_device(); if (r) return r;
@@ -189,6 +207,7 @@ size_t mf_transition_fwd_workspace_bytes(const mf_transition_fwd_args* args) {
 }
 
 int mf_transition_fwd(const mf_transition_fwd_args* args, void* stream) {
+  Range nvtx_range("mf_transition_fwd");
   MF_REQUIRE(args, MF_ERR_BAD_ARG, "args is NULL");
   const mf_transition_fwd_args& a = *args;
   MF_REQUIRE(a.M > 0 && a.dim > 0 && a.inner > 0, MF_ERR_BAD_ARG, "bad sizes");
@@ -211,10 +230,11 @@ int mf_transition_fwd(const mf_transition_fwd_args* args, void* stream) {
 
 size_t mf_transition_bwd_workspace_bytes(const mf_transition_bwd_args* args) {
   if (!args) return 0;
-  return transition_bwd_simt_workspace(*args);
+  return transition_bwd_workspace(*args);
 }
 
 int mf_transition_bwd(const mf_transition_bwd_args* args, void* stream) {
+  Range nvtx_range("mf_transition_bwd");
   MF_REQUIRE(args, MF_ERR_BAD_ARG, "args is NULL");
   const mf_transition_bwd_args& a = *args;
   MF_REQUIRE(a.M > 0 && a.dim > 0 && a.inner > 0, MF_ERR_BAD_ARG, "bad sizes");
@@ -227,7 +247,7 @@ int mf_transition_bwd(const mf_transition_bwd_args* args, void* stream) {
              a.workspace ? a.workspace_bytes : (size_t)0);
   MF_REQUIRE(((uintptr_t)a.workspace & 255) == 0, MF_ERR_ALIGNMENT, "workspace must be 256-byte aligned");
   int r = check_device(); if (r) return r;
-  r = transition_bwd_simt(a, static_cast<cudaStream_t>(stream));
+  r = transition_bwd(a, static_cast<cudaStream_t>(stream));
   if (r == MF_OK) set_last_path(transition_bwd_runs_on_tc(a) ? "tcgen05" : "simt");
   return r;
 }

@@ -137,20 +137,20 @@ size_t evo_bwd_ws_workspace(const mf_evo_bwd_args& a);
 int lnl_fwd_simt(const mf_lnl_fwd_args& a, cudaStream_t st);
 bool lnl_fwd_tc_supported(const mf_lnl_fwd_args& a);
 int lnl_fwd_tc(const mf_lnl_fwd_args& a, cudaStream_t st);
-int lnl_bwd_simt(const mf_lnl_bwd_args& a, cudaStream_t st);   // picks tensor-core GEMMs when lnl_bwd_runs_on_tc
+int lnl_bwd(const mf_lnl_bwd_args& a, cudaStream_t st);   // picks tensor-core GEMMs when lnl_bwd_runs_on_tc
 bool lnl_bwd_runs_on_tc(const mf_lnl_bwd_args& a);
 bool transition_bwd_runs_on_tc(const mf_transition_bwd_args& a);
 bool transition_bwd_fused_ok(const mf_transition_bwd_args& a);
 int transition_bwd_fused(const mf_transition_bwd_args& a, void* g, void* dh, float* dyln, cudaStream_t st);
 int unpermute_dw1(const float* src, float* dst, int dim, int inner, cudaStream_t st);
-size_t lnl_bwd_simt_workspace(const mf_lnl_bwd_args& a);
+size_t lnl_bwd_workspace(const mf_lnl_bwd_args& a);
 
 int transition_fwd_simt(const mf_transition_fwd_args& a, cudaStream_t st);
 bool transition_fwd_tc_supported(const mf_transition_fwd_args& a);
 int transition_fwd_tc(const mf_transition_fwd_args& a, cudaStream_t st);
-int transition_bwd_simt(const mf_transition_bwd_args& a, cudaStream_t st);
+int transition_bwd(const mf_transition_bwd_args& a, cudaStream_t st);
 size_t transition_fwd_simt_workspace(const mf_transition_fwd_args& a);
-size_t transition_bwd_simt_workspace(const mf_transition_bwd_args& a);
+size_t transition_bwd_workspace(const mf_transition_bwd_args& a);
 
 int swiglu_fwd(const void* x, void* y, int64_t M, int inner, int dtype, cudaStream_t st);
 int swiglu_bwd(const void* x, const void* dy, void* dx, int64_t M, int inner, int dtype, cudaStream_t st);

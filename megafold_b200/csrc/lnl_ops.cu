@@ -1,8 +1,10 @@
-// LayernormLinear, SwiGLU and Transition on CUDA cores (fp32 arithmetic).
+// LayernormLinear, SwiGLU and Transition: launch plans, and the CUDA-core kernels (fp32 arithmetic).
 //
-// These kernels take every shape and dtype; the tensor-core kernels cover the bf16 hot shapes.
-// All reductions over rows (weight, gain and bias gradients) are split into slices whose partial
-// sums are added in a fixed order, so results are bit-reproducible.
+// The forward entry points named *_simt and every kernel in this file run on CUDA cores and take every shape and dtype.
+// lnl_bwd and transition_bwd are the backward launch plans: they choose, per call, between the tensor-core GEMMs
+// (gemm_tc.cuh, transition_bwd_tc.cu) for the 16-bit hot shapes and the CUDA-core GEMMs (gemm_simt.cuh) for the rest.
+// All reductions over rows (weight, gain and bias gradients) are split into slices whose partial sums are added in a
+// fixed order, so results are bit-reproducible.
 #include "gemm_simt.cuh"
 #include "gemm_tc.cuh"
 
@@ -542,7 +544,7 @@ int lnl_fwd_simt(const mf_lnl_fwd_args& a, cudaStream_t st) {
   return MF_OK;
 }
 
-size_t lnl_bwd_simt_workspace(const mf_lnl_bwd_args& a) {
+size_t lnl_bwd_workspace(const mf_lnl_bwd_args& a) {
   // the larger of the two paths, so that the answer does not depend on pointer alignment
   const size_t simt = lnl_bwd_core_bytes(a.M, a.K, a.N, true, false, a.dtype);
   const size_t tc = lnl_bwd_use_tc(a) ? lnl_bwd_core_bytes(a.M, a.K, a.N, true, true, a.dtype) : 0;
@@ -551,7 +553,7 @@ size_t lnl_bwd_simt_workspace(const mf_lnl_bwd_args& a) {
 bool lnl_bwd_runs_on_tc(const mf_lnl_bwd_args& a) { return lnl_bwd_use_tc(a); }
 bool transition_bwd_runs_on_tc(const mf_transition_bwd_args& a) { return transition_bwd_use_tc(a); }
 
-int lnl_bwd_simt(const mf_lnl_bwd_args& a, cudaStream_t st) {
+int lnl_bwd(const mf_lnl_bwd_args& a, cudaStream_t st) {
   Carver ws(a.workspace);
   const bool tc = lnl_bwd_use_tc(a);
   MF_DISPATCH_FLOAT(a.dtype, T, {
@@ -632,7 +634,7 @@ int transition_fwd_simt(const mf_transition_fwd_args& a, cudaStream_t st) {
   return MF_OK;
 }
 
-size_t transition_bwd_simt_workspace(const mf_transition_bwd_args& a) {
+size_t transition_bwd_workspace(const mf_transition_bwd_args& a) {
   size_t simt = align_up((size_t)a.M * 2 * a.inner * dtype_size(a.dtype), 256);     // h, then dh in place
   int S = dw_splits(a.dim, a.inner, a.M);
   if (S > 1) simt += align_up(sizeof(float) * (size_t)S * a.dim * a.inner, 256);     // dw2 slices
@@ -706,7 +708,7 @@ int transition_bwd_fused_path(const mf_transition_bwd_args& a, cudaStream_t st) 
   return unpermute_dw1(dw1p, a.dw1, a.dim, I, st);
 }
 
-int transition_bwd_simt(const mf_transition_bwd_args& a, cudaStream_t st) {
+int transition_bwd(const mf_transition_bwd_args& a, cudaStream_t st) {
   if (transition_bwd_use_tc(a)) {
     if (transition_bwd_fused_ok(a))
       return a.dtype == MF_BF16 ? transition_bwd_fused_path<__nv_bfloat16>(a, st) : transition_bwd_fused_path<__half>(a, st);

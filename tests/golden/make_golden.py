@@ -177,4 +177,6 @@ def main(ref):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: python tests/golden/make_golden.py /path/to/reference   (the reference checkout is not looked for anywhere else)")
+    main(sys.argv[1])
