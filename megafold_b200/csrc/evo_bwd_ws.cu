@@ -1043,9 +1043,9 @@ int launch_bwd_ws(const mf_evo_bwd_args& a, cudaStream_t st) {
 }  // namespace
 
 bool evo_bwd_ws_shape_ok(int L, int D) {
-  // head sizes above 32 would need more shared memory than an SM has with this tiling; rows longer than 1024 tokens
-  // more than it has for the per-row statistics
-  return D <= 32 && L <= 1024;
+  // head sizes above 32 would need more shared memory than an SM has with this tiling; rows of more than six query tiles
+  // stream dQ through an fp32 accumulator in global memory, which has been validated up to 2048 tokens
+  return D <= 32 && L <= 2048;
 }
 
 size_t evo_bwd_ws_workspace(const mf_evo_bwd_args& a) { return plan_bwd(a).total; }

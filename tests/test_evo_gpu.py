@@ -302,7 +302,8 @@ def test_host_pipeline_matches_device_call():
     assert pipe.graph is not None, "the three-stream schedule was not captured into a CUDA graph"
 
 
-@pytest.mark.parametrize("B,N,L,H,D", [(1, 2, 1000, 2, 32), (1, 150, 800, 1, 32), (1, 3, 1024, 1, 24)])
+@pytest.mark.parametrize("B,N,L,H,D", [(1, 2, 1000, 2, 32), (1, 150, 800, 1, 32), (1, 3, 1024, 1, 24), (1, 2, 1536, 2, 32),
+                                       (1, 1, 2048, 2, 16)])
 def test_long_rows_stream_dq(B, N, L, H, D):
     """More than six query tiles: the backward kernel no longer keeps every dQ accumulator on chip but adds each block's
     product to an fp32 accumulator in global memory (with and without the key tiles spread over CTAs)."""
