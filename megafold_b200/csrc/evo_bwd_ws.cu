@@ -76,7 +76,7 @@ __device__ __forceinline__ void bulk_load_1d(void* dst, const void* src, uint32_
                ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
 
-// One thread per (b, n, i < lpad, h): delta = sum_d dO * O (16-byte loads; D is a multiple of 8), the XQ row of query i
+// One thread per (b, n, h, i < lpad): delta = sum_d dO * O (16-byte loads; D is a multiple of 8), the XQ row of query i
 // and, for h == 0, the XK row of key i.  flags[bnh] is raised when the row (b, n) has every key masked (lse = -FLT_MAX).
 template <typename T>
 __global__ void evo_extras_ws_kernel(const T* __restrict__ o, const T* __restrict__ d_o, const float* __restrict__ lse,
@@ -85,7 +85,9 @@ __global__ void evo_extras_ws_kernel(const T* __restrict__ o, const T* __restric
                                      int64_t rows_pad, int N, int L, int lpad, int H, int D) {
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= rows_pad) return;
-  const int h = (int)(idx % H); const int64_t t = idx / H; const int i = (int)(t % lpad); const int64_t bn = t / lpad;
+  // consecutive threads take consecutive queries of one (b, n, h): their lse reads and term-tile rows are contiguous, and
+  // each reads whole 64-byte pieces of o / dO
+  const int i = (int)(idx % lpad); const int64_t t = idx / lpad; const int h = (int)(t % H); const int64_t bn = t / H;
   const int64_t bnh = bn * H + h;
   const float sqrt_d = sqrtf((float)D);
   const __nv_bfloat16 one = __float2bfloat16_rn(1.f), zero = __float2bfloat16_rn(0.f);

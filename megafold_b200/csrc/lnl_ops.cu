@@ -409,7 +409,8 @@ int dw_splits(int K, int N, int64_t M) {
   return pick_splits(tiles, M);
 }
 
-constexpr int kRowBlocks = 296;   // blocks of the fused row pass (two per SM)
+constexpr int kRowBlocks = 1184;  // blocks of the fused row pass: eight per SM (64 resident warps), because a warp keeps only one row in
+                                  // flight and the pass is bound by memory latency, not bandwidth, with fewer
 
 // Can the backward GEMMs of a LayernormLinear with these sizes run on the tensor cores?
 bool lnl_bwd_core_tc_ok(int64_t M, int K, int N, int dtype, bool has_ln, const void* x, const void* w, const void* dy,
