@@ -300,6 +300,30 @@ int colsum(const char* name, F f, float* out, float* scratch, int64_t M, int nco
   return after_launch("sum_slices_kernel");
 }
 
+// Column sums of a small fp32 matrix [rows, ncols] (the per-block partial sums of a row pass) in one launch and in a fixed
+// order: columns [0, split) go to out_a, the others to out_b (which may be NULL).
+__global__ void __launch_bounds__(1024)
+colsum_small_kernel(const float* __restrict__ p, int rows, int ncols, float* __restrict__ out_a, float* __restrict__ out_b, int split) {
+  __shared__ float red[32][33];
+  const int c = blockIdx.x * 32 + threadIdx.x;
+  float s = 0.f;
+  if (c < ncols)
+    for (int m = threadIdx.y; m < rows; m += 32) s += p[(int64_t)m * ncols + c];
+  red[threadIdx.y][threadIdx.x] = s;
+  __syncthreads();
+  if (threadIdx.y == 0 && c < ncols) {
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) t += red[i][threadIdx.x];
+    if (c < split) out_a[c] = t;
+    else if (out_b) out_b[c - split] = t;
+  }
+}
+int colsum_small(const char* name, const float* p, int rows, int ncols, float* out_a, float* out_b, int split, cudaStream_t st) {
+  colsum_small_kernel<<<(ncols + 31) / 32, dim3(32, 32), 0, st>>>(p, rows, ncols, out_a, out_b, split);
+  return after_launch(name);
+}
+
 int sum_slices(const float* part, float* out, int64_t n, int slices, cudaStream_t st) {
   sum_slices_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(part, out, n, slices);
   return after_launch("sum_slices_kernel");
@@ -451,9 +475,8 @@ int lnl_bwd_core(int64_t M, int K, int N, const T* x, const T* gain, const T* sh
       if (kj == 1) MF_ROWS(1); else if (kj == 2) MF_ROWS(2); else if (kj == 3) MF_ROWS(3); else MF_ROWS(4);
 #undef MF_ROWS
       MF_LAUNCHED("ln_bwd_rows_fused_kernel");
-      r = colsum("lnl_bwd_dgain", ColF32{part, 2 * K}, d_ln_w, col_scratch, blocks, K, st);
+      r = colsum_small("lnl_bwd_dgain_dshift", part, blocks, 2 * K, d_ln_w, d_ln_b, K, st);
       if (r) return r;
-      if (d_ln_b) { r = colsum("lnl_bwd_dshift", ColF32{part + K, 2 * K}, d_ln_b, col_scratch, blocks, K, st); if (r) return r; }
       if (db) {
         if (N <= 2048) {
           int cb = (int)((M + 63) / 64); if (cb > kRowBlocks) cb = kRowBlocks;
@@ -463,7 +486,7 @@ int lnl_bwd_core(int64_t M, int K, int N, const T* x, const T* gain, const T* sh
           const int lanes = 256 / (N / 8);
           colsum16_partial_kernel<T><<<cb, 256, sizeof(float) * lanes * N, st>>>(dy, dpart, M, N, rows);
           MF_LAUNCHED("colsum16_partial_kernel");
-          r = colsum("lnl_bwd_dbias", ColF32{dpart, N}, db, col_scratch, cb, N, st);
+          r = colsum_small("lnl_bwd_dbias", dpart, cb, N, db, nullptr, N, st);
         } else {
           r = colsum("lnl_bwd_dbias", ColT<T>{dy, N}, db, col_scratch, M, N, st);
         }
