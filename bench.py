@@ -452,6 +452,21 @@ def extras(dev, steps=5):
         "tflops": 14.0 * B3 * H3 * L3 * L3 * D3 / ((ms_f + ms_b) * 1e-3) / 1e12,
         "hbm_gbs_algorithmic": bytes3 / ((ms_f + ms_b) * 1e-3) / 1e9, "hbm_frac_of_measured": bytes3 / ((ms_f + ms_b) * 1e-3) / 1e9 / peaks["hbm"]}
     del c, o, lse
+    # the shape of the reference's own kernel benchmark (B = 4, H = 32, D = 64, one row, L = 384, 16-bit): forward on the
+    # general tensor-core kernel, backward on the CUDA-core kernels (the tensor-core backward covers head sizes up to 32)
+    c = {k: v.to(dev) for k, v in workloads.single_attention(L=384, H=32, D=64, B=4, drop=0.0).items()}
+    o, lse = mfb.evo_attention_forward(c["q"], c["k"], c["v"], c["mask"], c["bias"])
+    pf = _lib.last_path()
+    ms_f = _time_cuda(lambda: mfb.evo_attention_forward(c["q"], c["k"], c["v"], c["mask"], c["bias"]), steps, 2)
+    ms_b = _time_cuda(lambda: mfb.evo_attention_backward(c["d_out"], c["q"], c["k"], c["v"], c["mask"], c["bias"], o, lse), 3, 1)
+    fl = 4.0 * 4 * 32 * 384 * 384 * 64
+    out["reference_benchmark_shape_B4_H32_D64_L384"] = {
+        "ms_forward": ms_f, "ms_backward": ms_b, "path_forward": pf, "path_backward": _lib.last_path(),
+        "tflops_forward": fl / (ms_f * 1e-3) / 1e12, "tflops_backward": 2.5 * fl / (ms_b * 1e-3) / 1e12,
+        "tflops_fwd_bwd": 3.5 * fl / ((ms_f + ms_b) * 1e-3) / 1e12,
+        "reference_comment_block": "Triton fp16 at L=384: 40.7 fwd / 11.2 bwd / 14.0 fwd+bwd TFLOP/s, hardware not stated "
+                                   "(benchmarks/evoattention_speed.py:123-153)"}
+    del c, o, lse
     # LayernormLinear 128 -> 512 on the [384*384, 128] pair representation (the projection around config 2)
     c = {k: (v.to(dev) if v is not None else None) for k, v in workloads.layernorm_linear().items()}
     y, mean, rstd = layernorm_linear_forward(c["x"], c["w"], c["b"], c["ln_w"], c["ln_b"])
