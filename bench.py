@@ -453,7 +453,7 @@ def extras(dev, steps=5):
         "hbm_gbs_algorithmic": bytes3 / ((ms_f + ms_b) * 1e-3) / 1e9, "hbm_frac_of_measured": bytes3 / ((ms_f + ms_b) * 1e-3) / 1e9 / peaks["hbm"]}
     del c, o, lse
     # the shape of the reference's own kernel benchmark (B = 4, H = 32, D = 64, one row, L = 384, 16-bit): forward on the
-    # general tensor-core kernel, backward on the CUDA-core kernels (the tensor-core backward covers head sizes up to 32)
+    # general tensor-core kernel, backward on the warp-specialised kernels with the head size taken as two halves of 32
     c = {k: v.to(dev) for k, v in workloads.single_attention(L=384, H=32, D=64, B=4, drop=0.0).items()}
     o, lse = mfb.evo_attention_forward(c["q"], c["k"], c["v"], c["mask"], c["bias"])
     pf = _lib.last_path()

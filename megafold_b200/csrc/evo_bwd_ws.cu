@@ -37,8 +37,21 @@ constexpr int kThreads = (kComputeWarps + 4) * 32;
 constexpr int kTileB = 128 * 64;    // [128 x 32] 16-bit operand tile, 64-byte rows, 64B swizzle
 constexpr int kAtomB = 128 * 128;   // [128 x 64] 16-bit tile, 128-byte rows, 128B swizzle (bias^T atoms, dS^T atoms)
 constexpr int kDP = 32;             // padded head size
-constexpr int kStageB = 2 * kTileB + 4096;             // main kernel: a (K, V, XK) or (Q, dO, XQ) stage
-constexpr int kDbStageB = 4 * kTileB + 2 * 4096;      // dBias kernel: one row's Q, dO, K, V tiles and its two rank-one term tiles
+// Head sizes up to 64 are handled as NH = 1 or 2 halves of 32 columns: every operand is loaded as NH tiles of [128 x 32]
+// (the same layout whatever the head size), the score products run over 2 * NH slices of 16, and each half has its own
+// 32 columns in the dK, dV and dQ accumulators.  With two halves the stages are twice as large, so there are fewer:
+template <int NH> struct Geo {
+  static constexpr int kStageB = 2 * NH * kTileB + 4096;            // main kernel: a (K, V, XK) or (Q, dO, XQ) stage
+  static constexpr int kDbStageB = 4 * NH * kTileB + 2 * 4096;      // dBias kernel: one row's Q, dO, K, V tiles and its two term tiles
+  static constexpr int NQ = NH == 1 ? 3 : 2;       // (Q, dO, XQ) stages
+  static constexpr int NKV = NH == 1 ? 2 : 1;      // (K, V, XK) stages
+  static constexpr int NB = NH == 1 ? 3 : 2;       // bias^T atoms
+  static constexpr int NS = NH == 1 ? 3 : 2;       // dBias kernel: operand stages
+  static constexpr size_t kMainSmem = 1024 + 4 * (size_t)kAtomB + NB * (size_t)kAtomB + (NQ + NKV) * (size_t)kStageB + 2048 + kXTileB;
+  static constexpr size_t kDbSmem = 1024 + 2 * (size_t)kAtomB + NS * (size_t)kDbStageB + 2048 + kXTileB;
+};
+static_assert(Geo<2>::kMainSmem + 1024 <= 227 * 1024 && Geo<1>::kMainSmem + 1024 <= 227 * 1024, "shared memory of the main kernel");
+static_assert(Geo<2>::kDbSmem + 1024 <= 227 * 1024 && Geo<1>::kDbSmem + 1024 <= 227 * 1024, "shared memory of the dBias kernel");
 // registers per thread: at launch (640 threads) / compute warps / helper warps after setmaxnreg.  The raise of the
 // compute warps can only draw on what the helper warps release inside the CTA - otherwise it never returns.
 constexpr int kLaunchRegs = 96, kComputeRegs = 104, kHelperRegs = 64;
@@ -199,18 +212,19 @@ __device__ __forceinline__ void p_and_ds(const uint32_t (&sr)[16], const uint32_
   }
 }
 
-template <typename T, typename TB, bool DQS>      // DQS: dQ streamed block by block through global memory
+template <typename T, typename TB, bool DQS, int NH>      // DQS: dQ streamed block by block through global memory
 __global__ void __launch_bounds__(kThreads, 1)
 evo_bwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mk,
                   const __grid_constant__ CUtensorMap mv, const __grid_constant__ CUtensorMap mg,
                   const __grid_constant__ CUtensorMap mbt, const BwdWsP p MF_TRACE_PARAM) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  constexpr int kStageB = Geo<NH>::kStageB, NQ = Geo<NH>::NQ, NKV = Geo<NH>::NKV, NB = Geo<NH>::NB;
   uint8_t* sDS = smem;                          // [2 blocks][2 atoms]: dS^T tiles for the dQ product
-  uint8_t* sBT = sDS + 4 * kAtomB;              // bias^T atoms, ring of 3
-  uint8_t* sKV = sBT + 3 * kAtomB;              // [2 stages][K, V, XK]
-  uint8_t* sQD = sKV + 2 * kStageB;             // [3 stages][Q, dO, XQ]
-  uint8_t* sI = sQD + 3 * kStageB;              // alpha * I, two terms
+  uint8_t* sBT = sDS + 4 * kAtomB;              // bias^T atoms, ring of NB
+  uint8_t* sKV = sBT + NB * kAtomB;             // [NKV stages][K halves, V halves, XK]
+  uint8_t* sQD = sKV + NKV * kStageB;           // [NQ stages][Q halves, dO halves, XQ]
+  uint8_t* sI = sQD + NQ * kStageB;             // alpha * I, two terms
   uint8_t* sXC = sI + 2048;                     // constant tile of the -delta term
 
   __shared__ Bars bar;
@@ -226,13 +240,13 @@ evo_bwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
       mbar_init(&bar.buf_free[i], 1);
       mbar_init(&bar.ds_written[i], kComputeWarps); mbar_init(&bar.dq_done[i], 1);
       mbar_init(&bar.item_done[i], kComputeWarps);
-      mbar_init(&bar.dq_drained[i], 4);
+      mbar_init(&bar.dq_drained[i], 4 * NH);
     }
     for (int i = 0; i < 3; ++i) {
       mbar_init(&bar.qd_full[i], 1); mbar_init(&bar.qd_empty[i], 1); mbar_init(&bar.bt_full[i], 1); mbar_init(&bar.bt_empty[i], 1);
     }
     mbar_init(&bar.kv_done, 1);
-    mbar_init(&bar.kv_drained, 8);
+    mbar_init(&bar.kv_drained, 8 * NH);
     mbar_fence_init();
     prefetch_tmap(&mq); prefetch_tmap(&mk); prefetch_tmap(&mv); prefetch_tmap(&mg); prefetch_tmap(&mbt);
   }
@@ -250,8 +264,9 @@ evo_bwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
   const bool dbuf = p.dbuf != 0;
   // TMEM: team t's scores S''^T at t*128 + [0,64), dP^T at t*128 + [64,128) (P^T / dS^T are packed over them);
   // dK | dV accumulators (one or two sets); dQ accumulators (one per query tile, or two used in turn when streaming)
-  const uint32_t tKV = tm0 + 256, tDQ = tm0 + 256 + (dbuf ? 128 : 64);
-  const uint32_t kv_set = dbuf ? 64 : 0;         // column distance between the two dK|dV accumulator sets
+  // (each accumulator has 32 columns per head half: dK = [0, 32 NH), dV = [32 NH, 64 NH) of a set)
+  const uint32_t tKV = tm0 + 256, tDQ = tm0 + 256 + (dbuf ? 128 : 64) * NH;
+  const uint32_t kv_set = dbuf ? 64 * NH : 0;    // column distance between the two dK|dV accumulator sets
   // work item = (b, n, h, range of key tiles)
   auto item_range = [&](int item, int& jt0, int& jt1) {
     const int sp = item % p.ksplit;
@@ -269,19 +284,21 @@ evo_bwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
     const uint32_t tST = tm0 + team * 128 + ch * 32 + lane_addr, tDP = tST + 64;
     MF_TRACE_DECL(tr, team, blockIdx.x == 0 && (warp == 0 || warp == 8) && lane == 0);
 
-    // dK (scaled) and dV rows of key `j` from accumulator set `kc`: warps 0-3 write dK, warps 4-7 dV
+    // dK (scaled) and dV rows of key `j` from accumulator set `kc`: the warps with w < 2 NH take one (dK or dV, head
+    // half) each
+    const int kv_which = NH == 1 ? w : (w >> 1), kv_hh = NH == 1 ? 0 : (w & 1);
     auto store_kv = [&](uint32_t kc, int j, int b, int n, int h) {
       tc_fence_after();
       uint32_t o32[32];
-      tmem_ld32(tKV + (kc & 1) * kv_set + (w == 0 ? 0 : 32) + lane_addr, o32);
+      tmem_ld32(tKV + (kc & 1) * kv_set + kv_which * 32 * NH + kv_hh * 32 + lane_addr, o32);
       tmem_ld_wait();
       tc_fence_before();
       if (j < p.L && !*abort_flag) {
-        const float sc = w == 0 ? p.scale : 1.f;
-        T* orow = static_cast<T*>(w == 0 ? p.dk : p.dv) + ((((int64_t)b * p.N + n) * p.L + j) * p.H + h) * p.D;
+        const float sc = kv_which == 0 ? p.scale : 1.f;
+        T* orow = static_cast<T*>(kv_which == 0 ? p.dk : p.dv) + ((((int64_t)b * p.N + n) * p.L + j) * p.H + h) * p.D + kv_hh * 32;
 #pragma unroll
         for (int d8 = 0; d8 < 4; ++d8) {
-          if (d8 * 8 < p.D) {
+          if (kv_hh * 32 + d8 * 8 < p.D) {
             uint4 v;
             v.x = Pack2<T>::pack(__uint_as_float(o32[d8 * 8]) * sc, __uint_as_float(o32[d8 * 8 + 1]) * sc);
             v.y = Pack2<T>::pack(__uint_as_float(o32[d8 * 8 + 2]) * sc, __uint_as_float(o32[d8 * 8 + 3]) * sc);
@@ -293,24 +310,27 @@ evo_bwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
       }
     };
     // rows of a dQ accumulator (TMEM lane = query) added, scaled, to the fp32 dQ rows in global memory
-    auto add_dq = [&](uint32_t tacc, int it2, int b, int n, int h) {
+    auto add_dq = [&](uint32_t tacc, int it2, int hh, int b, int n, int h) {
       tc_fence_after();
       uint32_t o32[32];
-      tmem_ld32(tacc + lane_addr, o32);
+      tmem_ld32(tacc + hh * 32 + lane_addr, o32);
       tmem_ld_wait();
       tc_fence_before();
       const int i = it2 * kT + r;
       if (i < p.L && !*abort_flag) {
-        float* arow = p.dq_acc + ((((int64_t)b * p.N + n) * p.L + i) * p.H + h) * p.D;
+        float* arow = p.dq_acc + ((((int64_t)b * p.N + n) * p.L + i) * p.H + h) * p.D + hh * 32;
 #pragma unroll
         for (int d4 = 0; d4 < 8; ++d4)
-          if (d4 * 4 < p.D)
+          if (hh * 32 + d4 * 4 < p.D)
             asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(arow + d4 * 4),
                          "f"(__uint_as_float(o32[d4 * 4]) * p.scale), "f"(__uint_as_float(o32[d4 * 4 + 1]) * p.scale),
                          "f"(__uint_as_float(o32[d4 * 4 + 2]) * p.scale), "f"(__uint_as_float(o32[d4 * 4 + 3]) * p.scale) : "memory");
       }
     };
 
+    // streamed dQ: which warps drain the accumulator of block g2, and which head half each takes
+    const int dq_hh = NH == 1 ? 0 : (w & 1);
+    auto dq_mine = [&](uint32_t g2) { return NH == 1 ? w == (int)(g2 & 3) : (w >> 1) == (int)(g2 & 1); };
     uint32_t g = 0;                 // full blocks seen by this CTA (both teams count every block)
     uint32_t kv_cnt = 0;            // (item, j) pairs so far
     int item_no = 0;
@@ -368,16 +388,16 @@ evo_bwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
           // ---- streamed dQ: the product of the previous block sits in accumulator (g - 1) & 1; the four warps with
           // w == (g - 1) & 3 add it to global memory and hand the accumulator back
           if constexpr (DQS) {
-            if (dqp_it >= 0 && w == (int)(dqp_g & 3)) {
+            if (dqp_it >= 0 && dq_mine(dqp_g)) {
               wait_or_flag(&bar.dq_done[dqp_g & 1], (dqp_g >> 1) & 1, abort_flag);
-              add_dq(tDQ + (dqp_g & 1) * 32, dqp_it, dqp_b, dqp_n, dqp_h);
+              add_dq(tDQ + (dqp_g & 1) * 32 * NH, dqp_it, dq_hh, dqp_b, dqp_n, dqp_h);
               __syncwarp();
               if (lane == 0) mbar_arrive(&bar.dq_drained[dqp_g & 1]);
             }
             dqp_it = it; dqp_g = g; dqp_b = b; dqp_n = n; dqp_h = h;
           }
           // ---- dK_j, dV_j of the key tile that finished one block ago (warps 0-7)
-          if (pend_j >= 0 && w < 2) {
+          if (pend_j >= 0 && w < 2 * NH) {
             wait_or_flag(&bar.kv_done, pend_kc & 1, abort_flag);
             store_kv(pend_kc, pend_j, pend_b, pend_n, pend_h);
             if (!dbuf) { __syncwarp(); if (lane == 0) mbar_arrive(&bar.kv_drained); }
@@ -388,7 +408,7 @@ evo_bwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
       }
       // ---- end of the item: the last key tile's dK/dV, the last streamed dQ, or every query tile's dQ
       tr(7);
-      if (pend_j >= 0 && w < 2) {
+      if (pend_j >= 0 && w < 2 * NH) {
         wait_or_flag(&bar.kv_done, pend_kc & 1, abort_flag);
         store_kv(pend_kc, pend_j, pend_b, pend_n, pend_h);
         if (!dbuf) { __syncwarp(); if (lane == 0) mbar_arrive(&bar.kv_drained); }
@@ -397,28 +417,29 @@ evo_bwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
       const uint32_t gl = g - 1;
       wait_or_flag(&bar.dq_done[gl & 1], (gl >> 1) & 1, abort_flag);
       if constexpr (DQS) {
-        if (dqp_it >= 0 && w == (int)(dqp_g & 3)) {
-          add_dq(tDQ + (dqp_g & 1) * 32, dqp_it, dqp_b, dqp_n, dqp_h);
+        if (dqp_it >= 0 && dq_mine(dqp_g)) {
+          add_dq(tDQ + (dqp_g & 1) * 32 * NH, dqp_it, dq_hh, dqp_b, dqp_n, dqp_h);
           __syncwarp();
           if (lane == 0) mbar_arrive(&bar.dq_drained[dqp_g & 1]);
         }
         dqp_it = -1;
       } else {
-        for (int it = w; it < nt; it += 4) {
+        for (int u = w; u < nt * NH; u += 4) {          // one (query tile, head half) accumulator per turn
+          const int it = u / NH, hh = u - it * NH;
           if (p.ksplit > 1) {
-            add_dq(tDQ + it * 32, it, b, n, h);
+            add_dq(tDQ + it * 32 * NH, it, hh, b, n, h);
           } else {
             tc_fence_after();
             uint32_t o32[32];
-            tmem_ld32(tDQ + it * 32 + lane_addr, o32);
+            tmem_ld32(tDQ + it * 32 * NH + hh * 32 + lane_addr, o32);
             tmem_ld_wait();
             tc_fence_before();
             const int i = it * kT + r;
             if (i < p.L && !*abort_flag) {
-              T* orow = static_cast<T*>(p.dq) + ((((int64_t)b * p.N + n) * p.L + i) * p.H + h) * p.D;
+              T* orow = static_cast<T*>(p.dq) + ((((int64_t)b * p.N + n) * p.L + i) * p.H + h) * p.D + hh * 32;
 #pragma unroll
               for (int d8 = 0; d8 < 4; ++d8) {
-                if (d8 * 8 < p.D) {
+                if (hh * 32 + d8 * 8 < p.D) {
                   uint4 v;
                   v.x = Pack2<T>::pack(__uint_as_float(o32[d8 * 8]) * p.scale, __uint_as_float(o32[d8 * 8 + 1]) * p.scale);
                   v.y = Pack2<T>::pack(__uint_as_float(o32[d8 * 8 + 2]) * p.scale, __uint_as_float(o32[d8 * 8 + 3]) * p.scale);
@@ -444,10 +465,13 @@ evo_bwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
     constexpr uint32_t hi64 = desc_hi(512, kSw64), hi128 = desc_hi(1024, kSw128);
     constexpr uint32_t kTile16 = kTileB / 16, kAtom16 = kAtomB / 16;      // descriptor address units
     constexpr uint32_t hi32 = desc_hi(256, kSw32), kStage16 = kStageB / 16, kX16 = kXTileB / 16;
+    // inside a stage: the NH halves of the first operand (K or Q), the NH halves of the second (V or dO), the term tile
+    constexpr uint32_t kOp2 = NH * kTile16, kTerm16 = 2 * NH * kTile16;
     const uint32_t kv_base = desc_lo(smem_u32(sKV), 16), qd_base = desc_lo(smem_u32(sQD), 16);
     if (warp == kComputeWarps) {
       // ========================================================================== dV / dK issuer: per half block
-      //   dV_j += P^T dO_i,  dK_j += dS^T Q_i   (A = packed P^T / dS^T in TMEM, B = the dO / Q rows of the half, MN-major)
+      //   dV_j += P^T dO_i,  dK_j += dS^T Q_i   (A = packed P^T / dS^T in TMEM, B = the dO / Q rows of the half, MN-major;
+      //   one group of four products per head half, into that half's 32 accumulator columns)
       const uint32_t id_kv = idesc_f16(128, 32, p.fmt, 0, 1);
       MF_TRACE_DECL(tr, 2, blockIdx.x == 0 && lane == 0);
       uint32_t g = 0, kv = 0, qslot = 0;
@@ -455,9 +479,9 @@ evo_bwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
         int jt0, jt1; item_range(item, jt0, jt1);
         for (int jt = jt0; jt < jt1 && !dead(); ++jt, ++kv) {
           if (!dbuf && kv > 0) wait_or_flag(&bar.kv_drained, (kv - 1) & 1, abort_flag);
-          const uint32_t tdk = tKV + (kv & 1) * kv_set, tdv = tdk + 32;
+          const uint32_t tdk = tKV + (kv & 1) * kv_set, tdv = tdk + 32 * NH;
           for (int it = 0; it < nt && !dead(); ++it, ++g) {
-            const uint32_t q_lo = qd_base + qslot * kStage16, do_lo = q_lo + kTile16;
+            const uint32_t q_lo = qd_base + qslot * kStage16, do_lo = q_lo + kOp2;
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
               tr(20);
@@ -465,22 +489,25 @@ evo_bwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
               tc_fence_after();
               tr(21);
               const uint32_t tPt = tm0 + half * 128, tDSt = tPt + 64;
-              const uint32_t b_do = do_lo + half * 256, b_q = q_lo + half * 256;
               const bool first = it == 0 && half == 0;
-              mma_ts_el(tdv, tPt, b_do, hi64, id_kv, !first);
-              mma_ts_el(tdv, tPt + 8, b_do + 64, hi64, id_kv, true);
-              mma_ts_el(tdv, tPt + 32, b_do + 128, hi64, id_kv, true);
-              mma_ts_el(tdv, tPt + 40, b_do + 192, hi64, id_kv, true);
-              mma_ts_el(tdk, tDSt, b_q, hi64, id_kv, !first);
-              mma_ts_el(tdk, tDSt + 8, b_q + 64, hi64, id_kv, true);
-              mma_ts_el(tdk, tDSt + 32, b_q + 128, hi64, id_kv, true);
-              mma_ts_el(tdk, tDSt + 40, b_q + 192, hi64, id_kv, true);
+#pragma unroll
+              for (int hh = 0; hh < NH; ++hh) {
+                const uint32_t b_do = do_lo + hh * kTile16 + half * 256, b_q = q_lo + hh * kTile16 + half * 256;
+                mma_ts_el(tdv + hh * 32, tPt, b_do, hi64, id_kv, !first);
+                mma_ts_el(tdv + hh * 32, tPt + 8, b_do + 64, hi64, id_kv, true);
+                mma_ts_el(tdv + hh * 32, tPt + 32, b_do + 128, hi64, id_kv, true);
+                mma_ts_el(tdv + hh * 32, tPt + 40, b_do + 192, hi64, id_kv, true);
+                mma_ts_el(tdk + hh * 32, tDSt, b_q, hi64, id_kv, !first);
+                mma_ts_el(tdk + hh * 32, tDSt + 8, b_q + 64, hi64, id_kv, true);
+                mma_ts_el(tdk + hh * 32, tDSt + 32, b_q + 128, hi64, id_kv, true);
+                mma_ts_el(tdk + hh * 32, tDSt + 40, b_q + 192, hi64, id_kv, true);
+              }
               tc_commit_el(&bar.buf_free[half]);
               tr(22);
             }
             tc_commit_el(&bar.qd_empty[qslot]);
             if (it == nt - 1) tc_commit_el(&bar.kv_done);
-            if (++qslot == 3) qslot = 0;
+            if (++qslot == NQ) qslot = 0;
           }
         }
       }
@@ -496,18 +523,22 @@ evo_bwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
         // the on-chip dQ accumulators of the previous item must have been read out before they start afresh
         if (!DQS && item_no > 0) wait_or_flag(&bar.item_done[(item_no - 1) & 1], ((item_no - 1) >> 1) & 1, abort_flag);
         for (int jt = jt0; jt < jt1 && !dead(); ++jt, ++kv) {
-          const uint32_t k_lo = kv_base + (kv & 1) * kStage16;
+          const uint32_t k_lo = kv_base + (kv % NKV) * kStage16;
           for (int it = 0; it < nt && !dead(); ++it, ++g) {
             wait_or_flag(&bar.ds_written[g & 1], (g >> 1) & 1, abort_flag);
             if constexpr (DQS) { if (g >= 2) wait_or_flag(&bar.dq_drained[g & 1], ((g >> 1) - 1) & 1, abort_flag); }
             tc_fence_after();
             const uint32_t a_lo = ds_base + (g & 1) * 2 * kAtom16;
-            const uint32_t tacc = tDQ + (DQS ? (g & 1) : it) * 32;
-            mma_ss_el(tacc, a_lo, hi128, k_lo, hi64, id_q, DQS ? false : jt > jt0);
+            const uint32_t tacc = tDQ + (DQS ? (g & 1) : it) * 32 * NH;
 #pragma unroll
-            for (int ks = 1; ks < 8; ++ks) mma_ss_el(tacc, a_lo + ks * (2048 / 16), hi128, k_lo + ks * 64, hi64, id_q, true);
+            for (int hh = 0; hh < NH; ++hh) {          // one group of eight products per head half
+              const uint32_t kh = k_lo + hh * kTile16;
+              mma_ss_el(tacc + hh * 32, a_lo, hi128, kh, hi64, id_q, DQS ? false : jt > jt0);
+#pragma unroll
+              for (int ks = 1; ks < 8; ++ks) mma_ss_el(tacc + hh * 32, a_lo + ks * (2048 / 16), hi128, kh + ks * 64, hi64, id_q, true);
+            }
             tc_commit_el(&bar.dq_done[g & 1]);
-            if (it == nt - 1) tc_commit_el(&bar.kv_empty[kv & 1]);
+            if (it == nt - 1) tc_commit_el(&bar.kv_empty[kv % NKV]);
           }
         }
       }
@@ -526,8 +557,8 @@ evo_bwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
       for (int item = blockIdx.x; item < p.n_items && !dead(); item += gridDim.x) {
         int jt0, jt1; item_range(item, jt0, jt1);
         for (int jt = jt0; jt < jt1 && !dead(); ++jt, ++kv) {
-          wait_or_flag(&bar.kv_full[kv & 1], (kv >> 1) & 1, abort_flag);
-          const uint32_t k_lo = kv_base + (kv & 1) * kStage16, v_lo = k_lo + kTile16, xk_lo = k_lo + 2 * kTile16;
+          wait_or_flag(&bar.kv_full[kv % NKV], (kv / NKV) & 1, abort_flag);
+          const uint32_t k_lo = kv_base + (kv % NKV) * kStage16, v_lo = k_lo + kOp2, xk_lo = k_lo + kTerm16;
           for (int it = 0; it < nt && !dead(); ++it, ++g) {
             wait_or_flag(&bar.qd_full[qslot], quse & 1, abort_flag);
             const uint32_t q_blk = qd_base + qslot * kStage16;
@@ -539,9 +570,12 @@ evo_bwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
               tc_fence_after();
               tr(31);
               const uint32_t tS = tm0 + half * 128, tD = tS + 64;
-              const uint32_t q_lo = q_blk + half * 256, g_lo = q_lo + kTile16, xq_lo = q_blk + 2 * kTile16 + half * (kX16 / 2);
-              mma_ss_el(tS, k_lo, hi64, q_lo, hi64, id_s, false);
-              mma_ss_el(tS, k_lo + 2, hi64, q_lo + 2, hi64, id_s, true);
+              const uint32_t q_lo = q_blk + half * 256, g_lo = q_lo + kOp2, xq_lo = q_blk + kTerm16 + half * (kX16 / 2);
+#pragma unroll
+              for (int hh = 0; hh < NH; ++hh) {
+                mma_ss_el(tS, k_lo + hh * kTile16, hi64, q_lo + hh * kTile16, hi64, id_s, hh > 0);
+                mma_ss_el(tS, k_lo + hh * kTile16 + 2, hi64, q_lo + hh * kTile16 + 2, hi64, id_s, true);
+              }
               mma_ss_el(tS, xk_lo, hi32, xq_lo, hi32, id_x, true);               // + mask_j - lse_i
               const uint32_t a_lo = bt_base + bslot * kAtom16;
 #pragma unroll
@@ -550,15 +584,18 @@ evo_bwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
 #pragma unroll
                 for (int c = 0; c < 4; ++c) mma_ss_el(tS + c * 16, a_lo + c * 2, hi128, i_lo1, hi64, id_b, true);
               }
-              mma_ss_el(tD, v_lo, hi64, g_lo, hi64, id_s, false);
-              mma_ss_el(tD, v_lo + 2, hi64, g_lo + 2, hi64, id_s, true);
+#pragma unroll
+              for (int hh = 0; hh < NH; ++hh) {
+                mma_ss_el(tD, v_lo + hh * kTile16, hi64, g_lo + hh * kTile16, hi64, id_s, hh > 0);
+                mma_ss_el(tD, v_lo + hh * kTile16 + 2, hi64, g_lo + hh * kTile16 + 2, hi64, id_s, true);
+              }
               mma_ss_el(tD, xc_lo, hi32, xq_lo, hi32, id_x, true);               // - delta_i
               tc_commit_el(&bar.sd_ready[half]);
               tc_commit_el(&bar.bt_empty[bslot]);
-              if (++bslot == 3) { bslot = 0; ++buse; }
+              if (++bslot == NB) { bslot = 0; ++buse; }
               tr(32);
             }
-            if (++qslot == 3) { qslot = 0; ++quse; }
+            if (++qslot == NQ) { qslot = 0; ++quse; }
           }
         }
       }
@@ -571,15 +608,18 @@ evo_bwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
         int jt0, jt1; item_range(item, jt0, jt1);
         const int h = bnh % p.H, bn = bnh / p.H, n = bn % p.N, b = bn / p.N;
         for (int jt = jt0; jt < jt1 && !dead(); ++jt, ++kv) {
-          if (kv >= 2) wait_or_flag(&bar.kv_empty[kv & 1], ((kv >> 1) - 1) & 1, abort_flag);
+          if (kv >= (uint32_t)NKV) wait_or_flag(&bar.kv_empty[kv % NKV], ((kv / NKV) - 1) & 1, abort_flag);
           if (dead()) break;
           if (elect_one()) {
-            uint64_t* fb = &bar.kv_full[kv & 1];
-            uint8_t* st = sKV + (kv & 1) * kStageB;
+            uint64_t* fb = &bar.kv_full[kv % NKV];
+            uint8_t* st = sKV + (kv % NKV) * kStageB;
             mbar_expect_tx(fb, kStageB);
-            tma_load_5d(st, &mk, fb, 0, h, jt * kT, n, b);
-            tma_load_5d(st + kTileB, &mv, fb, 0, h, jt * kT, n, b);
-            bulk_load_1d(st + 2 * kTileB, p.xk + ((int64_t)bn * nt + jt) * kXTileB, kXTileB, fb);
+#pragma unroll
+            for (int hh = 0; hh < NH; ++hh) {
+              tma_load_5d(st + hh * kTileB, &mk, fb, hh * kDP, h, jt * kT, n, b);
+              tma_load_5d(st + (NH + hh) * kTileB, &mv, fb, hh * kDP, h, jt * kT, n, b);
+            }
+            bulk_load_1d(st + 2 * NH * kTileB, p.xk + ((int64_t)bn * nt + jt) * kXTileB, kXTileB, fb);
           }
           for (int it = 0; it < nt; ++it, ++g) {
             if (quse >= 1) wait_or_flag(&bar.qd_empty[qslot], (quse - 1) & 1, abort_flag);
@@ -588,11 +628,14 @@ evo_bwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
               uint64_t* fb = &bar.qd_full[qslot];
               uint8_t* st = sQD + qslot * kStageB;
               mbar_expect_tx(fb, kStageB);
-              tma_load_5d(st, &mq, fb, 0, h, it * kT, n, b);
-              tma_load_5d(st + kTileB, &mg, fb, 0, h, it * kT, n, b);
-              bulk_load_1d(st + 2 * kTileB, p.xq + ((int64_t)bnh * nt + it) * kXTileB, kXTileB, fb);
+#pragma unroll
+              for (int hh = 0; hh < NH; ++hh) {
+                tma_load_5d(st + hh * kTileB, &mq, fb, hh * kDP, h, it * kT, n, b);
+                tma_load_5d(st + (NH + hh) * kTileB, &mg, fb, hh * kDP, h, it * kT, n, b);
+              }
+              bulk_load_1d(st + 2 * NH * kTileB, p.xq + ((int64_t)bnh * nt + it) * kXTileB, kXTileB, fb);
             }
-            if (++qslot == 3) { qslot = 0; ++quse; }
+            if (++qslot == NQ) { qslot = 0; ++quse; }
             for (int half = 0; half < 2; ++half) {
               if (buse >= 1) wait_or_flag(&bar.bt_empty[bslot], (buse - 1) & 1, abort_flag);
               if (dead()) break;
@@ -601,16 +644,16 @@ evo_bwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
                 tma_load_4d(sBT + bslot * kAtomB, &mbt, &bar.bt_full[bslot], it * kT + half * kHalf, jt * kT, h, b * p.bias_b_mul);
               }
               ++nbt;
-              if (++bslot == 3) { bslot = 0; ++buse; }
+              if (++bslot == NB) { bslot = 0; ++buse; }
             }
           }
         }
       }
       if (dead() && lane == 0) {
         // the copies already requested must land before the CTA's shared memory is given back (bounded)
-        for (uint32_t back = 0; back < 2 && back < kv; ++back) { const uint32_t c = kv - 1 - back; mbar_wait(&bar.kv_full[c & 1], (c >> 1) & 1); }
-        for (uint32_t back = 0; back < 3 && back < g; ++back) { const uint32_t c = g - 1 - back; mbar_wait(&bar.qd_full[c % 3], (c / 3) & 1); }
-        for (uint32_t back = 0; back < 3 && back < nbt; ++back) { const uint32_t c = nbt - 1 - back; mbar_wait(&bar.bt_full[c % 3], (c / 3) & 1); }
+        for (uint32_t back = 0; back < (uint32_t)NKV && back < kv; ++back) { const uint32_t c = kv - 1 - back; mbar_wait(&bar.kv_full[c % NKV], (c / NKV) & 1); }
+        for (uint32_t back = 0; back < (uint32_t)NQ && back < g; ++back) { const uint32_t c = g - 1 - back; mbar_wait(&bar.qd_full[c % NQ], (c / NQ) & 1); }
+        for (uint32_t back = 0; back < (uint32_t)NB && back < nbt; ++back) { const uint32_t c = nbt - 1 - back; mbar_wait(&bar.bt_full[c % NB], (c / NB) & 1); }
       }
     }
   }
@@ -640,7 +683,7 @@ struct DbBars {
   uint64_t sd_ready[2], loaded[2];
 };
 
-template <typename T, typename TB>
+template <typename T, typename TB, int NH>
 __global__ void __launch_bounds__(kThreads, 1)
 evo_dbias_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mk,
                     const __grid_constant__ CUtensorMap mv, const __grid_constant__ CUtensorMap mg,
@@ -648,8 +691,9 @@ evo_dbias_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constan
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* sBT = smem;                          // two bias^T atoms (queries 0-63 | 64-127 of the tile)
-  uint8_t* sOP = sBT + 2 * kAtomB;              // [3 stages][Q, dO, K, V, XQ, XK]
-  uint8_t* sI = sOP + 3 * kDbStageB;
+  constexpr int kDbStageB = Geo<NH>::kDbStageB, NS = Geo<NH>::NS;
+  uint8_t* sOP = sBT + 2 * kAtomB;              // [NS stages][Q halves, dO halves, K halves, V halves, XQ, XK]
+  uint8_t* sI = sOP + NS * kDbStageB;
   uint8_t* sXC = sI + 2048;                     // constant tile of the -delta term
 
   __shared__ DbBars bar;
@@ -779,11 +823,14 @@ evo_dbias_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constan
           if (g >= 2) wait_or_flag(&bar.loaded[g & 1], ((g >> 1) - 1) & 1, abort_flag);
           tc_fence_after();
           tr(21);
-          const uint32_t q_lo = op_base + stage * kStage16, k_lo = q_lo + 2 * kTile16;
-          const uint32_t xq_lo = q_lo + 4 * kTile16, xk_lo = xq_lo + kXTileB / 16;
+          const uint32_t q_lo = op_base + stage * kStage16, k_lo = q_lo + 2 * NH * kTile16;
+          const uint32_t xq_lo = q_lo + 4 * NH * kTile16, xk_lo = xq_lo + kXTileB / 16;
           const uint32_t tST = tm0 + (g & 1) * 256;
-          mma_ss_el(tST, k_lo, hi64, q_lo, hi64, id_s, false);
-          mma_ss_el(tST, k_lo + 2, hi64, q_lo + 2, hi64, id_s, true);
+#pragma unroll
+          for (int hh = 0; hh < NH; ++hh) {
+            mma_ss_el(tST, k_lo + hh * kTile16, hi64, q_lo + hh * kTile16, hi64, id_s, hh > 0);
+            mma_ss_el(tST, k_lo + hh * kTile16 + 2, hi64, q_lo + hh * kTile16 + 2, hi64, id_s, true);
+          }
           mma_ss_el(tST, xk_lo, hi32, xq_lo, hi32, id_x, true);                 // + mask_j - lse_i
 #pragma unroll
           for (int c = 0; c < 8; ++c) mma_ss_el(tST + c * 16, bt_lo + (c >> 2) * kAtom16 + (c & 3) * 2, hi128, i_lo0, hi64, id_b, true);
@@ -793,7 +840,7 @@ evo_dbias_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constan
           }
           tc_commit_el(&bar.sd_ready[g & 1]);
           tc_commit_el(&bar.op_empty[stage]);
-          if (++stage == 3) { stage = 0; ++suse; }
+          if (++stage == NS) { stage = 0; ++suse; }
           tr(22);
         }
         tc_commit_el(&bar.bt_free);       // every product that reads this unit's bias atoms is complete
@@ -807,15 +854,18 @@ evo_dbias_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constan
           wait_or_flag(&bar.op_full[stage], suse & 1, abort_flag);
           if (g >= 2) wait_or_flag(&bar.loaded[g & 1], ((g >> 1) - 1) & 1, abort_flag);
           tc_fence_after();
-          const uint32_t g_lo = op_base + stage * kStage16 + kTile16, v_lo = g_lo + 2 * kTile16;
-          const uint32_t xq_lo = op_base + stage * kStage16 + 4 * kTile16;
+          const uint32_t g_lo = op_base + stage * kStage16 + NH * kTile16, v_lo = g_lo + 2 * NH * kTile16;
+          const uint32_t xq_lo = op_base + stage * kStage16 + 4 * NH * kTile16;
           const uint32_t tDP = tm0 + (g & 1) * 256 + 128;
-          mma_ss_el(tDP, v_lo, hi64, g_lo, hi64, id_s, false);
-          mma_ss_el(tDP, v_lo + 2, hi64, g_lo + 2, hi64, id_s, true);
+#pragma unroll
+          for (int hh = 0; hh < NH; ++hh) {
+            mma_ss_el(tDP, v_lo + hh * kTile16, hi64, g_lo + hh * kTile16, hi64, id_s, hh > 0);
+            mma_ss_el(tDP, v_lo + hh * kTile16 + 2, hi64, g_lo + hh * kTile16 + 2, hi64, id_s, true);
+          }
           mma_ss_el(tDP, desc_lo(smem_u32(sXC), 16), hi32, xq_lo, hi32, id_x, true);      // - delta_i
           tc_commit_el(&bar.sd_ready[g & 1]);
           tc_commit_el(&bar.op_empty[stage]);
-          if (++stage == 3) { stage = 0; ++suse; }
+          if (++stage == NS) { stage = 0; ++suse; }
         }
       }
     } else if (warp == kComputeWarps + 1) {
@@ -837,19 +887,22 @@ evo_dbias_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constan
             uint64_t* fb = &bar.op_full[stage];
             uint8_t* st = sOP + stage * kDbStageB;
             mbar_expect_tx(fb, kDbStageB);
-            tma_load_5d(st, &mq, fb, 0, x.h, x.it * kT, n, x.b);
-            tma_load_5d(st + kTileB, &mg, fb, 0, x.h, x.it * kT, n, x.b);
-            tma_load_5d(st + 2 * kTileB, &mk, fb, 0, x.h, x.jt * kT, n, x.b);
-            tma_load_5d(st + 3 * kTileB, &mv, fb, 0, x.h, x.jt * kT, n, x.b);
+#pragma unroll
+            for (int hh = 0; hh < NH; ++hh) {
+              tma_load_5d(st + hh * kTileB, &mq, fb, hh * kDP, x.h, x.it * kT, n, x.b);
+              tma_load_5d(st + (NH + hh) * kTileB, &mg, fb, hh * kDP, x.h, x.it * kT, n, x.b);
+              tma_load_5d(st + (2 * NH + hh) * kTileB, &mk, fb, hh * kDP, x.h, x.jt * kT, n, x.b);
+              tma_load_5d(st + (3 * NH + hh) * kTileB, &mv, fb, hh * kDP, x.h, x.jt * kT, n, x.b);
+            }
             const int64_t bn = (int64_t)x.b * p.N + n;
-            bulk_load_1d(st + 4 * kTileB, p.xq + ((bn * p.H + x.h) * nt + x.it) * kXTileB, kXTileB, fb);
-            bulk_load_1d(st + 4 * kTileB + kXTileB, p.xk + (bn * nt + x.jt) * kXTileB, kXTileB, fb);
+            bulk_load_1d(st + 4 * NH * kTileB, p.xq + ((bn * p.H + x.h) * nt + x.it) * kXTileB, kXTileB, fb);
+            bulk_load_1d(st + 4 * NH * kTileB + kXTileB, p.xk + (bn * nt + x.jt) * kXTileB, kXTileB, fb);
           }
-          if (++stage == 3) { stage = 0; ++suse; }
+          if (++stage == NS) { stage = 0; ++suse; }
         }
       }
       if (dead() && lane == 0) {
-        for (uint32_t back = 0; back < 3 && back < g; ++back) { const uint32_t c = g - 1 - back; mbar_wait(&bar.op_full[c % 3], (c / 3) & 1); }
+        for (uint32_t back = 0; back < (uint32_t)NS && back < g; ++back) { const uint32_t c = g - 1 - back; mbar_wait(&bar.op_full[c % NS], (c / NS) & 1); }
         if (un > 0) mbar_wait(&bar.bt_full, (un - 1) & 1);
       }
     }
@@ -910,8 +963,14 @@ BwdPlan plan_bwd(const mf_evo_bwd_args& a) {
   pl.ksplit = bwd_ksplit((int64_t)a.B * a.N * a.H, pl.nt, sms);
   // dQ accumulators of all query tiles next to one set (up to six tiles) or two sets (up to four) of dK/dV accumulators;
   // longer rows stream dQ
-  pl.dq_stream = pl.nt > 6;
-  pl.dbuf = pl.dq_stream || pl.nt <= 4;
+  if (a.D <= kDP) {
+    pl.dq_stream = pl.nt > 6;
+    pl.dbuf = pl.dq_stream || pl.nt <= 4;
+  } else {
+    // two head halves: one set of dK|dV accumulators (128 columns) leaves room for two dQ accumulators of 64 columns
+    pl.dq_stream = pl.nt > 2;
+    pl.dbuf = 0;
+  }
   pl.dq_fp32 = pl.ksplit > 1 || pl.dq_stream;
   const int64_t combos = (int64_t)a.B * a.H * pl.nt * pl.nt;
   int64_t ns = sms / combos;
@@ -930,7 +989,7 @@ BwdPlan plan_bwd(const mf_evo_bwd_args& a) {
   return pl;
 }
 
-template <typename T, typename TB>
+template <typename T, typename TB, int NH>
 int launch_bwd_ws(const mf_evo_bwd_args& a, cudaStream_t st) {
   const BwdPlan pl = plan_bwd(a);
   CUtensorMap mq, mk, mv, mg, mbt;
@@ -990,10 +1049,10 @@ int launch_bwd_ws(const mf_evo_bwd_args& a, cudaStream_t st) {
     p.part = part;
     p.out16 = pl.part_direct && a.dbias_dtype != MF_F32 ? a.d_bias : nullptr;
     p.status = status;
-    const size_t smem = 1024 + 2 * (size_t)kAtomB + 3 * kDbStageB + 2048 + kXTileB;
+    const size_t smem = Geo<NH>::kDbSmem;
     int grid = sm_count();
     if (grid > p.n_units) grid = p.n_units;
-    auto kern = evo_dbias_ws_kernel<T, TT>;
+    auto kern = evo_dbias_ws_kernel<T, TT, NH>;
     MF_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     kern<<<grid, kThreads, smem, st>>>(mq, mk, mv, mg, mbt, p MF_TRACE_ARG);
     MF_LAUNCHED("evo_dbias_ws_kernel");
@@ -1021,15 +1080,15 @@ int launch_bwd_ws(const mf_evo_bwd_args& a, cudaStream_t st) {
     p.xq = xq; p.xk = xk; p.flags = flags;
     p.dq = a.dq; p.dk = a.dk; p.dv = a.dv;
     p.status = status;
-    const size_t smem = 1024 + 4 * (size_t)kAtomB + 3 * kAtomB + 5 * kStageB + 2048 + kXTileB;
+    const size_t smem = Geo<NH>::kMainSmem;
     int grid = sm_count();
     if (grid > p.n_items) grid = p.n_items;
     if (pl.dq_stream) {
-      auto kern = evo_bwd_ws_kernel<T, TT, true>;
+      auto kern = evo_bwd_ws_kernel<T, TT, true, NH>;
       MF_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
       kern<<<grid, kThreads, smem, st>>>(mq, mk, mv, mg, mbt, p MF_TRACE_ARG);
     } else {
-      auto kern = evo_bwd_ws_kernel<T, TT, false>;
+      auto kern = evo_bwd_ws_kernel<T, TT, false, NH>;
       MF_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
       kern<<<grid, kThreads, smem, st>>>(mq, mk, mv, mg, mbt, p MF_TRACE_ARG);
     }
@@ -1045,9 +1104,9 @@ int launch_bwd_ws(const mf_evo_bwd_args& a, cudaStream_t st) {
 }  // namespace
 
 bool evo_bwd_ws_shape_ok(int L, int D) {
-  // head sizes above 32 would need more shared memory than an SM has with this tiling; rows of more than six query tiles
+  // head sizes up to 64 (two halves of 32 columns); rows of more than six query tiles (two with a head size above 32)
   // stream dQ through an fp32 accumulator in global memory, which has been validated up to 2048 tokens
-  return D <= 32 && L <= 2048;
+  return D <= 64 && L <= 2048;
 }
 
 size_t evo_bwd_ws_workspace(const mf_evo_bwd_args& a) { return plan_bwd(a).total; }
@@ -1063,9 +1122,9 @@ size_t evo_bwd_ws_workspace(const mf_evo_bwd_args& a) { return plan_bwd(a).total
 int evo_bwd_ws(const mf_evo_bwd_args& a, cudaStream_t st) {
   int r = MF_OK;
   if (a.dtype == MF_BF16) {
-    MF_DISPATCH_BIAS(a.bias_dtype, TB, { r = launch_bwd_ws<__nv_bfloat16, TB>(a, st); });
+    MF_DISPATCH_BIAS(a.bias_dtype, TB, { r = a.D <= kDP ? launch_bwd_ws<__nv_bfloat16, TB, 1>(a, st) : launch_bwd_ws<__nv_bfloat16, TB, 2>(a, st); });
   } else {
-    MF_DISPATCH_BIAS(a.bias_dtype, TB, { r = launch_bwd_ws<__half, TB>(a, st); });
+    MF_DISPATCH_BIAS(a.bias_dtype, TB, { r = a.D <= kDP ? launch_bwd_ws<__half, TB, 1>(a, st) : launch_bwd_ws<__half, TB, 2>(a, st); });
   }
   return r;
 }

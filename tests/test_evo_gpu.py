@@ -93,7 +93,27 @@ def test_low_precision_against_fp32_oracle(dtype, flags, B, N, L, H, D):
     ref = orc.evo_attention_fwd_bwd(r["q"], r["k"], r["v"], r["mask"], r["bias"], r["d_out"])
     for g_, r_, n in zip(got, ref, NAMES):
         assert_close_lowp(g_, r_, f"{n} ({_lib.last_path()})")
+    # the backward (the last call) took the path asked for: the tensor-core kernels cover every head size up to 64
+    assert _lib.last_path() == ("simt" if flags else "tcgen05")
     # masked keys get exactly zero dK / dV, whatever the precision
+    keep = c["mask"][:, :, 0, 0, :].to(DEV)
+    assert torch.all(got[2][~keep] == 0) and torch.all(got[3][~keep] == 0)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,N,L,H,D", [(1, 2, 128, 2, 64), (1, 2, 256, 1, 64), (1, 3, 200, 2, 48), (1, 1, 768, 4, 64), (2, 1, 384, 8, 64),
+                                       (1, 2, 1100, 1, 56)])
+def test_head_sizes_above_32_on_the_tensor_cores(dtype, B, N, L, H, D):
+    """Head sizes 33..64 (the reference's single-representation attention uses 64) run as two halves of 32 columns in
+    the backward kernels: on-chip dQ accumulators for up to two query tiles, streamed dQ beyond; a head size that is not a
+    multiple of 32 leaves the second half partly empty."""
+    c = make_case(B, N, L, H, D, seed=3 * L + D)
+    got = run_gpu(c, dtype=dtype)
+    assert _lib.last_path() == "tcgen05"
+    r = rounded(c, dtype)
+    ref = orc.evo_attention_fwd_bwd(r["q"], r["k"], r["v"], r["mask"], r["bias"], r["d_out"])
+    for g_, r_, n in zip(got, ref, NAMES):
+        assert_close_lowp(g_, r_, n)
     keep = c["mask"][:, :, 0, 0, :].to(DEV)
     assert torch.all(got[2][~keep] == 0) and torch.all(got[3][~keep] == 0)
 
