@@ -70,6 +70,7 @@ struct BwdWsP {
   int bias_b_mul;
   const uint8_t* xq; const uint8_t* xk;     // rank-one term tiles (evo_extras_ws_kernel)
   const int* flags;                         // per (b, n, h): every key of the row is masked
+  void* dbias_direct;                       // N == 1 and a 16-bit d_pair_bias: dS is the answer, written by this kernel
   void *dq, *dk, *dv;
   int* status;
 };
@@ -371,6 +372,18 @@ evo_bwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&bar.written[team]);
+          // ---- a bias that only this row uses (N = 1): d_pair_bias[b, h, i, j] = dS[i, j], no sum over rows; lanes hold
+          // consecutive keys j, so every store instruction writes 64 contiguous bytes
+          if (p.dbias_direct && j < p.L) {
+            const int i0 = it * kT + team * kHalf + ch * 32;
+            T* dst = static_cast<T*>(p.dbias_direct) + (((int64_t)b * p.H + h) * p.L + i0) * p.L + j;
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+              if (i0 + 2 * c < p.L) *reinterpret_cast<unsigned short*>(dst) = (unsigned short)(dd[c] & 0xffffu);
+              if (i0 + 2 * c + 1 < p.L) *reinterpret_cast<unsigned short*>(dst + p.L) = (unsigned short)(dd[c] >> 16);
+              dst += 2 * (int64_t)p.L;
+            }
+          }
           // ---- dS^T also to the shared-memory tile of this block (A operand of the dQ product), once the dQ
           // product that read this buffer two blocks ago is complete
           if (g >= 2) wait_or_flag(&bar.dq_done[g & 1], ((g >> 1) - 1) & 1, abort_flag);
@@ -1035,8 +1048,11 @@ int launch_bwd_ws(const mf_evo_bwd_args& a, cudaStream_t st) {
 
   float alpha[2];
   const int n_alpha = split_alpha(a.D, bt_dtype, alpha);
+  // With one row per bias (N = 1, single-representation attention) and d_pair_bias in the q/k/v type, dS is the answer:
+  // the dQ/dK/dV kernel writes it and the d_pair_bias kernel is not needed.
+  const bool dbias_direct = a.N == 1 && a.dbias_dtype == a.dtype;
   // ---- dBias first: a caller that all-reduces it over row shards can start while dQ / dK / dV are computed
-  {
+  if (!dbias_direct) {
     DbP p{};
     p.B = a.B; p.N = a.N; p.L = a.L; p.H = a.H; p.D = a.D;
     p.n_t = pl.nt; p.lpad = lpad; p.nsplit = pl.nsplit;
@@ -1065,7 +1081,7 @@ int launch_bwd_ws(const mf_evo_bwd_args& a, cudaStream_t st) {
       MF_LAUNCHED("dbias_finish_kernel");
     }
   }
-  if (a.dbias_ready_event) MF_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(a.dbias_ready_event), st));
+  if (a.dbias_ready_event && !dbias_direct) MF_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(a.dbias_ready_event), st));
   // ---- dQ, dK, dV
   {
     BwdWsP p{};
@@ -1078,6 +1094,7 @@ int launch_bwd_ws(const mf_evo_bwd_args& a, cudaStream_t st) {
     p.n_alpha = n_alpha; p.alpha[0] = alpha[0]; p.alpha[1] = alpha[1];
     p.bias_b_mul = 1;
     p.xq = xq; p.xk = xk; p.flags = flags;
+    p.dbias_direct = dbias_direct ? a.d_bias : nullptr;
     p.dq = a.dq; p.dk = a.dk; p.dv = a.dv;
     p.status = status;
     const size_t smem = Geo<NH>::kMainSmem;
@@ -1093,6 +1110,7 @@ int launch_bwd_ws(const mf_evo_bwd_args& a, cudaStream_t st) {
       kern<<<grid, kThreads, smem, st>>>(mq, mk, mv, mg, mbt, p MF_TRACE_ARG);
     }
     MF_LAUNCHED("evo_bwd_ws_kernel");
+    if (a.dbias_ready_event && dbias_direct) MF_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(a.dbias_ready_event), st));
   }
   if (pl.dq_fp32) {
     cast_rows_ws_kernel<T><<<(unsigned)((n_dq + 255) / 256), 256, 0, st>>>(dq_acc, static_cast<T*>(a.dq), n_dq);
