@@ -68,6 +68,7 @@ struct BwdWsP {
   uint32_t fmt, bfmt;
   int n_alpha; float alpha[2];
   int bias_b_mul;
+  int bias_mn;           // the bias atoms hold the caller's bias as it is ([queries][keys]) and are read MN-major
   const uint8_t* xq; const uint8_t* xk;     // rank-one term tiles (evo_extras_ws_kernel)
   const int* flags;                         // per (b, n, h): every key of the row is masked
   void* dbias_direct;                       // N == 1 and a 16-bit d_pair_bias: dS is the answer, written by this kernel
@@ -559,10 +560,14 @@ evo_bwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
       // ========================================================================== score issuer: per half block
       //   S''^T = K_j Q_i^T + alpha * bias^T,  dP^T = V_j dO_i^T
       const uint32_t id_s = idesc_f16(128, kHalf, p.fmt, 0, 0);
-      const uint32_t id_b = idesc_f16(128, 16, p.bfmt, 0, 0);
+      // The bias atom of a half block is the A operand [128 keys x 64 queries] of four K = 16 products.  Either it holds
+      // rows of a transposed copy of the bias (keys as rows, K-major A), or - when TMA can address the caller's bias - the
+      // bias as it is: two [64 queries x 64 keys] pieces read MN-major (keys contiguous), and no copy is made.
+      const uint32_t id_b = idesc_f16(128, 16, p.bfmt, p.bias_mn ? 1u : 0u, 0);
       const uint32_t id_x = idesc_f16(128, kHalf, 1u, 0, 0);        // the rank-one term tiles are bf16 whatever q/k/v are
       const uint32_t xc_lo = desc_lo(smem_u32(sXC), 16);
-      const uint32_t bt_base = desc_lo(smem_u32(sBT), 16);
+      const uint32_t bt_base = desc_lo(smem_u32(sBT), p.bias_mn ? 8192 : 16);
+      const uint32_t bstep = p.bias_mn ? 2048 / 16 : 2;            // 16 queries further: 16 rows of 128 bytes, or 32 bytes
       const uint32_t i_lo0 = desc_lo(smem_u32(sI), 16), i_lo1 = i_lo0 + 1024 / 16;
       const bool two_terms = p.n_alpha > 1;
       MF_TRACE_DECL(tr, 3, blockIdx.x == 0 && lane == 0);
@@ -592,10 +597,10 @@ evo_bwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
               mma_ss_el(tS, xk_lo, hi32, xq_lo, hi32, id_x, true);               // + mask_j - lse_i
               const uint32_t a_lo = bt_base + bslot * kAtom16;
 #pragma unroll
-              for (int c = 0; c < 4; ++c) mma_ss_el(tS + c * 16, a_lo + c * 2, hi128, i_lo0, hi64, id_b, true);
+              for (int c = 0; c < 4; ++c) mma_ss_el(tS + c * 16, a_lo + c * bstep, hi128, i_lo0, hi64, id_b, true);
               if (two_terms) {
 #pragma unroll
-                for (int c = 0; c < 4; ++c) mma_ss_el(tS + c * 16, a_lo + c * 2, hi128, i_lo1, hi64, id_b, true);
+                for (int c = 0; c < 4; ++c) mma_ss_el(tS + c * 16, a_lo + c * bstep, hi128, i_lo1, hi64, id_b, true);
               }
 #pragma unroll
               for (int hh = 0; hh < NH; ++hh) {
@@ -654,7 +659,12 @@ evo_bwd_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
               if (dead()) break;
               if (elect_one()) {
                 mbar_expect_tx(&bar.bt_full[bslot], kAtomB);
-                tma_load_4d(sBT + bslot * kAtomB, &mbt, &bar.bt_full[bslot], it * kT + half * kHalf, jt * kT, h, b * p.bias_b_mul);
+                if (p.bias_mn) {       // [64 queries x 64 keys] pieces of the bias itself: keys 0-63 | 64-127 of the tile
+                  tma_load_4d(sBT + bslot * kAtomB, &mbt, &bar.bt_full[bslot], jt * kT, it * kT + half * kHalf, h, b * p.bias_b_mul);
+                  tma_load_4d(sBT + bslot * kAtomB + 8192, &mbt, &bar.bt_full[bslot], jt * kT + 64, it * kT + half * kHalf, h, b * p.bias_b_mul);
+                } else {
+                  tma_load_4d(sBT + bslot * kAtomB, &mbt, &bar.bt_full[bslot], it * kT + half * kHalf, jt * kT, h, b * p.bias_b_mul);
+                }
               }
               ++nbt;
               if (++bslot == NB) { bslot = 0; ++buse; }
@@ -684,6 +694,7 @@ struct DbP {
   uint32_t fmt, bfmt;
   int n_alpha; float alpha[2];
   int bias_b_mul;
+  int bias_mn;            // as in BwdWsP
   const uint8_t* xq; const uint8_t* xk;      // rank-one term tiles (evo_extras_ws_kernel)
   float* part;            // fp32 [nsplit][B][H][L][L] partial sums
   void* out16;            // with a single row range and a 16-bit d_bias: the result itself, [B][H][L][L] in the q/k/v type
@@ -821,8 +832,9 @@ evo_dbias_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constan
     const uint32_t id_x = idesc_f16(128, 128, 1u, 0, 0);          // the rank-one term tiles are bf16 whatever q/k/v are
     if (warp == kComputeWarps) {
       // ========================================================================== score issuer: S''^T = K Q^T + alpha * bias^T
-      const uint32_t id_b = idesc_f16(128, 16, p.bfmt, 0, 0);
-      const uint32_t bt_lo = desc_lo(smem_u32(sBT), 16);
+      const uint32_t id_b = idesc_f16(128, 16, p.bfmt, p.bias_mn ? 1u : 0u, 0);      // see the main kernel's score issuer
+      const uint32_t bt_lo = desc_lo(smem_u32(sBT), p.bias_mn ? 8192 : 16);
+      const uint32_t bstep = p.bias_mn ? 2048 / 16 : 2;
       const uint32_t i_lo0 = desc_lo(smem_u32(sI), 16), i_lo1 = i_lo0 + 1024 / 16;
       const bool two_terms = p.n_alpha > 1;
       MF_TRACE_DECL(tr, 2, blockIdx.x == 0 && lane == 0);
@@ -846,10 +858,10 @@ evo_dbias_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constan
           }
           mma_ss_el(tST, xk_lo, hi32, xq_lo, hi32, id_x, true);                 // + mask_j - lse_i
 #pragma unroll
-          for (int c = 0; c < 8; ++c) mma_ss_el(tST + c * 16, bt_lo + (c >> 2) * kAtom16 + (c & 3) * 2, hi128, i_lo0, hi64, id_b, true);
+          for (int c = 0; c < 8; ++c) mma_ss_el(tST + c * 16, bt_lo + (c >> 2) * kAtom16 + (c & 3) * bstep, hi128, i_lo0, hi64, id_b, true);
           if (two_terms) {
 #pragma unroll
-            for (int c = 0; c < 8; ++c) mma_ss_el(tST + c * 16, bt_lo + (c >> 2) * kAtom16 + (c & 3) * 2, hi128, i_lo1, hi64, id_b, true);
+            for (int c = 0; c < 8; ++c) mma_ss_el(tST + c * 16, bt_lo + (c >> 2) * kAtom16 + (c & 3) * bstep, hi128, i_lo1, hi64, id_b, true);
           }
           tc_commit_el(&bar.sd_ready[g & 1]);
           tc_commit_el(&bar.op_empty[stage]);
@@ -890,8 +902,15 @@ evo_dbias_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constan
         if (dead()) break;
         if (elect_one()) {
           mbar_expect_tx(&bar.bt_full, 2 * kAtomB);
-          tma_load_4d(sBT, &mbt, &bar.bt_full, x.it * kT, x.jt * kT, x.h, x.b * p.bias_b_mul);
-          tma_load_4d(sBT + kAtomB, &mbt, &bar.bt_full, x.it * kT + kHalf, x.jt * kT, x.h, x.b * p.bias_b_mul);
+          if (p.bias_mn) {
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4)       // (query half, key half) pieces of [64 x 64]
+              tma_load_4d(sBT + (q4 >> 1) * kAtomB + (q4 & 1) * 8192, &mbt, &bar.bt_full, x.jt * kT + (q4 & 1) * 64,
+                          x.it * kT + (q4 >> 1) * kHalf, x.h, x.b * p.bias_b_mul);
+          } else {
+            tma_load_4d(sBT, &mbt, &bar.bt_full, x.it * kT, x.jt * kT, x.h, x.b * p.bias_b_mul);
+            tma_load_4d(sBT + kAtomB, &mbt, &bar.bt_full, x.it * kT + kHalf, x.jt * kT, x.h, x.b * p.bias_b_mul);
+          }
         }
         for (int n = x.n0; n < x.n1; ++n, ++g) {
           if (suse >= 1) wait_or_flag(&bar.op_empty[stage], (suse - 1) & 1, abort_flag);
@@ -962,9 +981,21 @@ int bwd_ksplit(int64_t bnh, int nt, int sms) {
   return k < 1 ? 1 : (int)k;
 }
 
+// Can TMA address the caller's bias ([.., queries, keys], 16-bit, keys contiguous, 16-byte multiples elsewhere)?  Then its
+// tiles are loaded as they are and read MN-major; otherwise a transposed 16-bit copy is made first.
+bool bias_tma_ok(const mf_evo_bwd_args& a) {
+  if (a.bias_dtype != MF_BF16 && a.bias_dtype != MF_F16) return false;
+  const int64_t* s = a.bias_strides;
+  if (s[3] != 1 || (reinterpret_cast<uintptr_t>(a.bias) & 15) != 0) return false;
+  if ((s[2] * 2) % 16 != 0 || s[2] <= 0) return false;
+  if (a.H > 1 && ((s[1] * 2) % 16 != 0 || s[1] <= 0)) return false;
+  if (a.B > 1 && s[0] != 0 && ((s[0] * 2) % 16 != 0 || s[0] < 0)) return false;
+  return true;
+}
+
 struct BwdPlan {
   int nt, lpad, ksplit, dq_stream, dbuf, nsplit;
-  bool dq_fp32, part_direct;
+  bool dq_fp32, part_direct, bias_direct;
   size_t off_flags, off_xq, off_xk, off_part, off_dq, off_biasT, total;
 };
 
@@ -997,7 +1028,8 @@ BwdPlan plan_bwd(const mf_evo_bwd_args& a) {
   pl.off_xk = off; off += (size_t)a.B * a.N * pl.nt * kXTileB;
   pl.off_part = off; if (!pl.part_direct) off += align_up(sizeof(float) * (size_t)pl.nsplit * a.B * a.H * a.L * a.L, 256);
   pl.off_dq = off; if (pl.dq_fp32) off += align_up(sizeof(float) * (size_t)a.B * a.N * a.L * a.H * a.D, 256);
-  pl.off_biasT = off; off += align_up(2 * (size_t)a.B * a.H * a.L * pl.lpad, 256);
+  pl.bias_direct = bias_tma_ok(a);
+  pl.off_biasT = off; if (!pl.bias_direct) off += align_up(2 * (size_t)a.B * a.H * a.L * pl.lpad, 256);
   pl.total = off;
   return pl;
 }
@@ -1026,7 +1058,13 @@ int launch_bwd_ws(const mf_evo_bwd_args& a, cudaStream_t st) {
   const int bt_dtype = sizeof(TB) == 2 ? a.bias_dtype : a.dtype;
   TT* biasT = reinterpret_cast<TT*>(ws + pl.off_biasT);
   const int lpad = pl.lpad;
-  {
+  const int bias_b_mul = pl.bias_direct ? (a.bias_strides[0] == 0 ? 0 : 1) : 1;
+  if (pl.bias_direct) {
+    const int64_t dims[4] = {a.L, a.L, a.H, bias_b_mul ? a.B : 1};
+    const int64_t str[4] = {1, a.bias_strides[2], a.bias_strides[1], a.bias_strides[0]};
+    const int box[4] = {64, 64, 1, 1};
+    if ((r = make_tiled_map(&mbt, a.bias, a.bias_dtype, 4, dims, str, box, 128))) return r;
+  } else {
     if (lpad != a.L) MF_CUDA(cudaMemsetAsync(biasT, 0, 2 * (size_t)a.B * a.H * a.L * lpad, st));      // the row padding
     dim3 grid((a.L + 63) / 64, (a.L + 63) / 64, a.B * a.H), block(32, 8);
     transpose_bias_ws_kernel<TB, TT><<<grid, block, 0, st>>>(static_cast<const TB*>(a.bias), biasT, a.H, a.L, lpad, a.bias_strides[0],
@@ -1060,7 +1098,7 @@ int launch_bwd_ws(const mf_evo_bwd_args& a, cudaStream_t st) {
     p.c1 = kLog2e / sqrtf((float)a.D);
     p.fmt = a.dtype == MF_BF16 ? 1u : 0u; p.bfmt = bt_dtype == MF_BF16 ? 1u : 0u;
     p.n_alpha = n_alpha; p.alpha[0] = alpha[0]; p.alpha[1] = alpha[1];
-    p.bias_b_mul = 1;
+    p.bias_b_mul = bias_b_mul; p.bias_mn = pl.bias_direct ? 1 : 0;
     p.xq = xq; p.xk = xk;
     p.part = part;
     p.out16 = pl.part_direct && a.dbias_dtype != MF_F32 ? a.d_bias : nullptr;
@@ -1092,7 +1130,7 @@ int launch_bwd_ws(const mf_evo_bwd_args& a, cudaStream_t st) {
     p.scale = 1.0f / sqrtf((float)a.D); p.c1 = kLog2e * p.scale; p.inv_L = 1.0f / a.L;
     p.fmt = a.dtype == MF_BF16 ? 1u : 0u; p.bfmt = bt_dtype == MF_BF16 ? 1u : 0u;
     p.n_alpha = n_alpha; p.alpha[0] = alpha[0]; p.alpha[1] = alpha[1];
-    p.bias_b_mul = 1;
+    p.bias_b_mul = bias_b_mul; p.bias_mn = pl.bias_direct ? 1 : 0;
     p.xq = xq; p.xk = xk; p.flags = flags;
     p.dbias_direct = dbias_direct ? a.d_bias : nullptr;
     p.dq = a.dq; p.dk = a.dk; p.dv = a.dv;
