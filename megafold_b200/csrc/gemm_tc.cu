@@ -252,7 +252,7 @@ int gemm_tc(const GemmTcArgs& g, cudaStream_t st) {
   p.status = status_word();
   MF_REQUIRE(p.status, MF_ERR_CUDA, "could not allocate the device status word");
   MF_REQUIRE(tc_async_status() == 0, MF_ERR_CUDA, "an earlier tensor-core kernel gave up on a bounded wait; results are invalid");
-  if (g.out_kind == 2) MF_CUDA(cudaMemsetAsync(g.c, 0, sizeof(float) * (size_t)g.M * g.N, st));
+  if (g.out_kind == 2 && !g.accumulate) MF_CUDA(cudaMemsetAsync(g.c, 0, sizeof(float) * (size_t)g.M * g.N, st));
   const size_t smem = 1024 + kStages * (size_t)kStageBytes + 65536;
   const int n_items = p.m_tiles * p.n_tiles * p.k_splits;
   int grid = sms < n_items ? sms : n_items;

@@ -446,6 +446,22 @@ bool lnl_bwd_core_tc_ok(int64_t M, int K, int N, int dtype, bool has_ln, const v
   return (al & 15) == 0;
 }
 
+// The fused LayerNorm-backward row pass over M rows; returns the number of blocks (= rows of `part`, [blocks][2 K]).
+template <typename T>
+int launch_ln_bwd_rows(const float* dyln, const T* x, const T* gain, const T* shift, const float* mean, const float* rstd,
+                       T* dx, T* xln, float* part, int64_t M, int K, cudaStream_t st) {
+  int blocks = (int)((M + 63) / 64); if (blocks > kRowBlocks) blocks = kRowBlocks;
+  const int64_t rpb = (M + blocks - 1) / blocks;
+  blocks = (int)((M + rpb - 1) / rpb);
+  const size_t sm = sizeof(float) * 8 * 2 * K;
+  const int kj = (K + 127) / 128;
+#define MF_ROWS(KJ) ln_bwd_rows_fused_kernel<T, KJ><<<blocks, 256, sm, st>>>(dyln, x, gain, shift, mean, rstd, dx, xln, part, M, K, rpb)
+  if (kj == 1) MF_ROWS(1); else if (kj == 2) MF_ROWS(2); else if (kj == 3) MF_ROWS(3); else MF_ROWS(4);
+#undef MF_ROWS
+  MF_LAUNCHED("ln_bwd_rows_fused_kernel");
+  return blocks;
+}
+
 // Shared tail of LayernormLinear backward: given dy [M,N] computes dx, dw, d_ln_w, d_ln_b, db.
 // gain == nullptr: no LayerNorm (dx = dy @ w^T, dw = x^T dy).
 // tc: both GEMMs on the tensor cores (gemm_tc), with one fused row pass between them.
@@ -466,15 +482,7 @@ int lnl_bwd_core(int64_t M, int K, int N, const T* x, const T* gain, const T* sh
         r = gemm_tc(GemmTcArgs{dy, w, dyln, M, K, N, dtype, 0, 0, 1}, st);
         if (r) return r;
       }
-      int blocks = (int)((M + 63) / 64); if (blocks > kRowBlocks) blocks = kRowBlocks;
-      const int64_t rpb = (M + blocks - 1) / blocks;
-      blocks = (int)((M + rpb - 1) / rpb);
-      const size_t sm = sizeof(float) * 8 * 2 * K;
-      const int kj = (K + 127) / 128;
-#define MF_ROWS(KJ) ln_bwd_rows_fused_kernel<T, KJ><<<blocks, 256, sm, st>>>(dyln, x, gain, shift, mean, rstd, dx, xln, part, M, K, rpb)
-      if (kj == 1) MF_ROWS(1); else if (kj == 2) MF_ROWS(2); else if (kj == 3) MF_ROWS(3); else MF_ROWS(4);
-#undef MF_ROWS
-      MF_LAUNCHED("ln_bwd_rows_fused_kernel");
+      const int blocks = launch_ln_bwd_rows<T>(dyln, x, gain, shift, mean, rstd, dx, xln, part, M, K, st);
       r = colsum_small("lnl_bwd_dgain_dshift", part, blocks, 2 * K, d_ln_w, d_ln_b, K, st);
       if (r) return r;
       if (db) {
@@ -658,23 +666,23 @@ int transition_fwd_simt(const mf_transition_fwd_args& a, cudaStream_t st) {
   return MF_OK;
 }
 
+size_t transition_bwd_fused_bytes(const mf_transition_bwd_args& a);
+
+// Scratch of the path that exactly these arguments take (the choice depends on dtype, sizes and pointer alignment, all of
+// which the caller has filled in when it asks).
 size_t transition_bwd_workspace(const mf_transition_bwd_args& a) {
+  if (transition_bwd_use_tc(a)) {
+    if (transition_bwd_fused_ok(a)) return transition_bwd_fused_bytes(a);
+    const size_t es = dtype_size(a.dtype);
+    return align_up((size_t)a.M * 2 * a.inner * es, 256) + 2 * align_up((size_t)a.M * a.inner * es, 256) +   // h/dh, g, dg
+           align_up((size_t)a.M * a.dim * es, 256) +                                                          // LN(x)
+           lnl_bwd_core_bytes(a.M, a.dim, 2 * a.inner, true, true, a.dtype);
+  }
   size_t simt = align_up((size_t)a.M * 2 * a.inner * dtype_size(a.dtype), 256);     // h, then dh in place
   int S = dw_splits(a.dim, a.inner, a.M);
   if (S > 1) simt += align_up(sizeof(float) * (size_t)S * a.dim * a.inner, 256);     // dw2 slices
   simt += lnl_bwd_core_bytes(a.M, a.dim, 2 * a.inner, a.ln_w != nullptr, false, a.dtype);
-  size_t tc = 0;
-  if (transition_bwd_use_tc(a)) {
-    const size_t es = dtype_size(a.dtype);
-    const size_t fused = align_up((size_t)a.M * a.inner * es, 256) + align_up((size_t)a.M * 2 * a.inner * es, 256) +   // g, dh
-                         align_up(sizeof(float) * (size_t)a.M * a.dim, 256) + align_up(sizeof(float) * (size_t)a.dim * 2 * a.inner, 256) +
-                         lnl_bwd_core_bytes(a.M, a.dim, 2 * a.inner, true, true, a.dtype);
-    if (fused > simt) simt = fused;
-    tc = align_up((size_t)a.M * 2 * a.inner * es, 256) + 2 * align_up((size_t)a.M * a.inner * es, 256) +   // h/dh, g, dg
-         align_up((size_t)a.M * a.dim * es, 256) +                                                          // LN(x)
-         lnl_bwd_core_bytes(a.M, a.dim, 2 * a.inner, true, true, a.dtype);
-  }
-  return simt > tc ? simt : tc;
+  return simt;
 }
 
 // Tensor-core composition: xln = LN(x) from the saved statistics; h = xln w1 (recomputed, never saved by forward);
@@ -711,25 +719,68 @@ int transition_bwd_tc(const mf_transition_bwd_args& a, cudaStream_t st) {
 }
 
 // Fused composition (dim = 128): one kernel recomputes h on chip and leaves g, dh (chunk-ordered columns) and dyln in
-// HBM; then the LayerNorm row pass and the two weight-gradient GEMMs.
+// HBM; then the LayerNorm row pass and the two weight-gradient GEMMs.  The rows are processed in ranges of at most
+// kTransitionChunkRows so that the scratch (g, dh, dyln, LN(x): 3.8 KB per row at inner = 512) stays below what the
+// reference's forward keeps as saved activations; the weight gradients accumulate over the ranges, the partial column
+// sums of every range are reduced together at the end.
+constexpr int64_t kTransitionChunkRows = 131072;
+struct TransitionChunks { int n; int64_t rows; };
+TransitionChunks transition_chunks(int64_t M) {
+  TransitionChunks c;
+  c.n = (int)((M + kTransitionChunkRows - 1) / kTransitionChunkRows);
+  if (c.n < 1) c.n = 1;
+  c.rows = (((M + c.n - 1) / c.n) + 127) / 128 * 128;
+  return c;
+}
+size_t transition_bwd_fused_bytes(const mf_transition_bwd_args& a) {
+  const size_t es = dtype_size(a.dtype);
+  const TransitionChunks ch = transition_chunks(a.M);
+  const size_t rows = (size_t)(ch.rows < a.M ? ch.rows : a.M);
+  return align_up(rows * a.inner * es, 256) + align_up(rows * 2 * a.inner * es, 256) + align_up(sizeof(float) * rows * a.dim, 256) +
+         align_up(rows * a.dim * es, 256) + align_up(sizeof(float) * (size_t)a.dim * 2 * a.inner, 256) +
+         align_up(sizeof(float) * (size_t)ch.n * kRowBlocks * 2 * a.dim, 256);
+}
+
 template <typename T>
 int transition_bwd_fused_path(const mf_transition_bwd_args& a, cudaStream_t st) {
   Carver ws(a.workspace);
-  const int I = a.inner;
+  const int I = a.inner, K = a.dim;
   const int64_t M = a.M;
-  T* g = ws.take<T>((size_t)M * I);
-  T* dh = ws.take<T>((size_t)M * 2 * I);
-  float* dyln = ws.take<float>((size_t)M * a.dim);
-  float* dw1p = ws.take<float>((size_t)a.dim * 2 * I);
-  int r = transition_bwd_fused(a, g, dh, dyln, st);
+  const TransitionChunks ch = transition_chunks(M);
+  const size_t rows_max = (size_t)(ch.rows < M ? ch.rows : M);
+  T* g = ws.take<T>(rows_max * I);
+  T* dh = ws.take<T>(rows_max * 2 * I);
+  float* dyln = ws.take<float>(rows_max * K);
+  T* xln = ws.take<T>(rows_max * K);
+  float* dw1p = ws.take<float>((size_t)K * 2 * I);
+  float* part = ws.take<float>((size_t)ch.n * kRowBlocks * 2 * K);
+  int part_rows = 0;
+  for (int c = 0; c < ch.n; ++c) {
+    const int64_t m0 = (int64_t)c * ch.rows, rows = (m0 + ch.rows < M ? ch.rows : M - m0);
+    if (rows <= 0) break;
+    mf_transition_bwd_args ac = a;
+    ac.M = rows;
+    ac.x = static_cast<const T*>(a.x) + m0 * K;
+    ac.dy = static_cast<const T*>(a.dy) + m0 * K;
+    ac.dx = static_cast<T*>(a.dx) + m0 * K;
+    ac.mean = a.mean + m0; ac.rstd = a.rstd + m0;
+    int r = transition_bwd_fused(ac, g, dh, dyln, st);
+    if (r) return r;
+    GemmTcArgs g2{ac.dy, g, a.dw2, K, I, rows, a.dtype, 1, 1, 2};
+    g2.accumulate = c > 0;
+    r = gemm_tc(g2, st);
+    if (r) return r;
+    part_rows += launch_ln_bwd_rows<T>(dyln, static_cast<const T*>(ac.x), static_cast<const T*>(a.ln_w), static_cast<const T*>(a.ln_b),
+                                       ac.mean, ac.rstd, static_cast<T*>(ac.dx), xln, part + (size_t)part_rows * 2 * K, rows, K, st);
+    // dw1 (chunk-ordered columns) += LN(x)^T dh
+    GemmTcArgs g1{xln, dh, dw1p, K, 2 * I, rows, a.dtype, 1, 1, 2};
+    g1.accumulate = c > 0;
+    r = gemm_tc(g1, st);
+    if (r) return r;
+  }
+  int r = colsum_small("transition_bwd_dgain_dshift", part, part_rows, 2 * K, a.d_ln_w, a.d_ln_b, K, st);
   if (r) return r;
-  r = gemm_tc(GemmTcArgs{a.dy, g, a.dw2, a.dim, I, M, a.dtype, 1, 1, 2}, st);
-  if (r) return r;
-  r = lnl_bwd_core<T>(M, a.dim, 2 * I, static_cast<const T*>(a.x), static_cast<const T*>(a.ln_w),
-                      static_cast<const T*>(a.ln_b), static_cast<const T*>(a.w1), dh, a.mean, a.rstd,
-                      static_cast<T*>(a.dx), dw1p, nullptr, a.d_ln_w, a.d_ln_b, ws, true, a.dtype, st, nullptr, dyln);
-  if (r) return r;
-  return unpermute_dw1(dw1p, a.dw1, a.dim, I, st);
+  return unpermute_dw1(dw1p, a.dw1, K, I, st);
 }
 
 int transition_bwd(const mf_transition_bwd_args& a, cudaStream_t st) {
