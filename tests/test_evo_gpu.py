@@ -130,6 +130,32 @@ def test_fp32_bias_with_bf16_qkv():
         assert_close_lowp(g_, r_, n)
 
 
+@pytest.mark.parametrize("L", [128, 150])
+def test_bias_views_that_are_not_contiguous(L):
+    """A pair bias shared by the batch elements (expanded view: batch stride 0) and one whose rows are slices of a wider
+    buffer (row stride larger than L).  With L = 128 TMA can address both as they are (forward tiles, and the backward's
+    MN-major operand); with L = 150 the rows are not 16-byte multiples and the backward makes its transposed copy."""
+    B, N, H, D = 2, 3, 2, 32
+    c = make_case(B, N, L, H, D, seed=11 + L)
+    dt = torch.bfloat16
+    q, k, v, d_o = (c[n].to(DEV, dt) for n in ("q", "k", "v", "d_out"))
+    mask = c["mask"].to(DEV)
+    shared = c["bias"][:1].to(DEV, dt)                                   # [1, 1, H, L, L]
+    wide = torch.zeros(B, 1, H, L, L + 8, device=DEV, dtype=dt)
+    wide[..., :L] = c["bias"].to(DEV, dt)
+    for name, bias, ref_bias in (("expanded", shared.expand(B, 1, H, L, L), c["bias"][:1].expand(B, 1, H, L, L)),
+                                 ("row-sliced", wide[..., :L], c["bias"])):
+        assert not bias.is_contiguous()
+        o, lse = mfb.evo_attention_forward(q, k, v, mask, bias)
+        dq, dk, dv, db = mfb.evo_attention_backward(d_o, q, k, v, mask, bias, o, lse)
+        torch.cuda.synchronize()
+        assert _lib.last_path() == "tcgen05"
+        r = rounded(c, dt)
+        ref = orc.evo_attention_fwd_bwd(r["q"], r["k"], r["v"], r["mask"], ref_bias.to(dt).float(), r["d_out"])
+        for g_, r_, n in zip((o, dq, dk, dv, db), ref, NAMES):
+            assert_close_lowp(g_, r_, f"{name} bias, L={L}: {n}", summed_over=N if n == "dbias" else 1)
+
+
 def test_additive_float_mask_and_fully_masked_row():
     c = cases.evo_small()
     add = dict(c)
