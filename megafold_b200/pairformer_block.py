@@ -188,7 +188,7 @@ class PairformerBlock(nn.Module):
         q, k, v, g = y.unbind(dim=3)                                # strided views, no copies
         res_mask = mask.view(1, 1, 1, 1, L).expand(1, n, 1, 1, L)
         o = self.ops.attention(q, k, v, res_mask, bias)             # [1, n, L, H, D]
-        o = o.reshape(n, L, a.inner) * torch.sigmoid(g.reshape(n, L, a.inner))
+        o = (o * torch.sigmoid(g)).reshape(n, L, a.inner)            # the gate is read through its strided view: no packing copy
         return F.linear(o, a.w_out)
 
     # ---- block -------------------------------------------------------------------------------------
