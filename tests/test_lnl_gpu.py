@@ -214,3 +214,23 @@ def test_transition_backward_tensor_core_path(M, dim, ef, dtype):
     ref = orc.transition_fwd_bwd(*[t.float().cpu() for t in (x, ln_w, ln_b, w1, w2, dy)])
     for g_, r_, n in zip(got, ref[1:], ("dx", "d_ln_w", "d_ln_b", "dw1", "dw2")):
         lowp(g_, r_, n, M)
+
+
+def test_transition_backward_in_two_row_ranges():
+    """More than 131072 rows: the fused backward goes through the rows in ranges that share one scratch area, the weight
+    gradients accumulate over the ranges and the partial column sums of all ranges are reduced together.  M is chosen so
+    that the second range is ragged (not a multiple of the 128-row tile).  Oracle: fp32 on the GPU, TF32 off."""
+    M, dim, ef = 131072 + 4096 + 77, 128, 4
+    x, ln_w, ln_b, w1, w2, dy = [t.to(DEV, torch.bfloat16) for t in _transition_case(M, dim, ef, seed=9)]
+    _, mean, rstd = mfb.transition_forward(x, ln_w, ln_b, w1, w2)
+    got = mfb.transition_backward(dy, x, ln_w, ln_b, w1, w2, mean, rstd)
+    assert _lib.last_path() == "tcgen05"
+    a, b = torch.backends.cuda.matmul.allow_tf32, torch.backends.cudnn.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    torch.backends.cudnn.allow_tf32 = False
+    try:
+        ref = orc.transition_fwd_bwd(*[t.float() for t in (x, ln_w, ln_b, w1, w2, dy)])
+    finally:
+        torch.backends.cuda.matmul.allow_tf32, torch.backends.cudnn.allow_tf32 = a, b
+    for g_, r_, n in zip(got, ref[1:], ("dx", "d_ln_w", "d_ln_b", "dw1", "dw2")):
+        lowp(g_, r_, n, M)
