@@ -1,10 +1,11 @@
-// Pair-biased masked attention backward on the tensor cores (tcgen05 + TMEM + TMA), head sizes up to 32.
+// Pair-biased masked attention backward on the tensor cores (tcgen05 + TMEM + TMA), head sizes up to 64 (as one or two
+// halves of 32 columns, template parameter NH).
 //
 // Two kernels share the transposed-score scheme (keys on the TMEM lanes):
 //
-//   S''^T = K_j Q_i^T + sqrt(D) * bias^T        dP^T = V_j dO_i^T          (tcgen05.mma into TMEM; the bias term is
-//   P^T   = 2^(c1 * S''^T + mask_j - lse2_i)    dS^T = P^T (dP^T - delta_i)  itself a product with alpha * I, see
-//                                                                            evo_tc_common.cuh)
+//   S''^T = K_j Q_i^T + sqrt(D) * bias^T + terms        dP''^T = V_j dO_i^T - delta_i      (tcgen05.mma into TMEM; the bias
+//   P^T   = 2^(c1 * S''^T)                              dS^T   = P^T dP''^T                 term is itself a product with
+//   alpha * I, and the key mask, the log-sum-exp and delta enter through one more K = 16 product: evo_tc_common.cuh)
 //
 // evo_bwd_ws_kernel (dQ, dK, dV).  A persistent CTA owns a (b, n, h) - or a range of its key tiles - and walks the
 // key tiles j and, inside, the query tiles i in HALF blocks of [128 keys x 64 queries].  Two teams of eight compute
@@ -18,9 +19,12 @@
 // evo_dbias_ws_kernel (dBias = sum of dS over the N rows that share the bias).  A CTA keeps ONE (b, h, i tile,
 // j tile) and walks a range of rows n: scores and dP for row n+1 are produced while the 16 compute warps turn row n
 // into dS and add it to register accumulators; nothing is reduced through memory until the range is done.  Ranges
-// are summed in a fixed order afterwards, so dBias is bit-reproducible.
+// are summed in a fixed order afterwards, so dBias is bit-reproducible.  With one row per bias (N = 1) the kernel is not
+// run: dS is the answer and evo_bwd_ws_kernel stores it.
 //
-// delta_i = rowsum(dO_i * O_i) comes from a small pre-kernel, bias^T from a transposing copy.  All waits are bounded
+// delta_i = rowsum(dO_i * O_i) and the term tiles come from a small pre-kernel.  The bias tile of a half block is the A
+// operand [128 keys x 16 queries] of the products that add it: the caller's bias ([queries][keys]) is exactly that in
+// MN-major form and is loaded in place when TMA can address it; otherwise a transposed 16-bit copy is made first.  All waits are bounded
 // (tc.cuh); on expiry the CTA runs dry without touching global memory and the host sees mf_async_status() != 0.
 #include <type_traits>
 
