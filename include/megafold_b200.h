@@ -91,7 +91,8 @@ MF_API int mf_evo_fwd(const mf_evo_fwd_args* args, void* stream);
  * the N rows; it is fully overwritten (no need to zero it).  d_bias is summed in a fixed order on every
  * path and is bit-reproducible run to run; so are dk and dv.  dq is bit-reproducible except where the
  * tensor-core path spreads one row's key tiles over several CTAs or streams dq through memory (N*B*H below
- * the SM count, or L > 768): those partial sums meet in fp32 atomic adds whose order varies.
+ * the SM count, or more than six query tiles of 128 - two with a head size above 32): those partial sums meet in
+ * fp32 atomic adds whose order varies.
  * workspace: at least mf_evo_bwd_workspace_bytes() bytes, 256-byte aligned.
  *
  * Replaces EvoformerAttention.backward, evoattention.py:783-903 (kernels _attn_bwd_preprocess
@@ -225,6 +226,8 @@ typedef struct mf_transition_bwd_args {
   void* workspace; size_t workspace_bytes;
 } mf_transition_bwd_args;
 
+/* The scratch size is that of the path these very arguments take (it depends on dtype, sizes and pointer alignment):
+ * ask with the structure filled in as it will be passed to mf_transition_bwd. */
 MF_API size_t mf_transition_bwd_workspace_bytes(const mf_transition_bwd_args* args);
 MF_API int mf_transition_bwd(const mf_transition_bwd_args* args, void* stream);
 
