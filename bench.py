@@ -373,12 +373,14 @@ def run_only(args):
     from megafold_b200.fused_transition import transition_backward, transition_forward
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
-    if args.only in ("fwd", "bwd", "step"):
-        c = {k: v.to(dev) for k, v in workloads.triangle_attention(L=L, N=args.rows, H=H, D=D).items()}
+    if args.only in ("fwd", "bwd", "step", "single_step"):
+        # single_step: configuration 3 (single-representation attention: one row, sixteen heads of 24, L = 768)
+        c = {k: v.to(dev) for k, v in (workloads.single_attention() if args.only == "single_step"
+                                       else workloads.triangle_attention(L=L, N=args.rows, H=H, D=D)).items()}
         o, lse = mfb.evo_attention_forward(c["q"], c["k"], c["v"], c["mask"], c["bias"])
         if args.only == "fwd":
             fn = lambda: mfb.evo_attention_forward(c["q"], c["k"], c["v"], c["mask"], c["bias"])            # noqa: E731
-        elif args.only == "step":
+        elif args.only in ("step", "single_step"):
             def fn():
                 o2, lse2 = mfb.evo_attention_forward(c["q"], c["k"], c["v"], c["mask"], c["bias"])
                 mfb.evo_attention_backward(c["d_out"], c["q"], c["k"], c["v"], c["mask"], c["bias"], o2, lse2)
@@ -585,7 +587,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--rows", type=int, default=ROWS, help="rows (N) per GPU; smaller values give profiler-sized cases")
-    ap.add_argument("--only", default="all", choices=["all", "fwd", "bwd", "step", "lnl", "lnl_bwd", "transition", "transition_bwd", "block"],
+    ap.add_argument("--only", default="all", choices=["all", "fwd", "bwd", "step", "single_step", "lnl", "lnl_bwd", "transition", "transition_bwd", "block"],
                     help="run just one kernel family in the timed loop (for ncu captures); prints no JSON line")
     ap.add_argument("--L", type=int, default=768, help="crop length of --only block")
     ap.add_argument("--no-graph", action="store_true", help="--only block: issue the step directly instead of replaying a CUDA graph")
